@@ -1,0 +1,212 @@
+/*
+ * C ABI of the sm_100a (B200) MoE-layer and DSA/MLA sparse-decode library.
+ *
+ * Every entry point returns a status code (0 = ok), takes plain device
+ * pointers and sizes, works asynchronously on the given CUDA stream and does
+ * no host synchronisation.  Scratch memory comes from a workspace handle
+ * (NULL selects a lazily created per-device default workspace).  A workspace
+ * serves one call at a time; calls on one stream are ordered by the stream.
+ *
+ * The comment above each declaration names the reference interface it stands
+ * in for (file:line in arun-reddy-a/llm-sys-project).
+ */
+#ifndef B200_MOE_DSA_H
+#define B200_MOE_DSA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200_API __attribute__((visibility("default")))
+#else
+#define B200_API
+#endif
+
+typedef struct CUstream_st* b200_stream_t; /* == cudaStream_t */
+typedef struct b200_ws b200_ws;
+
+enum b200_status {
+    B200_OK = 0,
+    B200_BAD_SHAPE = 1,   /* a dimension is zero/negative or breaks a divisibility rule */
+    B200_UNSUPPORTED = 2, /* valid request this build has no kernel for */
+    B200_CUDA_ERROR = 3,  /* a CUDA runtime/driver call failed; see b200_last_error_string */
+    B200_TIMEOUT = 4,     /* a bounded device-side wait ran out (read back by b200_ws_device_status) */
+    B200_NCCL_ERROR = 5,
+    B200_BAD_ARG = 6      /* null pointer / misaligned pointer */
+};
+
+/* kernels/moe/naive_moe.cuh:9-15 (struct MoeConfig) — same five ints, same order. */
+typedef struct b200_moe_config {
+    int num_tokens;       /* T */
+    int num_experts;      /* E */
+    int top_k;            /* K */
+    int hidden_dim;       /* D */
+    int intermediate_dim; /* I */
+} b200_moe_config;
+
+/* kernels/dsa/naive_dsa.cuh:9-17 (struct DsaConfig) — same seven ints, same order.
+ * page_size and total_kv_tokens are carried but, as in the reference, not read:
+ * the cache is flat [N, D*] and indices are flat physical token ids. */
+typedef struct b200_dsa_config {
+    int num_queries;         /* Q */
+    int num_heads;           /* H */
+    int head_dim_compressed; /* Dc */
+    int head_dim_positional; /* Dp */
+    int num_selected_kv;     /* S */
+    int page_size;           /* P */
+    int total_kv_tokens;     /* N */
+} b200_dsa_config;
+
+/* Routing modes of the FP8 layer. */
+enum b200_scoring {
+    B200_SCORE_SOFTMAX = 0,        /* the reference's gate: softmax over all E, top-K, renormalise */
+    B200_SCORE_SIGMOID_GROUPED = 1 /* sigmoid + per-expert bias, group-limited top-K, routed scaling */
+};
+
+/* Extended configuration of the FP8 block-scale layer (no reference counterpart;
+ * extends MoeConfig, kernels/moe/naive_moe.cuh:9-15). */
+typedef struct b200_moe_fp8_config {
+    int num_tokens, num_experts, top_k, hidden_dim, intermediate_dim;
+    int scoring;        /* enum b200_scoring */
+    int n_group;        /* expert groups (E % n_group == 0); 1 = ungrouped */
+    int topk_group;     /* groups kept per token */
+    float routed_scale; /* factor applied to the normalised weights */
+} b200_moe_fp8_config;
+
+/* --------------------------------------------------------------------------- */
+/* Library / workspace                                                         */
+/* --------------------------------------------------------------------------- */
+B200_API const char* b200_status_string(int status);
+B200_API const char* b200_last_error_string(void); /* text of the last CUDA error seen by this thread */
+B200_API int b200_ws_create(b200_ws** ws);          /* on the current device */
+B200_API int b200_ws_destroy(b200_ws* ws);
+B200_API int b200_ws_reserve(b200_ws* ws, size_t bytes); /* pre-size so timed calls never allocate */
+B200_API size_t b200_ws_capacity(const b200_ws* ws);
+/* Synchronises `stream`, then reads and clears the device status word. */
+B200_API int b200_ws_device_status(b200_ws* ws, b200_stream_t stream, int* status);
+/* Number of kernels this library has launched on the calling thread since the last reset. */
+B200_API long long b200_launch_count(int reset);
+
+/* --------------------------------------------------------------------------- */
+/* MoE layer, fp32 (the reference's data types)                                 */
+/* --------------------------------------------------------------------------- */
+/* kernels/moe/naive_moe.cuh:73-75 / naive_moe.cu:400-471 (moe_forward): whole layer,
+ * output [T,D] is overwritten. */
+B200_API int b200_moe_forward_f32(b200_ws* ws, const float* x, const float* gate_w, const float* w1,
+                                  const float* w2, float* out, const b200_moe_config* cfg, b200_stream_t stream);
+/* naive_moe.cuh:27-29 / naive_moe.cu:341-355 (moe_gate): ids/weights [T,K] in the
+ * reference's replacement-slot order; ties keep the lowest expert id. */
+B200_API int b200_moe_gate_f32(b200_ws* ws, const float* x, const float* gate_w, int* expert_ids,
+                               float* expert_w, const b200_moe_config* cfg, b200_stream_t stream);
+/* Replaces the E serial gather scans (naive_moe.cu:147-166, :424-429) by one stable
+ * counting pass: counts[E], offsets[E+1] (exclusive prefix sum), row_pair[T*K] where
+ * row_pair[r] = t*K+k of the pair in sorted row r (experts ascending, tokens ascending). */
+B200_API int b200_moe_permute(b200_ws* ws, const int* expert_ids, int T, int K, int E, int* counts,
+                              int* offsets, int* row_pair, b200_stream_t stream);
+/* naive_moe.cuh:38-41 / naive_moe.cu:357-366 (moe_gather), one expert. */
+B200_API int b200_moe_gather_f32(const float* x, const int* expert_ids, int expert_id, float* gathered,
+                                 int* token_map, int* count, const b200_moe_config* cfg, b200_stream_t stream);
+/* naive_moe.cuh:44-45 (naive_gemm): C[M,N] = A[M,K] * B[K,N], row-major. */
+B200_API int b200_gemm_f32(const float* A, const float* B, float* C, int M, int N, int K, b200_stream_t stream);
+/* naive_moe.cuh:50-51 (swiglu): out[i] = silu(gate[i]) * up[i]. */
+B200_API int b200_swiglu_f32(const float* gate, const float* up, float* out, int n, b200_stream_t stream);
+/* naive_moe.cuh:59-62 / naive_moe.cu:384-395 (moe_scatter): out[token_map[i],:] += w * expert_out[i,:].
+ * Unlike the reference (one thread per column, D <= 1024) any D is accepted. */
+B200_API int b200_moe_scatter_f32(const float* expert_out, const int* token_map, const float* expert_w,
+                                  const int* expert_ids, int expert_id, float* out, int count,
+                                  const b200_moe_config* cfg, b200_stream_t stream);
+
+/* --------------------------------------------------------------------------- */
+/* MoE layer, FP8 e4m3 block-scale (no reference counterpart; extends           */
+/* moe_forward, naive_moe.cu:400-471, to the DeepSeek-V3 data types)            */
+/* --------------------------------------------------------------------------- */
+/* Quantisers: scale = amax/448 (1 for an all-zero block), q = e4m3_rn_sat(x/scale).
+ * Activations: 1x128 blocks, scales [rows, cols/128].  Weights: 128x128 blocks,
+ * scales [rows/128, cols/128] (stack experts along rows). */
+B200_API int b200_quant_act_1x128(const float* x, uint8_t* q, float* scales, long long rows, int cols,
+                                  b200_stream_t stream);
+B200_API int b200_quant_weight_128x128(const float* w, uint8_t* q, float* scales, long long rows, int cols,
+                                       b200_stream_t stream);
+/* Router on the dequantised FP8 activations: logits (fp32 fma chain over d), then
+ * softmax / top-K as moe_gate, or sigmoid + bias + group-limited top-K.  Also fills
+ * counts[E] (tokens per expert; may be NULL). bias may be NULL. logits_out may be NULL. */
+B200_API int b200_moe_route_fp8(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w,
+                                const float* bias, int* expert_ids, float* expert_w, int* counts,
+                                float* logits_out, const b200_moe_fp8_config* cfg, b200_stream_t stream);
+/* Whole layer: route, permute, grouped GEMM1 (+SwiGLU +requantise), grouped GEMM2
+ * (+router weight +scatter-add).  xq [T,D] e4m3, xs [T,D/128]; w1q [E,2I,D] with
+ * scales [E,2I/128,D/128] (rows [0,I) gate, [I,2I) up, naive_moe.cuh:71); w2q [E,D,I]
+ * with scales [E,D/128,I/128]; out [T,D] fp32, overwritten.  D % 128 == 0, I % 128 == 0. */
+B200_API int b200_moe_fp8_forward(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w,
+                                  const float* bias, const uint8_t* w1q, const float* w1s, const uint8_t* w2q,
+                                  const float* w2s, float* out, const b200_moe_fp8_config* cfg,
+                                  b200_stream_t stream);
+/* Same with the routing given (ids/weights [T,K]); ids outside [0,E) are skipped.
+ * This is the expert-parallel building block: E counts the local experts. */
+B200_API int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                                  const float* expert_w, const uint8_t* w1q, const float* w1s,
+                                  const uint8_t* w2q, const float* w2s, float* out,
+                                  const b200_moe_fp8_config* cfg, b200_stream_t stream);
+/* Stage access for parity tests: runs permute + GEMM1 and copies the requantised
+ * activations of sorted rows out (act_q [rows,I], act_s [rows,I/128], rows = T*K upper bound). */
+B200_API int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                                      const uint8_t* w1q, const float* w1s, uint8_t* act_q, float* act_s,
+                                      int* offsets, int* row_pair, const b200_moe_fp8_config* cfg,
+                                      b200_stream_t stream);
+
+/* --------------------------------------------------------------------------- */
+/* DSA / MLA sparse decode                                                      */
+/* --------------------------------------------------------------------------- */
+/* kernels/dsa/naive_dsa.cuh:79-87 / naive_dsa.cu:435-474 (dsa_forward), fp32, one fused
+ * kernel (gather + 576-dim dot + scale + online softmax + PV).  Any index order,
+ * duplicates allowed; offsets are 64-bit. */
+B200_API int b200_dsa_forward_f32(b200_ws* ws, const float* q_nope, const float* q_pe, const float* kc,
+                                  const float* kp, const float* v, const int* idx, float* out,
+                                  const b200_dsa_config* cfg, b200_stream_t stream);
+/* Same layer on bf16 inputs with fp32 accumulation on the tensor cores (tcgen05/TMEM);
+ * out [Q,H,Dc] fp32.  Requires H == 128 or 64, Dc == 512, Dp == 64, S % 64 == 0. */
+B200_API int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe,
+                                   const uint16_t* kc, const uint16_t* kp, const uint16_t* v, const int* idx,
+                                   float* out, const b200_dsa_config* cfg, b200_stream_t stream);
+/* naive_dsa.cuh:31-37 (dsa_kv_gather) */
+B200_API int b200_dsa_kv_gather_f32(const float* kc, const float* kp, const float* v, const int* idx,
+                                    float* g_kc, float* g_kp, float* g_v, const b200_dsa_config* cfg,
+                                    b200_stream_t stream);
+/* naive_dsa.cuh:43-44, :50-51, :55-58 (dsa_dot_compressed / dsa_dot_positional / dsa_dot_fused):
+ * scores[q,h,s] += dot(...) on already gathered rows; either half may be NULL. */
+B200_API int b200_dsa_dot_f32(const float* q_nope, const float* q_pe, const float* g_kc, const float* g_kp,
+                              float* scores, const b200_dsa_config* cfg, b200_stream_t stream);
+/* naive_dsa.cuh:62 (dsa_softmax): in place over S per (q,h). */
+B200_API int b200_dsa_softmax_f32(float* scores, const b200_dsa_config* cfg, b200_stream_t stream);
+/* naive_dsa.cuh:68-69 (dsa_output_proj): out[q,h,d] = sum_s attn[q,h,s] * g_v[q,s,d]. */
+B200_API int b200_dsa_output_proj_f32(const float* attn, const float* g_v, float* out, const b200_dsa_config* cfg,
+                                      b200_stream_t stream);
+
+/* --------------------------------------------------------------------------- */
+/* Synthetic inputs (stand in for utils/cuda_utils.cuh:56-60 random_fill at      */
+/* sizes a host loop cannot fill): counter-based, value i depends only on        */
+/* (seed, i); identical bits to the host twin in the Python package.             */
+/* --------------------------------------------------------------------------- */
+B200_API int b200_fill_normal_f32(float* dst, long long n, unsigned long long seed, float sigma,
+                                  b200_stream_t stream);
+B200_API int b200_fill_normal_bf16(uint16_t* dst, long long n, unsigned long long seed, float sigma,
+                                   b200_stream_t stream);
+/* Generates N(0,sigma) values block by block and quantises them on the fly
+ * (weights: 128x128 blocks; activations: 1x128) without an fp32 copy in memory. */
+B200_API int b200_fill_normal_fp8_w128(uint8_t* q, float* scales, long long rows, int cols,
+                                       unsigned long long seed, float sigma, b200_stream_t stream);
+
+/* Tensor-core self check: D[128,N] = A[128,K] * B[N,K]^T through the same shared-memory
+ * descriptors the production kernels use.  mode 0: bf16, both operands K-major;
+ * mode 1: bf16, B stored [K,N] (MN-major); mode 2: e4m3 K-major.  a/b are raw bits. */
+B200_API int b200_umma_selftest(int mode, const void* a, const void* b, float* d, int N, int K,
+                                b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_MOE_DSA_H */

@@ -1,0 +1,18 @@
+// Internal launch helpers shared by the MoE translation units.
+#pragma once
+#include "common.cuh"
+
+// Width of one reduction chunk of the FP8 router's logits (see moe_route.cu).
+#define MOE_GATE_CHUNK 1024
+
+void b200_count_launch(int n);
+
+int moe_gate_chunks(int D, bool fp8);
+int launch_gate_logits(const void* x, const float* xs, const float* wg, float* partials, int T, int E, int D,
+                       bool fp8, cudaStream_t stream);
+int launch_route_select(const float* partials, int n_chunks, const float* bias, int* ids, float* wts, int* counts,
+                        float* logits_out, int T, int E, int K, int scoring, int n_group, int topk_group,
+                        float routed_scale, cudaStream_t stream);
+int launch_permute(const int* ids, int T, int K, int E, int* counts, int* offsets, int* row_pair,
+                   cudaStream_t stream);
+int check_route_cfg(int T, int E, int K, int D, int scoring, int n_group, int topk_group);
