@@ -158,6 +158,12 @@ B200_API int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const floa
                                       int* offsets, int* row_pair, const b200_moe_fp8_config* cfg,
                                       b200_stream_t stream);
 
+/* Measurement aid (no reference counterpart): when enabled, CUDA events are recorded on
+ * the launch stream around the two grouped GEMM kernels of every FP8 layer call; the read
+ * returns the device time of the last call's GEMM1 and GEMM2 in milliseconds. */
+B200_API int b200_moe_fp8_profile(int enable);
+B200_API int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms);
+
 /* --------------------------------------------------------------------------- */
 /* DSA / MLA sparse decode                                                      */
 /* --------------------------------------------------------------------------- */

@@ -1,0 +1,514 @@
+// FP8 (e4m3) block-scale MoE expert path for sm_100a.
+//
+// Replaces the reference's per-expert host loop (kernels/moe/naive_moe.cu:424-469: gather,
+// D2H count + stream sync, GEMM1, SwiGLU, GEMM2, scatter; 5 launches and one host sync per
+// expert) with one row-sort pass and two persistent grouped GEMM launches:
+//
+//   sort_rows_fp8_kernel   expert-sorted copy of the FP8 rows + 1x128 scales, and the
+//                          row -> token / router-weight maps.
+//   grouped_gemm_fp8<1>    act = requant_1x128( silu(x W1g^T) * (x W1u^T) )   (SwiGLU and
+//                          requantisation fused in the epilogue: no fp32 GEMM1 output in HBM)
+//   grouped_gemm_fp8<2>    out[token] += w * (act W2^T)                      (router weight and
+//                          scatter-add fused in the epilogue)
+//
+// GEMM structure (one CTA per SM, tiles 128 x 256 x 128 handed out round-robin, expert-major):
+//   warp 8      TMA producer: A tile (128 rows x 128 B) and B tile (256 rows x 128 B) per
+//               K block into a 4-stage shared-memory ring (128-byte swizzle, K-major).
+//   warp 9      MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block into one
+//               of two 256-column TMEM accumulator stages, started fresh for every K block.
+//   warps 0-7   promotion + epilogue: tcgen05.ld the K block's partial sums and fold them
+//               into fp32 registers with a_scale[row,kb] * w_scale[nblk,kb] (the scales are
+//               arbitrary fp32 values, so the scaling cannot be left to the tensor core).
+// Every mbarrier wait is bounded; on give-up the CTA flags B200_TIMEOUT and winds down.
+#include "common.cuh"
+#include "moe_internal.cuh"
+#include "tma_host.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 128;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;            // 16384
+constexpr int B_BYTES = BN * BK;            // 32768
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_EPI_THREADS = 256;
+constexpr int GEMM_THREADS = 320;
+constexpr int MAX_E = 1024;
+
+struct GemmSmem {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint64_t amax_bar[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    int total_tiles;
+    int tile_prefix[MAX_E + 1];
+    float amax[2][2][BM];   // [tile parity][warpgroup][row]
+};
+
+constexpr size_t GEMM_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(GemmSmem);
+
+struct GemmParams {
+    const float* a_scale;      // [rows, nkb]
+    const float* w_scale;      // MODE 1: [E, 2I/128, D/128]   MODE 2: [E, D/128, I/128]
+    const int* offsets;        // [E+1]
+    const int* row_tok;        // MODE 2
+    const float* row_w;        // MODE 2
+    uint8_t* act_q;            // MODE 1 out [rows, I]
+    float* act_s;              // MODE 1 out [rows, I/128]
+    float* out;                // MODE 2 out [T, D]
+    int* status;
+    int E, D, I;
+    long long total_rows;      // capacity of the sorted row buffers
+};
+
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+                 : "memory");
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    GemmSmem* sm = reinterpret_cast<GemmSmem*>(tiles + (size_t)STAGES * STAGE_BYTES);
+    volatile int* abort_flag = &sm->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Kdim = (MODE == 1) ? p.D : p.I;
+    const int nkb = Kdim / BK;
+    const int NT = (MODE == 1) ? p.I / 128 : p.D / 256;     // N tiles per expert
+    const int w_rows = (MODE == 1) ? 2 * p.I : p.D;         // weight rows per expert
+
+    // ---- prologue ---------------------------------------------------------
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { ptx::mbar_init(&sm->full[s], 1); ptx::mbar_init(&sm->empty[s], 1); }
+        for (int a = 0; a < 2; a++) {
+            ptx::mbar_init(&sm->tmem_full[a], 1);
+            ptx::mbar_init(&sm->tmem_empty[a], NUM_EPI_THREADS);
+            ptx::mbar_init(&sm->amax_bar[a], NUM_EPI_THREADS);
+        }
+        sm->abort_flag = 0;
+        int acc = 0;
+        for (int e = 0; e < p.E; e++) {
+            sm->tile_prefix[e] = acc;
+            int cnt = p.offsets[e + 1] - p.offsets[e];
+            acc += ((cnt + BM - 1) / BM) * NT;
+        }
+        sm->tile_prefix[p.E] = acc;
+        sm->total_tiles = acc;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 9) {
+        ptx::tmem_alloc(&sm->tmem_base, 512);
+        ptx::tmem_relinquish();
+    }
+    if (warp == 8 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = sm->tmem_base;
+    const int total_tiles = sm->total_tiles;
+
+    // tile -> (expert, m_tile, n_tile): expert-major, then n, then m, so the CTAs that run
+    // together walk through one expert's weights once.
+    auto locate = [&](int tile, int& e, int& m_tile, int& n_tile, int& cnt) {
+        int lo = 0, hi = p.E;
+        while (hi - lo > 1) {
+            int mid = (lo + hi) >> 1;
+            if (sm->tile_prefix[mid] <= tile) lo = mid; else hi = mid;
+        }
+        // experts with zero tiles repeat the prefix value; the search lands on the last
+        // expert whose prefix is <= tile, which is the one that owns tiles.
+        e = lo;
+        cnt = p.offsets[e + 1] - p.offsets[e];
+        int mt = (cnt + BM - 1) / BM;
+        int local = tile - sm->tile_prefix[e];
+        n_tile = local / mt;
+        m_tile = local - n_tile * mt;
+    };
+
+    if (warp == 8) {
+        // ===================== TMA producer =====================
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                int e, m_tile, n_tile, cnt;
+                locate(tile, e, m_tile, n_tile, cnt);
+                const int row0 = p.offsets[e] + m_tile * BM;
+                const long long wrow0 = (long long)e * w_rows;
+                for (int kb = 0; kb < nkb; kb++) {
+                    if (!ptx::mbar_wait(&sm->empty[s], ph ^ 1, abort_flag)) goto done;
+                    uint8_t* a_dst = tiles + (size_t)s * STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + A_BYTES;
+                    ptx::mbar_expect_tx(&sm->full[s], STAGE_BYTES);
+                    ptx::tma_load_2d(a_dst, &tmap_a, &sm->full[s], kb * BK, row0);
+                    if (MODE == 1) {
+                        // accumulator columns: [gate j0..+63 | up j0..+63 | gate j0+64..+127 | up j0+64..+127]
+                        const int j0 = n_tile * 128;
+                        ptx::tma_load_2d(b_dst + 0 * 8192, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + j0));
+                        ptx::tma_load_2d(b_dst + 1 * 8192, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + p.I + j0));
+                        ptx::tma_load_2d(b_dst + 2 * 8192, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + j0 + 64));
+                        ptx::tma_load_2d(b_dst + 3 * 8192, &tmap_b, &sm->full[s], kb * BK,
+                                         (int)(wrow0 + p.I + j0 + 64));
+                    } else {
+                        ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + n_tile * 256));
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ===================== MMA issuer =====================
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc(0, 0, 0, 0, BM, BN);
+            int s = 0; uint32_t ph = 0;
+            int acc = 0; uint32_t acc_ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                for (int kb = 0; kb < nkb; kb++) {
+                    if (!ptx::mbar_wait(&sm->tmem_empty[acc], acc_ph ^ 1, abort_flag)) goto done;
+                    if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_BYTES;
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; k4++) {
+                        uint64_t ad = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
+                        uint64_t bd = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
+                        ptx::mma_f8(d_tmem, ad, bd, idesc, k4 > 0 ? 1u : 0u);
+                    }
+                    ptx::tc_commit(&sm->empty[s]);          // smem stage reusable once the MMAs have read it
+                    ptx::tc_commit(&sm->tmem_full[acc]);    // partial sums ready for promotion
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                    if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+                }
+            }
+        }
+    } else {
+        // ===================== promotion + epilogue (warps 0-7) =====================
+        const int wg = warp >> 2;                         // column half of the accumulator
+        const int row = (warp & 3) * 32 + lane;           // TMEM lane = tile row
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        int acc = 0; uint32_t acc_ph = 0;
+        int tile_par = 0; uint32_t amax_ph[2] = {0, 0};
+        const int nkb_w = Kdim / 128;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            int e, m_tile, n_tile, cnt;
+            locate(tile, e, m_tile, n_tile, cnt);
+            const long long grow = (long long)p.offsets[e] + m_tile * BM + row;   // sorted row
+            const bool row_ok = (m_tile * BM + row) < cnt;
+            const float* a_sc = p.a_scale + (grow < p.total_rows ? grow : 0) * nkb;
+            const float* w_sc0;
+            const float* w_sc1;
+            if (MODE == 1) {
+                const float* base = p.w_scale + (size_t)e * (2 * p.I / 128) * nkb_w;
+                w_sc0 = base + (size_t)n_tile * nkb_w;                     // gate rows' block
+                w_sc1 = base + (size_t)(p.I / 128 + n_tile) * nkb_w;       // up rows' block
+            } else {
+                const float* base = p.w_scale + (size_t)e * (p.D / 128) * nkb_w;
+                w_sc0 = base + (size_t)(n_tile * 2 + wg) * nkb_w;
+                w_sc1 = w_sc0;
+            }
+            float accv[128];
+#pragma unroll
+            for (int i = 0; i < 128; i++) accv[i] = 0.0f;
+
+            for (int kb = 0; kb < nkb; kb++) {
+                const float sa = row_ok ? a_sc[kb] : 0.0f;
+                const float s0 = sa * w_sc0[kb];
+                const float s1 = sa * w_sc1[kb];
+                if (!ptx::mbar_wait(&sm->tmem_full[acc], acc_ph, abort_flag)) goto done;
+                ptx::tc_fence_after();
+                const uint32_t t0 = tmem_base + lane_addr + acc * BN + wg * 128;
+#pragma unroll
+                for (int c4 = 0; c4 < 4; c4++) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(t0 + c4 * 32, r);
+                    ptx::tc_wait_ld();
+                    const float sc = (c4 < 2) ? s0 : s1;   // MODE 1: cols 0-63 gate, 64-127 up
+#pragma unroll
+                    for (int i = 0; i < 32; i++) accv[c4 * 32 + i] += __uint_as_float(r[i]) * sc;
+                }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(&sm->tmem_empty[acc]);
+                if (++acc == 2) { acc = 0; acc_ph ^= 1; }
+            }
+
+            if (MODE == 1) {
+                // SwiGLU on 64 activation columns, 1x128 requantisation shared with the other warpgroup
+                float amax = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 64; i++) {
+                    float g = accv[i], u = accv[64 + i];
+                    float a = __fdiv_rn(g, 1.0f + expf(-g)) * u;
+                    accv[i] = a;
+                    amax = fmaxf(amax, fabsf(a));
+                }
+                sm->amax[tile_par][wg][row] = amax;
+                ptx::mbar_arrive(&sm->amax_bar[tile_par]);
+                if (!ptx::mbar_wait(&sm->amax_bar[tile_par], amax_ph[tile_par], abort_flag)) goto done;
+                amax_ph[tile_par] ^= 1;
+                amax = fmaxf(amax, sm->amax[tile_par][wg ^ 1][row]);
+                const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+                if (row_ok) {
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        uint32_t wv = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; b++) {
+                            uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(accv[i * 4 + b], scale),
+                                                                         __NV_SATFINITE, __NV_E4M3);
+                            wv |= q << (8 * b);
+                        }
+                        packed[i] = wv;
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(p.act_q + grow * p.I + n_tile * 128 + wg * 64);
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    if (wg == 0) p.act_s[grow * (p.I / 128) + n_tile] = scale;
+                }
+                tile_par ^= 1;
+            } else {
+                if (row_ok) {
+                    const int tok = p.row_tok[grow];
+                    const float w = p.row_w[grow];
+                    float* dst = p.out + (size_t)tok * p.D + n_tile * 256 + wg * 128;
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        red_add_v4(dst + 4 * i, w * accv[4 * i], w * accv[4 * i + 1], w * accv[4 * i + 2],
+                                   w * accv[4 * i + 3]);
+                }
+            }
+        }
+    }
+done:
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 9) ptx::tmem_dealloc(tmem_base, 512);
+    if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
+}
+
+// Expert-sorted copy of the FP8 rows.  One block per sorted row.
+__global__ void __launch_bounds__(128)
+sort_rows_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, const int* __restrict__ row_pair,
+                     const int* __restrict__ offsets, const float* __restrict__ wts, int E, int K, int D,
+                     uint8_t* __restrict__ sq, float* __restrict__ ss, int* __restrict__ row_tok,
+                     float* __restrict__ row_w) {
+    const int r = blockIdx.x;
+    if (r >= offsets[E]) return;
+    const int pair = row_pair[r];
+    const int tok = pair / K;
+    const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)tok * D);
+    uint4* dst = reinterpret_cast<uint4*>(sq + (size_t)r * D);
+    for (int i = threadIdx.x; i < D / 16; i += blockDim.x) dst[i] = src[i];
+    const int nb = D / 128;
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) ss[(size_t)r * nb + i] = xs[(size_t)tok * nb + i];
+    if (threadIdx.x == 0) {
+        row_tok[r] = tok;
+        row_w[r] = wts[pair];
+    }
+}
+
+// Optional per-kernel timing: CUDA events recorded on the launch stream around the two grouped
+// GEMMs (used by the benchmark for the roofline line; off by default).
+bool g_prof_on = false;
+cudaEvent_t g_prof_ev[4] = {nullptr, nullptr, nullptr, nullptr};
+int g_prof_valid = 0;
+
+struct Fp8Scratch {
+    float* partials; int* ids; float* wts; int* counts; int* offsets; int* row_pair;
+    uint8_t* sq; float* ss; int* row_tok; float* row_w; uint8_t* act_q; float* act_s;
+};
+
+void carve_fp8(WsCarver& c, const b200_moe_fp8_config* cfg, bool with_route, Fp8Scratch& s) {
+    const size_t T = cfg->num_tokens, E = cfg->num_experts, K = cfg->top_k, D = cfg->hidden_dim,
+                 I = cfg->intermediate_dim;
+    const size_t TK = T * K;
+    s.partials = with_route ? c.take<float>((size_t)moe_gate_chunks((int)D, true) * T * E) : nullptr;
+    s.ids = c.take<int>(TK);
+    s.wts = c.take<float>(TK);
+    s.counts = c.take<int>(E);
+    s.offsets = c.take<int>(E + 1);
+    s.row_pair = c.take<int>(TK);
+    s.sq = c.take<uint8_t>(TK * D);
+    s.ss = c.take<float>(TK * (D / 128));
+    s.row_tok = c.take<int>(TK);
+    s.row_w = c.take<float>(TK);
+    s.act_q = c.take<uint8_t>(TK * I);
+    s.act_s = c.take<float>(TK * (I / 128));
+}
+
+int check_fp8_cfg(const b200_moe_fp8_config* cfg) {
+    if (!cfg) return B200_BAD_ARG;
+    if (cfg->num_tokens <= 0 || cfg->num_experts <= 0 || cfg->top_k <= 0) return B200_BAD_SHAPE;
+    if (cfg->hidden_dim <= 0 || cfg->intermediate_dim <= 0) return B200_BAD_SHAPE;
+    if (cfg->hidden_dim % 256 || cfg->intermediate_dim % 128) return B200_BAD_SHAPE;
+    if (cfg->num_experts > MAX_E) return B200_UNSUPPORTED;
+    if ((long long)cfg->num_experts * 2 * cfg->intermediate_dim > 0x7fffffffLL) return B200_UNSUPPORTED;
+    if ((long long)cfg->num_experts * cfg->hidden_dim > 0x7fffffffLL) return B200_UNSUPPORTED;
+    return B200_OK;
+}
+
+// permute + sort + GEMM1 (+ GEMM2) on given routing
+int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float* xs, const int* ids,
+                const float* wts, const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s,
+                float* out, const b200_moe_fp8_config* cfg, bool do_gemm2, cudaStream_t stream) {
+    const int T = cfg->num_tokens, E = cfg->num_experts, K = cfg->top_k, D = cfg->hidden_dim,
+              I = cfg->intermediate_dim;
+    const long long TK = (long long)T * K;
+    int st = launch_permute(ids, T, K, E, s.counts, s.offsets, s.row_pair, stream);
+    if (st) return st;
+    sort_rows_fp8_kernel<<<(unsigned)TK, 128, 0, stream>>>(xq, xs, s.row_pair, s.offsets, wts, E, K, D, s.sq, s.ss,
+                                                           s.row_tok, s.row_w);
+    b200_count_launch(1);
+    B200_CUDA_TRY(cudaGetLastError());
+
+    static bool attr_done = false;
+    if (!attr_done) {
+        B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)GEMM_SMEM_BYTES));
+        B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)GEMM_SMEM_BYTES));
+        attr_done = true;
+    }
+    CUtensorMap ta, tb;
+    GemmParams p{};
+    p.offsets = s.offsets; p.E = E; p.D = D; p.I = I; p.status = ws->d_status; p.total_rows = TK;
+
+    // GEMM1
+    st = b200_make_tmap_u8_sw128(&ta, s.sq, (unsigned long long)TK, D, 128);
+    if (st) return st;
+    st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, 64);
+    if (st) return st;
+    p.a_scale = s.ss; p.w_scale = w1s; p.act_q = s.act_q; p.act_s = s.act_s;
+    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[0], stream));
+    grouped_gemm_fp8_kernel<1><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[1], stream));
+    b200_count_launch(1);
+    B200_CUDA_TRY(cudaGetLastError());
+    if (!do_gemm2) return B200_OK;
+
+    // GEMM2
+    st = b200_make_tmap_u8_sw128(&ta, s.act_q, (unsigned long long)TK, I, 128);
+    if (st) return st;
+    st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D, I, 256);
+    if (st) return st;
+    p.a_scale = s.act_s; p.w_scale = w2s; p.row_tok = s.row_tok; p.row_w = s.row_w; p.out = out;
+    B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)T * D, stream));
+    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[2], stream));
+    grouped_gemm_fp8_kernel<2><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+    if (g_prof_on) { B200_CUDA_TRY(cudaEventRecord(g_prof_ev[3], stream)); g_prof_valid = 1; }
+    b200_count_launch(1);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200_moe_fp8_profile(int enable) {
+    if (enable && !g_prof_ev[0])
+        for (int i = 0; i < 4; i++) B200_CUDA_TRY(cudaEventCreate(&g_prof_ev[i]));
+    g_prof_on = enable != 0;
+    g_prof_valid = 0;
+    return B200_OK;
+}
+
+int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms) {
+    if (!gemm1_ms || !gemm2_ms) return B200_BAD_ARG;
+    if (!g_prof_valid) return B200_BAD_ARG;
+    B200_CUDA_TRY(cudaEventSynchronize(g_prof_ev[3]));
+    B200_CUDA_TRY(cudaEventElapsedTime(gemm1_ms, g_prof_ev[0], g_prof_ev[1]));
+    B200_CUDA_TRY(cudaEventElapsedTime(gemm2_ms, g_prof_ev[2], g_prof_ev[3]));
+    return B200_OK;
+}
+
+int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                         const float* expert_w, const uint8_t* w1q, const float* w1s, const uint8_t* w2q,
+                         const float* w2s, float* out, const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+    int st = check_fp8_cfg(cfg);
+    if (st) return st;
+    if (!xq || !xs || !expert_ids || !expert_w || !w1q || !w1s || !w2q || !w2s || !out) return B200_BAD_ARG;
+    if (!ws) ws = b200_default_ws();
+    if (!ws) return B200_CUDA_ERROR;
+    Fp8Scratch s;
+    WsCarver sz(nullptr);
+    carve_fp8(sz, cfg, false, s);
+    st = b200_ws_ensure(ws, sz.total());
+    if (st) return st;
+    WsCarver cv(ws->base);
+    carve_fp8(cv, cfg, false, s);
+    return run_experts(ws, s, xq, xs, expert_ids, expert_w, w1q, w1s, w2q, w2s, out, cfg, true, stream);
+}
+
+int b200_moe_fp8_forward(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w, const float* bias,
+                         const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s, float* out,
+                         const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+    int st = check_fp8_cfg(cfg);
+    if (st) return st;
+    if (!xq || !xs || !gate_w || !w1q || !w1s || !w2q || !w2s || !out) return B200_BAD_ARG;
+    const int T = cfg->num_tokens, E = cfg->num_experts, K = cfg->top_k, D = cfg->hidden_dim;
+    st = check_route_cfg(T, E, K, D, cfg->scoring, cfg->n_group, cfg->topk_group);
+    if (st) return st;
+    if (!ws) ws = b200_default_ws();
+    if (!ws) return B200_CUDA_ERROR;
+    Fp8Scratch s;
+    WsCarver sz(nullptr);
+    carve_fp8(sz, cfg, true, s);
+    st = b200_ws_ensure(ws, sz.total());
+    if (st) return st;
+    WsCarver cv(ws->base);
+    carve_fp8(cv, cfg, true, s);
+    const int nch = moe_gate_chunks(D, true);
+    st = launch_gate_logits(xq, xs, gate_w, s.partials, T, E, D, true, stream);
+    if (st) return st;
+    st = launch_route_select(s.partials, nch, bias, s.ids, s.wts, nullptr, nullptr, T, E, K, cfg->scoring,
+                             cfg->n_group, cfg->topk_group, cfg->routed_scale, stream);
+    if (st) return st;
+    return run_experts(ws, s, xq, xs, s.ids, s.wts, w1q, w1s, w2q, w2s, out, cfg, true, stream);
+}
+
+int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                             const uint8_t* w1q, const float* w1s, uint8_t* act_q, float* act_s, int* offsets,
+                             int* row_pair, const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+    int st = check_fp8_cfg(cfg);
+    if (st) return st;
+    if (!xq || !xs || !expert_ids || !w1q || !w1s || !act_q || !act_s || !offsets || !row_pair) return B200_BAD_ARG;
+    if (!ws) ws = b200_default_ws();
+    if (!ws) return B200_CUDA_ERROR;
+    Fp8Scratch s;
+    WsCarver sz(nullptr);
+    carve_fp8(sz, cfg, false, s);
+    float* dummy_w = sz.take<float>((size_t)cfg->num_tokens * cfg->top_k);
+    st = b200_ws_ensure(ws, sz.total());
+    if (st) return st;
+    WsCarver cv(ws->base);
+    carve_fp8(cv, cfg, false, s);
+    dummy_w = cv.take<float>((size_t)cfg->num_tokens * cfg->top_k);
+    const size_t TK = (size_t)cfg->num_tokens * cfg->top_k;
+    B200_CUDA_TRY(cudaMemsetAsync(dummy_w, 0, sizeof(float) * TK, stream));
+    B200_CUDA_TRY(cudaMemsetAsync(s.act_q, 0, TK * cfg->intermediate_dim, stream));
+    B200_CUDA_TRY(cudaMemsetAsync(s.act_s, 0, sizeof(float) * TK * (cfg->intermediate_dim / 128), stream));
+    st = run_experts(ws, s, xq, xs, expert_ids, dummy_w, w1q, w1s, nullptr, nullptr, nullptr, cfg, false, stream);
+    if (st) return st;
+    B200_CUDA_TRY(cudaMemcpyAsync(act_q, s.act_q, TK * cfg->intermediate_dim, cudaMemcpyDeviceToDevice, stream));
+    B200_CUDA_TRY(cudaMemcpyAsync(act_s, s.act_s, sizeof(float) * TK * (cfg->intermediate_dim / 128),
+                                  cudaMemcpyDeviceToDevice, stream));
+    B200_CUDA_TRY(cudaMemcpyAsync(offsets, s.offsets, sizeof(int) * (cfg->num_experts + 1),
+                                  cudaMemcpyDeviceToDevice, stream));
+    B200_CUDA_TRY(cudaMemcpyAsync(row_pair, s.row_pair, sizeof(int) * TK, cudaMemcpyDeviceToDevice, stream));
+    return B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,102 @@
+"""Layer objects a serving loop would hold: weights / caches stay resident in HBM, one
+``forward_host`` call moves a step's inputs from pinned host memory, runs the CUDA path and
+brings the result back (the end-to-end path the benchmark times)."""
+import torch
+
+from . import (DsaConfig, MoeFp8Config, SCORE_SIGMOID_GROUPED, dsa_forward_bf16, moe_fp8_experts,
+               moe_fp8_forward, moe_route_fp8)
+
+
+class MoeFp8Layer:
+    """FP8 block-scale MoE layer (extends moe_forward, kernels/moe/naive_moe.cu:400-471)."""
+
+    def __init__(self, gate_w, bias, w1q, w1s, w2q, w2s, top_k, scoring=SCORE_SIGMOID_GROUPED, n_group=8,
+                 topk_group=4, routed_scale=2.5):
+        self.gate_w, self.bias = gate_w, bias
+        self.w1q, self.w1s, self.w2q, self.w2s = w1q, w1s, w2q, w2s
+        self.E, self.D = gate_w.shape
+        self.I = w2q.shape[-1]
+        self.K = top_k
+        self.scoring, self.n_group, self.topk_group, self.routed_scale = scoring, n_group, topk_group, routed_scale
+        self._dev = {}
+
+    def cfg(self, T, E=None, K=None):
+        return MoeFp8Config(T, self.E if E is None else E, self.K if K is None else K, self.D, self.I, self.scoring,
+                            self.n_group, self.topk_group, self.routed_scale)
+
+    def forward(self, xq, xs, out=None):
+        T = xq.shape[0]
+        if out is None:
+            out = torch.empty((T, self.D), dtype=torch.float32, device=xq.device)
+        moe_fp8_forward(xq, xs, self.gate_w, self.bias, self.w1q, self.w1s, self.w2q, self.w2s, out, self.cfg(T))
+        return out
+
+    def route(self, xq, xs):
+        T = xq.shape[0]
+        ids = torch.empty((T, self.K), dtype=torch.int32, device=xq.device)
+        wts = torch.empty((T, self.K), dtype=torch.float32, device=xq.device)
+        moe_route_fp8(xq, xs, self.gate_w, self.bias, ids, wts, self.cfg(T))
+        return ids, wts
+
+    def local_experts(self, rq, rs, re, rw):
+        """Expert FFN for rows already dispatched to this rank: row r goes through local expert
+        re[r] and is scaled by rw[r] (one slot per row)."""
+        R = rq.shape[0]
+        y = torch.empty((R, self.D), dtype=torch.float32, device=rq.device)
+        E_local = self.w1q.shape[0]
+        moe_fp8_experts(rq, rs, re.reshape(R, 1), rw.reshape(R, 1), self.w1q, self.w1s, self.w2q, self.w2s, y,
+                        self.cfg(R, E=E_local, K=1))
+        return y
+
+    def forward_host(self, xq_host, xs_host, out_host):
+        """xq_host/xs_host/out_host: pinned host tensors.  Returns after the result is on the host."""
+        T = xq_host.shape[0]
+        key = ("moe", T)
+        if key not in self._dev:
+            dev = self.gate_w.device
+            self._dev[key] = (torch.empty(xq_host.shape, dtype=torch.uint8, device=dev),
+                              torch.empty(xs_host.shape, dtype=torch.float32, device=dev),
+                              torch.empty((T, self.D), dtype=torch.float32, device=dev))
+        dq, ds, do = self._dev[key]
+        dq.copy_(xq_host, non_blocking=True)
+        ds.copy_(xs_host, non_blocking=True)
+        self.forward(dq, ds, do)
+        out_host.copy_(do, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out_host
+
+
+class DsaDecodeLayer:
+    """bf16 sparse MLA decode (dsa_forward, kernels/dsa/naive_dsa.cu:435-474) over caches resident in HBM."""
+
+    def __init__(self, kc, kp, v, page_size=64):
+        self.kc, self.kp, self.v = kc, kp, v
+        self.page_size = page_size
+        self._dev = {}
+
+    def cfg(self, Q, H, S):
+        return DsaConfig(Q, H, self.kc.shape[1], self.kp.shape[1], S, self.page_size, self.kc.shape[0])
+
+    def forward(self, q_nope, q_pe, idx, out=None):
+        Q, H, _ = q_nope.shape
+        if out is None:
+            out = torch.empty((Q, H, self.kc.shape[1]), dtype=torch.float32, device=q_nope.device)
+        dsa_forward_bf16(q_nope, q_pe, self.kc, self.kp, self.v, idx, out, self.cfg(Q, H, idx.shape[1]))
+        return out
+
+    def forward_host(self, qn_host, qp_host, idx_host, out_host):
+        key = tuple(qn_host.shape) + tuple(idx_host.shape)
+        if key not in self._dev:
+            dev = self.kc.device
+            self._dev[key] = (torch.empty(qn_host.shape, dtype=torch.bfloat16, device=dev),
+                              torch.empty(qp_host.shape, dtype=torch.bfloat16, device=dev),
+                              torch.empty(idx_host.shape, dtype=torch.int32, device=dev),
+                              torch.empty(out_host.shape, dtype=torch.float32, device=dev))
+        dn, dp, di, do = self._dev[key]
+        dn.copy_(qn_host, non_blocking=True)
+        dp.copy_(qp_host, non_blocking=True)
+        di.copy_(idx_host, non_blocking=True)
+        self.forward(dn, dp, di, do)
+        out_host.copy_(do, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out_host

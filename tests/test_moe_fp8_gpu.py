@@ -1,0 +1,165 @@
+"""GPU parity of the FP8 block-scale MoE path through the C ABI: quantisers and the synthetic
+weight generator bit-exact against the oracle, grouped sigmoid routing bit-exact (ids, offsets,
+permutation), GEMM1+SwiGLU+requantise stage, and the whole layer against the fp32 CPU emulation
+of the same dequantise-GEMM-requantise sequence (2e-2 relative + 1e-2 absolute)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+RTOL, ATOL = 2e-2, 1e-2
+
+
+def _dev(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def _layer(rng, T, E, D, I, sigma_w=0.05):
+    x = rng.normal(0, 1, (T, D)).astype(np.float32)
+    wg = rng.normal(0, D ** -0.5, (E, D)).astype(np.float32)
+    bias = rng.normal(0, 0.01, E).astype(np.float32)
+    w1 = rng.normal(0, sigma_w, (E, 2 * I, D)).astype(np.float32)
+    w2 = rng.normal(0, sigma_w, (E, D, I)).astype(np.float32)
+    xq, xs = oracle.quant_act(x)
+    w1q, w1s = oracle.quant_weight(w1)
+    w2q, w2s = oracle.quant_weight(w2)
+    return x, wg, bias, w1, w2, xq, xs, w1q, w1s, w2q, w2s
+
+
+def test_quantisers_bit_exact(b200, cuda):
+    rng = np.random.default_rng(0)
+    x = rng.normal(0, 1, (37, 512)).astype(np.float32)
+    x[5, 128:256] = 0
+    q = torch.empty((37, 512), dtype=torch.uint8, device=cuda)
+    s = torch.empty((37, 4), dtype=torch.float32, device=cuda)
+    b200.quant_act_1x128(_dev(x, cuda), q, s)
+    oq, os_ = oracle.quant_act(x)
+    assert np.array_equal(q.cpu().numpy(), oq) and np.array_equal(s.cpu().numpy(), os_)
+    w = rng.normal(0, 0.02, (3, 256, 384)).astype(np.float32)
+    wq = torch.empty(w.shape, dtype=torch.uint8, device=cuda)
+    ws = torch.empty((3, 2, 3), dtype=torch.float32, device=cuda)
+    b200.quant_weight_128x128(_dev(w, cuda), wq, ws)
+    oq, os_ = oracle.quant_weight(w)
+    assert np.array_equal(wq.cpu().numpy(), oq) and np.array_equal(ws.cpu().numpy(), os_)
+
+
+def test_synthetic_fp8_weights_match_host_twin(b200, cuda):
+    rows, cols = 256, 384
+    q = torch.empty((rows, cols), dtype=torch.uint8, device=cuda)
+    s = torch.empty((rows // 128, cols // 128), dtype=torch.float32, device=cuda)
+    b200.fill_normal_fp8_w128_(q, s, 99, 0.02)
+    w = b200.synth_normal_host(99, 0, rows * cols, 0.02).reshape(rows, cols)
+    oq, os_ = oracle.quant_weight(w)
+    assert np.array_equal(q.cpu().numpy(), oq) and np.array_equal(s.cpu().numpy(), os_)
+    t = torch.empty(1000, dtype=torch.bfloat16, device=cuda)
+    b200.fill_normal_(t, 5, 0.5)
+    ref = oracle.bf16_bits(b200.synth_normal_host(5, 0, 1000, 0.5))
+    assert np.array_equal(t.view(torch.int16).cpu().numpy().view(np.uint16), ref)
+
+
+@pytest.mark.parametrize("T,E,K,D,ng,tg", [(64, 32, 4, 512, 4, 2), (200, 256, 8, 1024, 8, 4), (5, 16, 2, 2304, 1, 1)])
+def test_grouped_routing_bit_exact(b200, cuda, T, E, K, D, ng, tg):
+    rng = np.random.default_rng(T)
+    x = rng.normal(0, 1, (T, D)).astype(np.float32)
+    wg = rng.normal(0, D ** -0.5, (E, D)).astype(np.float32)
+    bias = rng.normal(0, 0.01, E).astype(np.float32)
+    xq, xs = oracle.quant_act(x)
+    cfg = b200.MoeFp8Config(T, E, K, D, 128, b200.SCORE_SIGMOID_GROUPED, ng, tg, 2.5)
+    ids = torch.empty((T, K), dtype=torch.int32, device=cuda)
+    wts = torch.empty((T, K), dtype=torch.float32, device=cuda)
+    counts = torch.empty(E, dtype=torch.int32, device=cuda)
+    logits = torch.empty((T, E), dtype=torch.float32, device=cuda)
+    b200.moe_route_fp8(_dev(xq, cuda), _dev(xs, cuda), _dev(wg, cuda), _dev(bias, cuda), ids, wts, cfg,
+                       counts=counts, logits_out=logits)
+    ol = oracle.gate_logits_fp8(xq, xs, wg)
+    assert np.array_equal(logits.cpu().numpy(), ol)            # fixed accumulation order -> identical bits
+    oi, ow = oracle.route_grouped(xq, xs, wg, bias, K, ng, tg, 2.5)
+    assert np.array_equal(ids.cpu().numpy(), oi)
+    assert np.abs(wts.cpu().numpy() - ow).max() <= 5e-7
+    assert np.array_equal(counts.cpu().numpy(), np.bincount(oi.reshape(-1), minlength=E))
+    # permutation offsets bit-exact
+    c = torch.empty(E, dtype=torch.int32, device=cuda); o = torch.empty(E + 1, dtype=torch.int32, device=cuda)
+    rp = torch.empty(T * K, dtype=torch.int32, device=cuda)
+    b200.moe_permute(ids, T, K, E, c, o, rp)
+    oc, oo, orp = oracle.permute(oi, E)
+    assert np.array_equal(o.cpu().numpy(), oo) and np.array_equal(rp.cpu().numpy(), orp)
+
+
+def test_gemm1_swiglu_requant_stage(b200, cuda):
+    rng = np.random.default_rng(1)
+    T, E, K, D, I = 40, 4, 2, 512, 256
+    x, wg, bias, w1, w2, xq, xs, w1q, w1s, w2q, w2s = _layer(rng, T, E, D, I)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.int32)
+    cfg = b200.MoeFp8Config(T, E, K, D, I, b200.SCORE_SIGMOID_GROUPED, 1, 1, 1.0)
+    act_q = torch.empty((T * K, I), dtype=torch.uint8, device=cuda)
+    act_s = torch.empty((T * K, I // 128), dtype=torch.float32, device=cuda)
+    offs = torch.empty(E + 1, dtype=torch.int32, device=cuda)
+    rp = torch.empty(T * K, dtype=torch.int32, device=cuda)
+    b200.moe_fp8_gemm1_stage(_dev(xq, cuda), _dev(xs, cuda), _dev(ids, cuda), _dev(w1q, cuda), _dev(w1s, cuda),
+                             act_q, act_s, offs, rp, cfg)
+    torch.cuda.synchronize()
+    assert b200.device_status() == 0
+    aq, asc, rp = act_q.cpu().numpy(), act_s.cpu().numpy(), rp.cpu().numpy()
+    bad = 0
+    for r in range(0, T * K, 3):
+        t, k = divmod(int(rp[r]), K)
+        oq, osc = oracle.moe_fp8_gemm1_row(xq[t], xs[t], w1q[ids[t, k]], w1s[ids[t, k]])
+        assert np.allclose(asc[r], osc, rtol=1e-4), (r, asc[r], osc)
+        got = oracle.e4m3_decode(aq[r]) * np.repeat(asc[r], 128)
+        ref = oracle.e4m3_decode(oq) * np.repeat(osc, 128)
+        # identical up to isolated one-step flips of an e4m3 code at rounding boundaries
+        step = np.maximum(np.abs(ref), np.repeat(osc, 128) * 2.0 ** -6) * 2.0 ** -3
+        assert np.all(np.abs(got - ref) <= step * 1.01)
+        bad += int((aq[r] != oq).sum())
+    assert bad <= 0.02 * (T * K // 3 + 1) * I, bad
+
+
+@pytest.mark.parametrize("T,E,K,D,I,ng,tg", [(48, 8, 2, 256, 128, 4, 2), (300, 16, 4, 512, 384, 4, 2),
+                                              (1, 8, 2, 256, 128, 4, 2), (130, 4, 4, 768, 256, 1, 1)])
+def test_fp8_layer_against_emulation(b200, cuda, T, E, K, D, I, ng, tg):
+    rng = np.random.default_rng(T + E)
+    x, wg, bias, w1, w2, xq, xs, w1q, w1s, w2q, w2s = _layer(rng, T, E, D, I)
+    cfg = b200.MoeFp8Config(T, E, K, D, I, b200.SCORE_SIGMOID_GROUPED, ng, tg, 2.5)
+    out = torch.full((T, D), float("nan"), dtype=torch.float32, device=cuda)
+    b200.moe_fp8_forward(_dev(xq, cuda), _dev(xs, cuda), _dev(wg, cuda), _dev(bias, cuda), _dev(w1q, cuda),
+                         _dev(w1s, cuda), _dev(w2q, cuda), _dev(w2s, cuda), out, cfg)
+    torch.cuda.synchronize()
+    assert b200.device_status() == 0
+    ids, wts = oracle.route_grouped(xq, xs, wg, bias, K, ng, tg, 2.5)
+    ref = oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, ids, wts, np.arange(T, dtype=np.int32))
+    got = out.cpu().numpy()
+    viol = np.abs(got - ref) > ATOL + RTOL * np.abs(ref)
+    assert not viol.any(), (int(viol.sum()), float(np.abs(got - ref).max()))
+    # linearity in the router weights (a size-independent property): doubling routed_scale doubles the output
+    cfg2 = b200.MoeFp8Config(T, E, K, D, I, b200.SCORE_SIGMOID_GROUPED, ng, tg, 5.0)
+    out2 = torch.empty_like(out)
+    b200.moe_fp8_forward(_dev(xq, cuda), _dev(xs, cuda), _dev(wg, cuda), _dev(bias, cuda), _dev(w1q, cuda),
+                         _dev(w1s, cuda), _dev(w2q, cuda), _dev(w2s, cuda), out2, cfg2)
+    assert np.allclose(out2.cpu().numpy(), 2 * got, rtol=1e-4, atol=1e-5)
+
+
+def test_fp8_experts_skips_foreign_ids(b200, cuda):
+    """Expert-parallel building block: ids outside [0,E) (experts owned by other ranks) are skipped."""
+    rng = np.random.default_rng(3)
+    T, E, K, D, I = 20, 4, 2, 256, 128
+    x, wg, bias, w1, w2, xq, xs, w1q, w1s, w2q, w2s = _layer(rng, T, E, D, I)
+    ids = np.stack([rng.permutation(E + 2)[:K] for _ in range(T)]).astype(np.int32)
+    ids[ids >= E] = -1
+    wts = rng.uniform(0.1, 1, (T, K)).astype(np.float32)
+    cfg = b200.MoeFp8Config(T, E, K, D, I, b200.SCORE_SIGMOID_GROUPED, 1, 1, 1.0)
+    out = torch.empty((T, D), dtype=torch.float32, device=cuda)
+    b200.moe_fp8_experts(_dev(xq, cuda), _dev(xs, cuda), _dev(ids, cuda), _dev(wts, cuda), _dev(w1q, cuda),
+                         _dev(w1s, cuda), _dev(w2q, cuda), _dev(w2s, cuda), out, cfg)
+    ref = oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, ids, wts, np.arange(T, dtype=np.int32))
+    got = out.cpu().numpy()
+    assert not (np.abs(got - ref) > ATOL + RTOL * np.abs(ref)).any()
+
+
+def test_fp8_bad_shapes(b200, cuda):
+    t = torch.zeros(16, dtype=torch.uint8, device=cuda)
+    f = torch.zeros(16, dtype=torch.float32, device=cuda)
+    with pytest.raises(b200.B200Error) as ei:
+        b200.moe_fp8_forward(t, f, f, f, t, f, t, f, f, b200.MoeFp8Config(4, 4, 2, 200, 128, 1, 1, 1, 1.0))
+    assert ei.value.status == b200.B200_BAD_SHAPE
