@@ -1,0 +1,544 @@
+#!/usr/bin/env python
+"""Benchmark of the two hot paths on B200.
+
+Headline (the JSON line's `metric`/`value`): FP8 block-scale MoE layer throughput in tokens/s
+at T = 4096 tokens per GPU (DeepSeek-V3 shape: D=7168, I=2048, E=256, top-8, 8 groups / top-4,
+sigmoid + bias scoring, routed scaling 2.5).  One GPU runs the whole layer (config "C3"); N > 1
+GPUs shard the experts (E/N per GPU), keep 4096 tokens per GPU and exchange rows with NCCL
+all-to-all (config "C5", Zipf(1.1)-skewed expert load) — weak scaling.
+The same line carries, under "dsa", the sparse MLA decode step time at B=64, H=128, Dc=512,
+Dp=64, top-2048 over a paged bf16 cache with 8192..131072 tokens per sequence (config "C4");
+it shards by batch, so with N > 1 every GPU runs an independent replica.
+
+All inputs are synthetic (seeded counter-based generator, DeepSeek shapes and the value
+distributions the configs name); weights are random-initialised.
+
+    python bench.py --gpus 1 --steps 20 --warmup 3
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference        # CPU arm: the oracle port on the host cores
+"""
+import argparse
+import importlib.util
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+MOE = dict(T=4096, E=256, K=8, D=7168, I=2048, n_group=8, topk_group=4, routed_scale=2.5)
+DSA = dict(B=64, H=128, Dc=512, Dp=64, S=2048, page=64, seq_min=8192, seq_max=131072)
+ZIPF_S, ZIPF_BETA = 1.1, 0.08
+RTOL, ATOL = 2e-2, 1e-2
+
+
+def load_package():
+    name = "llm_sys_project_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    pkg = os.path.join(ROOT, "llm-sys-project_b200")
+    spec = importlib.util.spec_from_file_location(name, os.path.join(pkg, "__init__.py"),
+                                                  submodule_search_locations=[pkg])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Polls NVML (read-only) for SM clock and throttle reasons while a timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "sw_thermal_slowdown": 0x20,
+                 "hw_thermal_slowdown": 0x40, "hw_power_brake": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def start(self):
+        if self.nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------
+def zipf_bias(E, seed):
+    rng = np.random.default_rng(seed)
+    rank_of = rng.permutation(E) + 1
+    logp = -ZIPF_S * np.log(rank_of.astype(np.float64))
+    return (ZIPF_BETA * (logp - logp.mean())).astype(np.float32)
+
+
+def build_moe(b200, torch, dev, world, rank):
+    """Weights of this rank's experts, the replicated router, and this rank's tokens."""
+    c = MOE
+    E_local = c["E"] // world
+    w1q = torch.empty((E_local, 2 * c["I"], c["D"]), dtype=torch.uint8, device=dev)
+    w1s = torch.empty((E_local, 2 * c["I"] // 128, c["D"] // 128), dtype=torch.float32, device=dev)
+    w2q = torch.empty((E_local, c["D"], c["I"]), dtype=torch.uint8, device=dev)
+    w2s = torch.empty((E_local, c["D"] // 128, c["I"] // 128), dtype=torch.float32, device=dev)
+    b200.fill_normal_fp8_w128_(w1q, w1s, 1000 + rank, 0.02)
+    b200.fill_normal_fp8_w128_(w2q, w2s, 2000 + rank, 0.02)
+    gate_w = torch.empty((c["E"], c["D"]), dtype=torch.float32, device=dev)
+    b200.fill_normal_(gate_w, 3000, c["D"] ** -0.5)
+    bias_h = b200.synth_normal_host(3001, 0, c["E"], 0.01)
+    if world > 1:
+        bias_h = bias_h + zipf_bias(c["E"], 7)
+    bias = torch.from_numpy(bias_h).to(dev)
+    x = torch.empty((c["T"], c["D"]), dtype=torch.float32, device=dev)
+    b200.fill_normal_(x, 4000 + rank, 1.0)
+    xq = torch.empty((c["T"], c["D"]), dtype=torch.uint8, device=dev)
+    xs = torch.empty((c["T"], c["D"] // 128), dtype=torch.float32, device=dev)
+    b200.quant_act_1x128(x, xq, xs)
+    del x
+    layer = b200.MoeFp8Layer(gate_w, bias, w1q, w1s, w2q, w2s, c["K"], b200.SCORE_SIGMOID_GROUPED, c["n_group"],
+                             c["topk_group"], c["routed_scale"])
+    return layer, xq, xs
+
+
+def moe_gemm1_bytes(counts):
+    """Algorithmic HBM bytes of one GEMM1 launch: FP8 weights + block scales of the active experts,
+    the sorted FP8 rows + 1x128 scales read, the requantised activations + scales written."""
+    c = MOE
+    active = int((counts > 0).sum())
+    rows = int(counts.sum())
+    w = active * (2 * c["I"] * c["D"] + 4 * (2 * c["I"] // 128) * (c["D"] // 128))
+    a = rows * (c["D"] + 4 * c["D"] // 128)
+    o = rows * (c["I"] + 4 * c["I"] // 128)
+    return w + a + o, active, rows
+
+
+def moe_layer_bytes(counts):
+    """Algorithmic bytes of the whole layer (weights once, x once, router weights, output)."""
+    c = MOE
+    active = int((counts > 0).sum())
+    w = active * (3 * c["D"] * c["I"] + 4 * ((2 * c["I"] // 128) * (c["D"] // 128) + (c["D"] // 128) * (c["I"] // 128)))
+    return w + c["T"] * (c["D"] + 4 * c["D"] // 128) + 4 * c["E"] * c["D"] + c["T"] * c["D"] * 4
+
+
+def moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out_dev, n_tokens, threads):
+    """Oracle (CPU emulation of the same FP8 sequence) on a seeded sample of tokens: parity of the
+    GPU output rows and the CPU throughput.  Only the experts the sample uses are copied to the host."""
+    c = MOE
+    rng = np.random.default_rng(5)
+    toks = np.sort(rng.choice(c["T"], n_tokens, replace=False)).astype(np.int32)
+    xq_h = xq.index_select(0, torch.from_numpy(toks).to(xq.device).long()).cpu().numpy()
+    xs_h = xs.index_select(0, torch.from_numpy(toks).to(xq.device).long()).cpu().numpy()
+    wg_h, bias_h = layer.gate_w.cpu().numpy(), layer.bias.cpu().numpy()
+    oracle.set_threads(threads)
+    t0 = time.perf_counter()
+    ids, wts = oracle.route_grouped(xq_h, xs_h, wg_h, bias_h, c["K"], c["n_group"], c["topk_group"], c["routed_scale"])
+    t_route = time.perf_counter() - t0
+    uniq = np.unique(ids)
+    remap = -np.ones(c["E"], np.int32)
+    remap[uniq] = np.arange(len(uniq), dtype=np.int32)
+    sel = torch.from_numpy(uniq.astype(np.int64)).to(xq.device)
+    w1q = layer.w1q.index_select(0, sel).cpu().numpy()
+    w1s = layer.w1s.index_select(0, sel).cpu().numpy()
+    w2q = layer.w2q.index_select(0, sel).cpu().numpy()
+    w2s = layer.w2s.index_select(0, sel).cpu().numpy()
+    t0 = time.perf_counter()
+    ref = oracle.moe_fp8_experts(xq_h, xs_h, w1q, w1s, w2q, w2s, remap[ids], wts,
+                                 np.arange(n_tokens, dtype=np.int32))
+    t_ffn = time.perf_counter() - t0
+    got = out_dev.index_select(0, torch.from_numpy(toks).to(xq.device).long()).cpu().numpy()
+    gids = None
+    err = np.abs(got - ref)
+    ok = bool(not (err > ATOL + RTOL * np.abs(ref)).any())
+    return {"tokens": int(n_tokens), "seconds": t_route + t_ffn, "ok": ok, "max_abs_err": float(err.max()),
+            "ref_absmax": float(np.abs(ref).max()), "ids": ids, "toks": toks, "gids": gids}
+
+
+def bench_moe_single(b200, torch, oracle, dev, args, sampler):
+    c = MOE
+    layer, xq, xs = build_moe(b200, torch, dev, 1, 0)
+    out = torch.empty((c["T"], c["D"]), dtype=torch.float32, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        layer.forward(xq, xs, out)
+    torch.cuda.synchronize()
+    assert b200.device_status() == 0, "device-side wait timed out"
+    ids, wts = layer.route(xq, xs)
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=c["E"]).cpu().numpy()
+
+    b200.moe_fp8_profile(True)
+    b200.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        layer.forward(xq, xs, out)
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.stop()
+    launches = b200.launch_count()
+    ms = e0.elapsed_time(e1) / args.steps
+    g1_ms, g2_ms, ncalls = b200.moe_fp8_profile_read()
+    b200.moe_fp8_profile(False)
+
+    # end to end through the host-facing layer call: pinned host in, pinned host out
+    xq_h, xs_h = xq.cpu().pin_memory(), xs.cpu().pin_memory()
+    out_h = torch.empty((c["T"], c["D"]), dtype=torch.float32).pin_memory()
+    for _ in range(2):
+        layer.forward_host(xq_h, xs_h, out_h)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        layer.forward_host(xq_h, xs_h, out_h)
+    e2e_s = (time.perf_counter() - t0) / args.steps
+
+    threads = oracle.max_threads()
+    cpu = moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out, args.cpu_tokens, threads)
+    hbm, bf16_tf, which = measured_peaks()
+    g1_bytes, active, rows = moe_gemm1_bytes(counts)
+    flops = 6.0 * rows * c["D"] * c["I"] + 2.0 * c["T"] * c["E"] * c["D"]
+    res = {
+        "value": c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),
+        "e2e": {"value": c["T"] / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(xq_h.numel() + xs_h.numel() * 4),
+                "d2h_bytes_per_step": int(out_h.numel() * 4), "ms_per_step": e2e_s * 1e3},
+        "roofline": {"kernel": "grouped_gemm_fp8<1> (GEMM1+SwiGLU+requant)", "bound": "hbm",
+                     "achieved": g1_bytes / (g1_ms * 1e-3) / 1e9 if g1_ms > 0 else None, "peak": hbm, "unit": "GB/s",
+                     "frac": (g1_bytes / (g1_ms * 1e-3) / 1e9 / hbm) if g1_ms > 0 else None, "traffic": None,
+                     "peak_source": which, "kernel_ms": g1_ms, "algorithmic_bytes": int(g1_bytes),
+                     "launches_timed": ncalls},
+        "kernels": {"gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "other_ms": ms - g1_ms - g2_ms,
+                    "layer_bytes": int(moe_layer_bytes(counts)),
+                    "layer_hbm_gbs": moe_layer_bytes(counts) / (ms * 1e-3) / 1e9,
+                    "layer_tflops": flops / (ms * 1e-3) / 1e12,
+                    "gemm_tflops": 6.0 * rows * c["D"] * c["I"] / ((g1_ms + g2_ms) * 1e-3) / 1e12 if g1_ms > 0 else None,
+                    "fp8_peak_tflops_nominal": 4500.0, "active_experts": active,
+                    "max_tokens_per_expert": int(counts.max()), "mean_tokens_per_expert": float(counts.mean())},
+        "cpu_baseline": {"value": cpu["tokens"] / cpu["seconds"], "unit": "tokens/s", "cores": threads, "kind": "port",
+                         "sample": f"{cpu['tokens']} seeded tokens of the same workload (routing + 8 experts each) "
+                                   f"through the fp32 CPU emulation, {cpu['seconds']:.2f} s"},
+        "parity": {"checked_tokens": cpu["tokens"], "ok": cpu["ok"], "max_abs_err": cpu["max_abs_err"],
+                   "ref_absmax": cpu["ref_absmax"], "tolerance": f"{RTOL} rel + {ATOL} abs"},
+    }
+    del layer, xq, xs, out
+    torch.cuda.empty_cache()
+    return res
+
+
+def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
+    c = MOE
+    layer, xq, xs = build_moe(b200, torch, dev, world, rank)
+    ep = b200.ExpertParallelMoe(dist.group.WORLD, c["E"], c["K"], layer.route, layer.local_experts,
+                                combine_dtype=torch.bfloat16)
+    for _ in range(max(args.warmup, 3)):
+        out, ids, _ = ep.forward(xq, xs)
+    torch.cuda.synchronize()
+    assert b200.device_status() == 0, "device-side wait timed out"
+    recv_rows = ep.last_stats["recv_rows"]
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=c["E"])
+    dist.all_reduce(counts)
+    counts = counts.cpu().numpy()
+    b200.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        ep.forward(xq, xs)
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    sampler.stop()
+    launches = b200.launch_count()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    rr = torch.tensor([recv_rows], device=dev, dtype=torch.float32)
+    rmax = rr.clone(); dist.all_reduce(rmax, op=dist.ReduceOp.MAX)
+    rsum = rr.clone(); dist.all_reduce(rsum)
+    per_gpu = counts.reshape(world, -1).sum(1)
+    flops_hot = 6.0 * float(rmax.item()) * c["D"] * c["I"]
+    res = {
+        "value": world * c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),
+        "kernels": {"rows_per_gpu_max": float(rmax.item()), "rows_per_gpu_mean": float(rsum.item()) / world,
+                    "max_tokens_per_expert": int(counts.max()), "mean_tokens_per_expert": float(counts.mean()),
+                    "rows_by_gpu": [int(v) for v in per_gpu],
+                    "hot_gpu_gemm_tflops_lower_bound": flops_hot / (ms * 1e-3) / 1e12,
+                    "fp8_peak_tflops_nominal": 4500.0},
+    }
+    return res
+
+
+def build_dsa(b200, torch, dev, seed):
+    c = DSA
+    rng = np.random.default_rng(seed)
+    seq = rng.integers(c["seq_min"], c["seq_max"] + 1, c["B"])
+    pages_per_seq = (seq + c["page"] - 1) // c["page"]
+    total_pages = int(pages_per_seq.sum())
+    N = total_pages * c["page"]
+    kc = torch.empty((N, c["Dc"]), dtype=torch.bfloat16, device=dev)
+    kp = torch.empty((N, c["Dp"]), dtype=torch.bfloat16, device=dev)
+    v = torch.empty((N, c["Dc"]), dtype=torch.bfloat16, device=dev)
+    b200.fill_normal_(kc, seed + 1, 0.5)
+    b200.fill_normal_(kp, seed + 2, 0.5)
+    b200.fill_normal_(v, seed + 3, 0.5)
+    qn = torch.empty((c["B"], c["H"], c["Dc"]), dtype=torch.bfloat16, device=dev)
+    qp = torch.empty((c["B"], c["H"], c["Dp"]), dtype=torch.bfloat16, device=dev)
+    b200.fill_normal_(qn, seed + 4, 1.0)
+    b200.fill_normal_(qp, seed + 5, 1.0)
+    # block table: physical pages handed out by a random permutation
+    page_perm = torch.from_numpy(rng.permutation(total_pages)).to(dev)
+    starts = np.concatenate([[0], np.cumsum(pages_per_seq)[:-1]])
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    idx_sets = []
+    for _ in range(4):
+        idx = torch.empty((c["B"], c["S"]), dtype=torch.int32, device=dev)
+        for b in range(c["B"]):
+            pos = torch.randperm(int(seq[b]), generator=g, device=dev)[: c["S"]]      # distinct, unsorted
+            phys = page_perm[int(starts[b]) + pos // c["page"]] * c["page"] + pos % c["page"]
+            idx[b] = phys.to(torch.int32)
+        idx_sets.append(idx)
+    layer = b200.DsaDecodeLayer(kc, kp, v, c["page"])
+    return layer, qn, qp, idx_sets, N, seq
+
+
+def dsa_bytes():
+    c = DSA
+    e = 2
+    return (c["B"] * c["S"] * (2 * c["Dc"] + c["Dp"]) * e + c["B"] * c["H"] * (c["Dc"] + c["Dp"]) * e
+            + c["B"] * c["H"] * c["Dc"] * e + 4 * c["B"] * c["S"])
+
+
+def bench_dsa(b200, torch, oracle, dev, args, sampler, do_cpu):
+    c = DSA
+    layer, qn, qp, idx_sets, N, seq = build_dsa(b200, torch, dev, 77)
+    out = torch.empty((c["B"], c["H"], c["Dc"]), dtype=torch.float32, device=dev)
+    steps = max(args.steps, 20)
+    for i in range(max(args.warmup, 3)):
+        layer.forward(qn, qp, idx_sets[i % 4], out)
+    torch.cuda.synchronize()
+    assert b200.device_status() == 0, "device-side wait timed out"
+    b200.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    e0.record()
+    for i in range(steps):
+        layer.forward(qn, qp, idx_sets[i % 4], out)      # a different row set each step: 4 x 285 MB > L2
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.stop()
+    launches = b200.launch_count()
+    us = e0.elapsed_time(e1) / steps * 1e3
+    hbm, bf16_tf, which = measured_peaks()
+    nbytes = dsa_bytes()
+    res = {"metric": "dsa_decode_us_per_step", "value": us, "unit": "us/step", "higher_is_better": False,
+           "steps": steps, "gpu_launches": int(launches), "dtype": "bf16",
+           "config": {"workload": "C4: B=64 H=128 Dc=512 Dp=64 top-k=2048, paged bf16 cache, page 64, "
+                                  f"seq_len U[8192,131072] ({N} cache rows), indices unsorted",
+                      "l2": "4 index sets rotate; 285 MB of rows per step > 126 MB L2"},
+           "roofline": {"kernel": "dsa_decode_bf16_kernel", "bound": "hbm", "achieved": nbytes / (us * 1e-6) / 1e9,
+                        "peak": hbm, "unit": "GB/s", "frac": nbytes / (us * 1e-6) / 1e9 / hbm, "traffic": None,
+                        "peak_source": which, "algorithmic_bytes": int(nbytes),
+                        "tflops": 2.0 * c["B"] * c["H"] * c["S"] * (2 * c["Dc"] + c["Dp"]) / (us * 1e-6) / 1e12,
+                        "frac_of_nominal_8TBs": nbytes / (us * 1e-6) / 8e12}}
+    if do_cpu:
+        qn_h, qp_h = qn.cpu().pin_memory(), qp.cpu().pin_memory()
+        idx_h = [i.cpu().pin_memory() for i in idx_sets]
+        out_h = torch.empty(out.shape, dtype=torch.float32).pin_memory()
+        for i in range(2):
+            layer.forward_host(qn_h, qp_h, idx_h[i], out_h)
+        t0 = time.perf_counter()
+        for i in range(steps):
+            layer.forward_host(qn_h, qp_h, idx_h[i % 4], out_h)
+        e2e_us = (time.perf_counter() - t0) / steps * 1e6
+        res["e2e"] = {"value": e2e_us, "unit": "us/step",
+                      "h2d_bytes_per_step": int(qn_h.numel() * 2 + qp_h.numel() * 2 + idx_h[0].numel() * 4),
+                      "d2h_bytes_per_step": int(out_h.numel() * 4)}
+        # CPU oracle on a sample of queries (rows gathered on the device, computed on the host)
+        nq = args.cpu_queries
+        idx = idx_sets[0][:nq].long()
+        layer.forward(qn, qp, idx_sets[0], out)
+        torch.cuda.synchronize()
+        as_u16 = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+        gkc = as_u16(layer.kc[idx.reshape(-1)]); gkp = as_u16(layer.kp[idx.reshape(-1)]); gv = as_u16(layer.v[idx.reshape(-1)])
+        threads = oracle.max_threads()
+        oracle.set_threads(threads)
+        t0 = time.perf_counter()
+        ref = oracle.dsa_forward_bf16_gathered(as_u16(qn[:nq]), as_u16(qp[:nq]), gkc, gkp, gv, c["S"])
+        cpu_s = time.perf_counter() - t0
+        err = float(np.abs(out[:nq].cpu().numpy() - ref).max())
+        res["cpu_baseline"] = {"value": cpu_s / nq * c["B"] * 1e6, "unit": "us/step", "cores": threads, "kind": "port",
+                               "sample": f"{nq} of the 64 queries ({cpu_s:.2f} s), scaled to the batch of 64"}
+        res["parity"] = {"checked_queries": nq, "max_abs_err": err, "ok": bool(err < 1e-2), "tolerance": "1e-2 abs"}
+    del layer
+    torch.cuda.empty_cache()
+    return res
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm: the CPU implementation of the path (oracle port) on the host cores
+# ---------------------------------------------------------------------------------------------
+def reference_arm(args, world, rank):
+    if rank != 0:
+        return
+    import oracle
+    b200 = load_package()
+    c = MOE
+    threads = oracle.max_threads()
+    oracle.set_threads(threads)
+    n_tok, n_exp = args.cpu_tokens, 2
+    # bounded sample of the same workload: n_tok tokens, their 8 experts mapped onto a pool of n_exp
+    # generated experts (the CPU cost per token does not depend on which expert it is)
+    def synth(seed, n, sigma, chunk=1 << 22):
+        return np.concatenate([b200.synth_normal_host(seed, i, min(chunk, n - i), sigma) for i in range(0, n, chunk)])
+    w1 = synth(1000, n_exp * 2 * c["I"] * c["D"], 0.02).reshape(n_exp, 2 * c["I"], c["D"])
+    w2 = synth(2000, n_exp * c["D"] * c["I"], 0.02).reshape(n_exp, c["D"], c["I"])
+    w1q, w1s = oracle.quant_weight(w1)
+    w2q, w2s = oracle.quant_weight(w2)
+    del w1, w2
+    wg = b200.synth_normal_host(3000, 0, c["E"] * c["D"], c["D"] ** -0.5).reshape(c["E"], c["D"])
+    bias = b200.synth_normal_host(3001, 0, c["E"], 0.01)
+    x = b200.synth_normal_host(4000, 0, n_tok * c["D"], 1.0).reshape(n_tok, c["D"])
+    xq, xs = oracle.quant_act(x)
+    times = []
+    for step in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        ids, wts = oracle.route_grouped(xq, xs, wg, bias, c["K"], c["n_group"], c["topk_group"], c["routed_scale"])
+        oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, (ids % n_exp).astype(np.int32), wts,
+                               np.arange(n_tok, dtype=np.int32))
+        dt = time.perf_counter() - t0
+        if step >= args.warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    val = n_tok / sec
+    line = {"impl": "reference", "metric": "fp8_moe_layer_tokens_per_s", "value": val, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": "C3: FP8 block-scale MoE, D=7168 I=2048 E=256 top-8 (8 groups/top-4), T=4096; "
+                                   f"each step = {n_tok} tokens of it on the host"},
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": f"{n_tok} tokens per step (routing + 8 experts each), fp32 CPU emulation of "
+                                       "the FP8 sequence; the reference's own CPU code is fp32-only and has no "
+                                       "FP8 / grouped-routing path"},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-dsa", action="store_true")
+    ap.add_argument("--skip-moe", action="store_true")
+    ap.add_argument("--cpu-tokens", type=int, default=24)
+    ap.add_argument("--cpu-queries", type=int, default=4)
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, world, rank)
+        return
+
+    import torch
+    import oracle            # the checker for the CPU-baseline / parity leg only
+    b200 = load_package()
+    b200.lib()               # fail loudly when the CUDA library is missing
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(local_rank)
+
+    if args.skip_moe:
+        moe = {"value": None, "ms_per_step": None, "gpu_launches": 0}
+    elif world == 1:
+        moe = bench_moe_single(b200, torch, oracle, dev, args, sampler)
+    else:
+        moe = bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler)
+    clocks = sampler.summary()
+    dsa = None
+    if not args.skip_dsa:
+        s2 = ClockSampler(local_rank)
+        dsa = bench_dsa(b200, torch, oracle, dev, args, s2, do_cpu=(rank == 0))
+        dsa["clocks"] = s2.summary()
+        if world > 1:
+            t = torch.tensor([dsa["value"]], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dsa["value"] = float(t.item())
+            dsa["replicas"] = world
+    if rank == 0:
+        c = MOE
+        line = {"metric": "fp8_moe_layer_tokens_per_s", "value": moe["value"], "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": moe["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
+                "data": "synthetic",
+                "config": {"workload": ("C3" if world == 1 else "C5") + ": FP8 block-scale MoE layer, D=7168 I=2048 "
+                           "E=256 top-8 (8 groups / top-4), sigmoid+bias scoring, routed_scaling 2.5, T=4096 per GPU"
+                           + ("" if world == 1 else f", experts sharded over {world} GPUs, Zipf(1.1) load"),
+                           "tokens_per_gpu": c["T"], "parallelism": "single" if world == 1 else f"ep{world}",
+                           "l2": "11.3 GB of FP8 weights stream every step (inputs > 126 MB L2)"},
+                "clocks": clocks, "gpu_launches": moe.get("gpu_launches", 0)}
+        for k in ("e2e", "roofline", "cpu_baseline", "parity", "kernels"):
+            if k in moe:
+                line[k] = moe[k]
+        if dsa is not None:
+            line["dsa"] = dsa
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

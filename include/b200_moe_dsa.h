@@ -159,10 +159,11 @@ B200_API int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const floa
                                       b200_stream_t stream);
 
 /* Measurement aid (no reference counterpart): when enabled, CUDA events are recorded on
- * the launch stream around the two grouped GEMM kernels of every FP8 layer call; the read
- * returns the device time of the last call's GEMM1 and GEMM2 in milliseconds. */
+ * the launch stream around the two grouped GEMM kernels of every FP8 layer call (enabling
+ * resets the record); the read returns the mean device time of GEMM1 and GEMM2 in
+ * milliseconds over the recorded calls (at most the last 256) and their number. */
 B200_API int b200_moe_fp8_profile(int enable);
-B200_API int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms);
+B200_API int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms, int* calls);
 
 /* --------------------------------------------------------------------------- */
 /* DSA / MLA sparse decode                                                      */

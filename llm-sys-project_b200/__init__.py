@@ -184,9 +184,9 @@ def moe_fp8_profile(enable):
 
 
 def moe_fp8_profile_read():
-    a, b = C.c_float(0), C.c_float(0)
-    _check(lib().b200_moe_fp8_profile_read(C.byref(a), C.byref(b)), "moe_fp8_profile_read")
-    return a.value, b.value
+    a, b, n = C.c_float(0), C.c_float(0), C.c_int(0)
+    _check(lib().b200_moe_fp8_profile_read(C.byref(a), C.byref(b), C.byref(n)), "moe_fp8_profile_read")
+    return a.value, b.value, n.value
 
 
 # ---------------------------------------------------------------------------

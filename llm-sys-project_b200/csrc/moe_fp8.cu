@@ -321,9 +321,11 @@ sort_rows_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ x
 
 // Optional per-kernel timing: CUDA events recorded on the launch stream around the two grouped
 // GEMMs (used by the benchmark for the roofline line; off by default).
+constexpr int PROF_SLOTS = 256;
 bool g_prof_on = false;
-cudaEvent_t g_prof_ev[4] = {nullptr, nullptr, nullptr, nullptr};
-int g_prof_valid = 0;
+cudaEvent_t g_prof_ev[PROF_SLOTS][4];
+bool g_prof_created = false;
+long long g_prof_calls = 0;      // layer calls recorded since profiling was enabled
 
 struct Fp8Scratch {
     float* partials; int* ids; float* wts; int* counts; int* offsets; int* row_pair;
@@ -391,9 +393,9 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, 64);
     if (st) return st;
     p.a_scale = s.ss; p.w_scale = w1s; p.act_q = s.act_q; p.act_s = s.act_s;
-    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[0], stream));
+    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][0], stream));
     grouped_gemm_fp8_kernel<1><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
-    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[1], stream));
+    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][1], stream));
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     if (!do_gemm2) return B200_OK;
@@ -405,9 +407,9 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     if (st) return st;
     p.a_scale = s.act_s; p.w_scale = w2s; p.row_tok = s.row_tok; p.row_w = s.row_w; p.out = out;
     B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)T * D, stream));
-    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[2], stream));
+    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][2], stream));
     grouped_gemm_fp8_kernel<2><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
-    if (g_prof_on) { B200_CUDA_TRY(cudaEventRecord(g_prof_ev[3], stream)); g_prof_valid = 1; }
+    if (g_prof_on) { B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][3], stream)); g_prof_calls++; }
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -418,19 +420,32 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
 extern "C" {
 
 int b200_moe_fp8_profile(int enable) {
-    if (enable && !g_prof_ev[0])
-        for (int i = 0; i < 4; i++) B200_CUDA_TRY(cudaEventCreate(&g_prof_ev[i]));
+    if (enable && !g_prof_created) {
+        for (int i = 0; i < PROF_SLOTS; i++)
+            for (int j = 0; j < 4; j++) B200_CUDA_TRY(cudaEventCreate(&g_prof_ev[i][j]));
+        g_prof_created = true;
+    }
     g_prof_on = enable != 0;
-    g_prof_valid = 0;
+    g_prof_calls = 0;
     return B200_OK;
 }
 
-int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms) {
-    if (!gemm1_ms || !gemm2_ms) return B200_BAD_ARG;
-    if (!g_prof_valid) return B200_BAD_ARG;
-    B200_CUDA_TRY(cudaEventSynchronize(g_prof_ev[3]));
-    B200_CUDA_TRY(cudaEventElapsedTime(gemm1_ms, g_prof_ev[0], g_prof_ev[1]));
-    B200_CUDA_TRY(cudaEventElapsedTime(gemm2_ms, g_prof_ev[2], g_prof_ev[3]));
+int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms, int* calls) {
+    if (!gemm1_ms || !gemm2_ms || !calls) return B200_BAD_ARG;
+    const int n = (int)(g_prof_calls < PROF_SLOTS ? g_prof_calls : PROF_SLOTS);
+    *calls = n;
+    *gemm1_ms = *gemm2_ms = 0.0f;
+    if (n == 0) return B200_OK;
+    double s1 = 0.0, s2 = 0.0;
+    for (int i = 0; i < n; i++) {
+        float a = 0.f, b = 0.f;
+        B200_CUDA_TRY(cudaEventSynchronize(g_prof_ev[i][3]));
+        B200_CUDA_TRY(cudaEventElapsedTime(&a, g_prof_ev[i][0], g_prof_ev[i][1]));
+        B200_CUDA_TRY(cudaEventElapsedTime(&b, g_prof_ev[i][2], g_prof_ev[i][3]));
+        s1 += a; s2 += b;
+    }
+    *gemm1_ms = (float)(s1 / n);
+    *gemm2_ms = (float)(s2 / n);
     return B200_OK;
 }
 
