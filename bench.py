@@ -480,7 +480,13 @@ def main():
     ap.add_argument("--skip-moe", action="store_true")
     ap.add_argument("--cpu-tokens", type=int, default=24)
     ap.add_argument("--cpu-queries", type=int, default=4)
+    ap.add_argument("--small", action="store_true",
+                    help="profiling-sized case of the same kernels (32 experts, 512 tokens; 16 queries, short caches): "
+                         "inputs still exceed L2 but only ~2 GB live on the device; not a bench value")
     args = ap.parse_args()
+    if args.small:
+        MOE.update(T=512, E=32, n_group=4, topk_group=2)
+        DSA.update(B=16, seq_min=8192, seq_max=16384)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -111,8 +111,8 @@ def test_reference_test_driver_passes(b200, cuda):
 # ---------------------------------------------------------------------------------------
 # tensor-core path
 # ---------------------------------------------------------------------------------------
-@pytest.mark.parametrize("mode,N,K", [(0, 32, 576), (0, 256, 64), (1, 256, 32), (1, 64, 64), (2, 256, 128),
-                                      (2, 128, 256), (3, 256, 32), (3, 64, 64)])
+@pytest.mark.parametrize("mode,N,K", [(0, 32, 576), (0, 256, 64), (1, 256, 128), (1, 64, 64), (2, 256, 128),
+                                      (2, 128, 256), (3, 256, 128), (3, 64, 64)])
 def test_umma_selftest(b200, cuda, mode, N, K):
     """D[128,N] = A[128,K] * B[N,K]^T through the production shared-memory layouts/descriptors."""
     rng = np.random.default_rng(100 + mode)
