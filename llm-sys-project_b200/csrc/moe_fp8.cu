@@ -32,7 +32,7 @@ constexpr int A_BYTES = BM * BK;            // 16384
 constexpr int B_BYTES = BN * BK;            // 32768
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_EPI_THREADS = 256;
-constexpr int GEMM_THREADS = 320;
+constexpr int GEMM_THREADS = 384;          // warpgroups 0,1: promotion/epilogue; warpgroup 2: TMA + MMA warps
 constexpr int MAX_E = 1024;
 
 struct GemmSmem {
@@ -135,7 +135,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         m_tile = local - n_tile * mt;
     };
 
-    if (warp == 8) {
+    // Register budget: the two promotion warpgroups hold a 128-value accumulator row plus a
+    // 64-value staging buffer per thread; the TMA/MMA warpgroup needs almost nothing.
+
+    if (warp >= 8) {
+        ptx::setmaxnreg_dec<40>();
+      if (warp == 8) {
         // ===================== TMA producer =====================
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
@@ -165,7 +170,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 }
             }
         }
-    } else if (warp == 9) {
+      } else if (warp == 9) {
         // ===================== MMA issuer =====================
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::make_idesc(0, 0, 0, 0, BM, BN);
@@ -192,8 +197,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 }
             }
         }
+      }
     } else {
         // ===================== promotion + epilogue (warps 0-7) =====================
+        ptx::setmaxnreg_inc<232>();
         const int wg = warp >> 2;                         // column half of the accumulator
         const int row = (warp & 3) * 32 + lane;           // TMEM lane = tile row
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
@@ -221,24 +228,36 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 #pragma unroll
             for (int i = 0; i < 128; i++) accv[i] = 0.0f;
 
+            // scales of K block kb+1 are fetched while block kb is being promoted
+            float sa_n = row_ok ? a_sc[0] : 0.0f, w0_n = w_sc0[0], w1_n = w_sc1[0];
             for (int kb = 0; kb < nkb; kb++) {
-                const float sa = row_ok ? a_sc[kb] : 0.0f;
-                const float s0 = sa * w_sc0[kb];
-                const float s1 = sa * w_sc1[kb];
+                const float s0 = sa_n * w0_n;
+                const float s1 = sa_n * w1_n;
+                if (kb + 1 < nkb) {
+                    sa_n = row_ok ? a_sc[kb + 1] : 0.0f;
+                    w0_n = w_sc0[kb + 1];
+                    w1_n = w_sc1[kb + 1];
+                }
                 if (!ptx::mbar_wait(&sm->tmem_full[acc], acc_ph, abort_flag)) goto done;
                 ptx::tc_fence_after();
                 const uint32_t t0 = tmem_base + lane_addr + acc * BN + wg * 128;
+                uint32_t ra[32], rb[32];
+                ptx::tmem_ld_32x32(t0, ra);               // MODE 1: gate columns
+                ptx::tmem_ld_32x32(t0 + 32, rb);
+                ptx::tc_wait_ld();
 #pragma unroll
-                for (int c4 = 0; c4 < 4; c4++) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32(t0 + c4 * 32, r);
-                    ptx::tc_wait_ld();
-                    const float sc = (c4 < 2) ? s0 : s1;   // MODE 1: cols 0-63 gate, 64-127 up
+                for (int i = 0; i < 32; i++) accv[i] += __uint_as_float(ra[i]) * s0;
 #pragma unroll
-                    for (int i = 0; i < 32; i++) accv[c4 * 32 + i] += __uint_as_float(r[i]) * sc;
-                }
+                for (int i = 0; i < 32; i++) accv[32 + i] += __uint_as_float(rb[i]) * s0;
+                ptx::tmem_ld_32x32(t0 + 64, ra);          // MODE 1: up columns
+                ptx::tmem_ld_32x32(t0 + 96, rb);
+                ptx::tc_wait_ld();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&sm->tmem_empty[acc]);
+                ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
+#pragma unroll
+                for (int i = 0; i < 32; i++) accv[64 + i] += __uint_as_float(ra[i]) * s1;
+#pragma unroll
+                for (int i = 0; i < 32; i++) accv[96 + i] += __uint_as_float(rb[i]) * s1;
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
 
