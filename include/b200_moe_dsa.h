@@ -179,6 +179,24 @@ B200_API int b200_dsa_forward_f32(b200_ws* ws, const float* q_nope, const float*
 B200_API int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe,
                                    const uint16_t* kc, const uint16_t* kp, const uint16_t* v, const int* idx,
                                    float* out, const b200_dsa_config* cfg, b200_stream_t stream);
+/* No counterpart in the reference.  Same computation and arguments as b200_dsa_forward_bf16, for
+ * callers that must not allocate device memory: processes whose memory pool owns all of HBM and
+ * forbids cudaMalloc after start-up, plugins that are only handed input and output buffers, and
+ * latency-critical loops that cannot tolerate a workspace that grows (and synchronises the device
+ * when it does).  The split-KV partial results go to a 16 MiB array built into the library (every
+ * GPU that loads the library holds it until the process exits) instead of the workspace; the call
+ * uses no workspace and calls no allocating routine.  Shapes whose partial results do not fit
+ * (queries x splits x 256 KiB + 1 KiB each, beyond 16 MiB) are rejected with B200_UNSUPPORTED and
+ * an explanatory b200_last_error_string.  The first call on each device looks up the array's
+ * device address (cudaGetSymbolAddress) and sets the kernel's shared-memory limit, so make that
+ * first call outside any stream capture.  All calls on a device share the one array: it keeps the
+ * previous call's contents (only the status word is cleared, everything read is rewritten first),
+ * and two calls that overlap on the GPU (different streams) race on it.  device_status, if not
+ * NULL, is a caller-owned device int that is cleared and receives B200_TIMEOUT should a bounded
+ * device-side wait run out. */
+B200_API int b200_dsa_forward_bf16_static(const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
+                                          const uint16_t* kp, const uint16_t* v, const int* idx, float* out,
+                                          const b200_dsa_config* cfg, int* device_status, b200_stream_t stream);
 /* naive_dsa.cuh:31-37 (dsa_kv_gather) */
 B200_API int b200_dsa_kv_gather_f32(const float* kc, const float* kp, const float* v, const int* idx,
                                     float* g_kc, float* g_kp, float* g_v, const b200_dsa_config* cfg,

@@ -50,7 +50,7 @@ EXPORTED_SYMBOLS = [
     "b200_swiglu_f32", "b200_moe_scatter_f32",
     "b200_quant_act_1x128", "b200_quant_weight_128x128", "b200_moe_route_fp8", "b200_moe_fp8_forward",
     "b200_moe_fp8_experts", "b200_moe_fp8_gemm1_stage", "b200_moe_fp8_profile", "b200_moe_fp8_profile_read",
-    "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
+    "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
     "b200_dsa_softmax_f32", "b200_dsa_output_proj_f32",
     "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128", "b200_umma_selftest",
 ]
@@ -204,6 +204,18 @@ def dsa_forward_bf16(q_nope, q_pe, kv_cache_compressed, kv_cache_positional, v_c
     _check(lib().b200_dsa_forward_bf16(None, _p(q_nope), _p(q_pe), _p(kv_cache_compressed),
                                        _p(kv_cache_positional), _p(v_cache), _p(sparse_indices), _p(output),
                                        C.byref(cfg), _stream(stream)), "dsa_forward_bf16")
+
+
+def dsa_forward_bf16_static(q_nope, q_pe, kv_cache_compressed, kv_cache_positional, v_cache, sparse_indices, output,
+                            cfg, device_status=None, stream=None):
+    """bf16 decode for callers that may not allocate device memory (a pool that owns all of HBM, a
+    plugin that only receives its input/output buffers): the split-KV partial results live in a
+    16 MiB array built into the library instead of the growable workspace.  Raises B200Error
+    (B200_UNSUPPORTED) when they would not fit.  Calls share the array; do not overlap them."""
+    _check(lib().b200_dsa_forward_bf16_static(_p(q_nope), _p(q_pe), _p(kv_cache_compressed),
+                                              _p(kv_cache_positional), _p(v_cache), _p(sparse_indices), _p(output),
+                                              C.byref(cfg), _p(device_status), _stream(stream)),
+           "dsa_forward_bf16_static")
 
 
 def dsa_kv_gather(kc, kp, v, sparse_indices, g_kc, g_kp, g_v, cfg, stream=None):

@@ -22,6 +22,7 @@
 // grows by more than 2^8 (the factor is carried in P and in the running sum instead).
 // Every mbarrier wait is bounded; on give-up the CTA flags B200_TIMEOUT and winds down.
 #include <cfloat>
+#include <cstdio>
 
 #include "common.cuh"
 
@@ -402,6 +403,118 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
     B200_CUDA_TRY(cudaGetLastError());
     if (NS > 1) {
         dsa_merge_kernel<<<dim3(H, Q), 128, 0, stream>>>(part_o, part_ml, out, H, NS);
+        b200_count_launch(1);
+        B200_CUDA_TRY(cudaGetLastError());
+    }
+    return B200_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the bf16 decode call.
+//
+// Some hosts of this library may not allocate device memory at all once they are running: a
+// serving process whose memory pool owns every byte of HBM and forbids cudaMalloc after start-up,
+// a plugin loaded into a framework that hands out only the input and output buffers, or a caller
+// sitting inside a latency-critical loop where a growing workspace (and the device synchronise
+// that growth implies) is unacceptable.  For them the split-KV partial results live in the
+// fixed array below instead of the growable workspace.  The array is part of the loaded module:
+// every GPU that loads the library holds B200_DSA_STATIC_SCRATCH_BYTES of it until the process
+// exits, whether or not this entry point is ever called.
+// ---------------------------------------------------------------------------------------------
+#define B200_DSA_STATIC_SCRATCH_BYTES (16u << 20)
+static __device__ __align__(256) unsigned char g_dsa_static_scratch[B200_DSA_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of the array per device.  In host code the array's name is only a handle for
+// the runtime, not a device pointer, so the address is asked for once per device (with that
+// device current) and cached.
+unsigned char* g_static_scratch_addr[64] = {nullptr};
+int g_static_sm_count[64] = {0};
+
+int static_scratch_setup(int dev) {
+    if (g_static_scratch_addr[dev]) return B200_OK;
+    void* p = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(&p, g_dsa_static_scratch));
+    if (!p) return B200_CUDA_ERROR;
+    int sms = 0;
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    B200_CUDA_TRY(cudaFuncSetAttribute(dsa_decode_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)DSA_SMEM_BYTES));
+    g_static_sm_count[dev] = sms;
+    g_static_scratch_addr[dev] = static_cast<unsigned char*>(p);
+    return B200_OK;
+}
+}  // namespace
+
+void b200_set_last_error_text(const char* text);
+
+extern "C" int b200_dsa_forward_bf16_static(const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
+                                            const uint16_t* kp, const uint16_t* v, const int* idx, float* out,
+                                            const b200_dsa_config* cfg, int* device_status,
+                                            b200_stream_t stream) {
+    if (!cfg) return B200_BAD_ARG;
+    if (!q_nope || !q_pe || !kc || !kp || !v || !idx || !out) return B200_BAD_ARG;
+    const int Q = cfg->num_queries, H = cfg->num_heads, S = cfg->num_selected_kv;
+    if (Q <= 0 || H <= 0 || S <= 0) return B200_BAD_SHAPE;
+    if (cfg->head_dim_compressed != DC || cfg->head_dim_positional != DP) return B200_UNSUPPORTED;
+    if (H > HEADS) return B200_UNSUPPORTED;
+    if (S % TKV) return B200_BAD_SHAPE;
+    if (Q > 65535) return B200_UNSUPPORTED;
+    const uintptr_t align = reinterpret_cast<uintptr_t>(q_nope) | reinterpret_cast<uintptr_t>(q_pe) |
+                            reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(kp) |
+                            reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out);
+    if (align & 15) return B200_BAD_ARG;
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return B200_UNSUPPORTED;
+    int st = static_scratch_setup(dev);      // first call on a device: not inside a stream capture
+    if (st) return st;
+    unsigned char* scratch = g_static_scratch_addr[dev];
+
+    // same work split as the workspace-backed call
+    const int nt_total = S / TKV;
+    int NS = 1;
+    if (2 * Q < g_static_sm_count[dev]) NS = g_static_sm_count[dev] / (2 * Q);
+    if (NS > nt_total) NS = nt_total;
+    if (NS > 64) NS = 64;
+    if (NS < 1) NS = 1;
+    const int tps = ceil_div(nt_total, NS);
+    NS = ceil_div(nt_total, tps);
+
+    // layout inside the array: [0,256) status word | partial (max,sum) pairs | partial outputs
+    const size_t ml_bytes = ((size_t)Q * NS * HEADS * 2 * sizeof(float) + 255) & ~size_t(255);
+    const size_t o_bytes = (size_t)Q * NS * HEADS * DC * sizeof(float);
+    const size_t need = (NS > 1) ? 256 + ml_bytes + o_bytes : 256;
+    if (need > B200_DSA_STATIC_SCRATCH_BYTES) {
+        char msg[200];
+        snprintf(msg, sizeof(msg),
+                 "b200_dsa_forward_bf16_static: %d queries x %d splits need %zu bytes of scratch, the built-in "
+                 "array holds %u; use b200_dsa_forward_bf16 or fewer queries per call",
+                 Q, NS, need, (unsigned)B200_DSA_STATIC_SCRATCH_BYTES);
+        b200_set_last_error_text(msg);
+        return B200_UNSUPPORTED;
+    }
+    int* status_word = device_status ? device_status : reinterpret_cast<int*>(scratch);
+    // the status word must start at zero; the partial results are fully rewritten by the decode
+    // kernel before the merge kernel reads them, so stale contents of earlier calls do not matter
+    B200_CUDA_TRY(cudaMemsetAsync(status_word, 0, sizeof(int), stream));
+
+    DsaParams p;
+    p.q_nope = reinterpret_cast<const __nv_bfloat16*>(q_nope);
+    p.q_pe = reinterpret_cast<const __nv_bfloat16*>(q_pe);
+    p.kc = reinterpret_cast<const __nv_bfloat16*>(kc);
+    p.kp = reinterpret_cast<const __nv_bfloat16*>(kp);
+    p.v = reinterpret_cast<const __nv_bfloat16*>(v);
+    p.idx = idx; p.out = out; p.status = status_word;
+    p.part_ml = reinterpret_cast<float*>(scratch + 256);
+    p.part_o = reinterpret_cast<float*>(scratch + 256 + ml_bytes);
+    p.H = H; p.S = S; p.NS = NS; p.tiles_per_split = tps;
+    p.sl2 = 1.4426950408889634f / sqrtf((float)(DC + DP));
+    dsa_decode_bf16_kernel<<<dim3(2, NS, Q), DSA_THREADS, DSA_SMEM_BYTES, stream>>>(p);
+    b200_count_launch(1);
+    B200_CUDA_TRY(cudaGetLastError());
+    if (NS > 1) {
+        dsa_merge_kernel<<<dim3(H, Q), 128, 0, stream>>>(p.part_o, p.part_ml, out, H, NS);
         b200_count_launch(1);
         B200_CUDA_TRY(cudaGetLastError());
     }

@@ -13,6 +13,7 @@ void b200_set_last_cuda_error(cudaError_t e, const char* file, int line) {
     snprintf(g_err, sizeof(g_err), "%s at %s:%d", cudaGetErrorString(e), file, line);
 }
 void b200_count_launch(int n) { g_launches += n; }
+void b200_set_last_error_text(const char* text) { snprintf(g_err, sizeof(g_err), "%s", text); }
 
 extern "C" {
 
