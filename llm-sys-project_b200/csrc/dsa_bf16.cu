@@ -23,6 +23,7 @@
 // Every mbarrier wait is bounded; on give-up the CTA flags B200_TIMEOUT and winds down.
 #include <cfloat>
 #include <cstdio>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -343,6 +344,10 @@ __global__ void __launch_bounds__(128) dsa_merge_kernel(const float* __restrict_
 
 }  // namespace
 
+int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, const void* kp, const void* v,
+                         const int* idx, float* out, float* part_o, float* part_ml, int* status, int Q, int H, int S,
+                         int NS, int tiles_per_split, cudaStream_t stream);
+
 extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
                                      const uint16_t* kp, const uint16_t* v, const int* idx, float* out,
                                      const b200_dsa_config* cfg, b200_stream_t stream) {
@@ -361,8 +366,12 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
     if (!ws) ws = b200_default_ws();
     if (!ws) return B200_CUDA_ERROR;
 
+    // The CTA-pair kernel (64-row tiles, double-buffered) handles every shape with S % 64 == 0; the
+    // single-CTA kernel (32-row tiles) takes the rest.  B200_DSA_SINGLE_CTA=1 forces the latter.
+    static const bool force_single = getenv("B200_DSA_SINGLE_CTA") != nullptr;
+    const bool use_pair = (S % 64 == 0) && !force_single;
     // split the selected rows so that the grid covers the machine about once
-    const int nt_total = S / TKV;
+    const int nt_total = S / (use_pair ? 64 : TKV);
     int NS = 1;
     if (2 * Q < ws->sm_count) NS = ws->sm_count / (2 * Q);
     if (NS > nt_total) NS = nt_total;
@@ -381,6 +390,17 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
         WsCarver cv(ws->base);
         part_o = cv.take<float>((size_t)Q * NS * HEADS * DC);
         part_ml = cv.take<float>((size_t)Q * NS * HEADS * 2);
+    }
+    if (use_pair) {
+        int st = b200_launch_dsa_pair(q_nope, q_pe, kc, kp, v, idx, out, part_o, part_ml, ws->d_status, Q, H, S, NS, tps,
+                                      stream);
+        if (st) return st;
+        if (NS > 1) {
+            dsa_merge_kernel<<<dim3(H, Q), 128, 0, stream>>>(part_o, part_ml, out, H, NS);
+            b200_count_launch(1);
+            B200_CUDA_TRY(cudaGetLastError());
+        }
+        return B200_OK;
     }
     static bool attr_done = false;
     if (!attr_done) {

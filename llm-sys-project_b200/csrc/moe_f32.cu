@@ -232,7 +232,7 @@ int b200_moe_forward_f32(b200_ws* ws, const float* x, const float* gate_w, const
     st = launch_route_select(partials, 1, nullptr, ids, wts, nullptr, nullptr, T, E, K, B200_SCORE_SOFTMAX, 1, 1,
                              1.0f, stream);
     if (st) return st;
-    st = launch_permute(ids, T, K, E, counts, offsets, row_pair, stream);
+    st = launch_permute(ids, T, K, E, nullptr, true, counts, offsets, row_pair, stream);
     if (st) return st;
     B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)T * D, stream));   // naive_moe.cu:413
     dim3 g1(ceil_div(I, G_TN), ceil_div(T, G_TM), E);

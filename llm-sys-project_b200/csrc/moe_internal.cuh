@@ -13,6 +13,8 @@ int launch_gate_logits(const void* x, const float* xs, const float* wg, float* p
 int launch_route_select(const float* partials, int n_chunks, const float* bias, int* ids, float* wts, int* counts,
                         float* logits_out, int T, int E, int K, int scoring, int n_group, int topk_group,
                         float routed_scale, cudaStream_t stream);
-int launch_permute(const int* ids, int T, int K, int E, int* counts, int* offsets, int* row_pair,
-                   cudaStream_t stream);
+// counts_in: the router's per-expert histogram (may be NULL: counted from ids).  trusted: ids come from
+// this library's router (an expert appears at most once per token), so the duplicate check is skipped.
+int launch_permute(const int* ids, int T, int K, int E, const int* counts_in, bool trusted, int* counts,
+                   int* offsets, int* row_pair, cudaStream_t stream);
 int check_route_cfg(int T, int E, int K, int D, int scoring, int n_group, int topk_group);

@@ -1,6 +1,6 @@
 // MoE routing and permutation (all data types share these kernels).
 //
-//   gate_logits_kernel   tokens x experts register-tiled dot products.  Each logit is
+//   gate_logits_kernel   tokens x experts register-tiled (128 x 128 x 16, 8 x 8 per thread) dot products.  Each logit is
 //                        accumulated in a fixed order so the CPU side can reproduce it
 //                        bit for bit: chunks of `chunk` consecutive d, each chunk a
 //                        sequential chain from 0, chunk partials summed in order.
@@ -21,76 +21,107 @@
 // ---------------------------------------------------------------------------
 // gate logits
 // ---------------------------------------------------------------------------
-#define GL_TM 64
-#define GL_TN 64
+#define GL_TM 128
+#define GL_TN 128
 #define GL_TK 16
+#define GL_LD (GL_TM + 4)
 
-template <bool FP8>
+// Block tile 128 tokens x 128 experts, 8 x 8 outputs per thread; every output is still one
+// sequential chain over d inside its chunk, so the CPU reproduces it bit for bit.
+// VEC: rows are 16-byte aligned and the chunk length is a multiple of 16 (vector loads).
+template <bool FP8, bool VEC>
 __global__ void __launch_bounds__(256)
 gate_logits_kernel(const void* __restrict__ x_, const float* __restrict__ xs, const float* __restrict__ wg,
                    float* __restrict__ partials, int T, int E, int D, int chunk) {
-    __shared__ float As[GL_TK][GL_TM + 4];
-    __shared__ float Bs[GL_TK][GL_TN + 4];
+    __shared__ __align__(16) float As[GL_TK][GL_LD];
+    __shared__ __align__(16) float Bs[GL_TK][GL_LD];
     const int t0 = blockIdx.x * GL_TM, e0 = blockIdx.y * GL_TN, c = blockIdx.z;
     const int d_begin = c * chunk;
     const int d_end = min(D, d_begin + chunk);
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // tx -> experts, ty -> tokens
-    float acc[4][4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // tx -> 8 experts, ty -> 8 tokens
+    float acc[8][8];
 #pragma unroll
-    for (int i = 0; i < 4; i++)
+    for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
 
-    const int lr = threadIdx.x >> 2;          // 0..63: row of the tile this thread loads
-    const int lk = (threadIdx.x & 3) * 4;     // 0,4,8,12
     for (int d0 = d_begin; d0 < d_end; d0 += GL_TK) {
-        {   // tokens
-            int t = t0 + lr;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (t < T) {
+        // ---- stage the token tile (dequantised) and the expert tile, k-major ----
+        if (VEC) {
+            if (FP8) {
+                if (threadIdx.x < GL_TM) {
+                    const int t = t0 + threadIdx.x;
+                    float v[16];
+                    if (t < T) {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(x_) +
+                                                                          (size_t)t * D + d0);
+                        const float sc = xs[(size_t)t * (D / 128) + d0 / 128];
+                        const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    int d = d0 + lk + i;
-                    if (d < d_end) {
-                        if (FP8) {
-                            const uint8_t* xq = static_cast<const uint8_t*>(x_);
+                        for (int i = 0; i < 16; i++) {
                             __nv_fp8_e4m3 q;
-                            q.__x = xq[(size_t)t * D + d];
-                            v[i] = __fmul_rn(float(q), xs[(size_t)t * (D / 128) + d / 128]);
+                            q.__x = b[i];
+                            v[i] = __fmul_rn(float(q), sc);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; i++) v[i] = 0.0f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 16; i++) As[i][threadIdx.x] = v[i];
+                }
+            } else {
+#pragma unroll
+                for (int rep = 0; rep < 2; rep++) {
+                    const int idx = threadIdx.x + rep * 256, r = idx >> 2, kq = (idx & 3) * 4;
+                    const int t = t0 + r;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (t < T) v = *reinterpret_cast<const float4*>(static_cast<const float*>(x_) + (size_t)t * D + d0 + kq);
+                    As[kq][r] = v.x; As[kq + 1][r] = v.y; As[kq + 2][r] = v.z; As[kq + 3][r] = v.w;
+                }
+            }
+#pragma unroll
+            for (int rep = 0; rep < 2; rep++) {
+                const int idx = threadIdx.x + rep * 256, r = idx >> 2, kq = (idx & 3) * 4;
+                const int e = e0 + r;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (e < E) v = *reinterpret_cast<const float4*>(wg + (size_t)e * D + d0 + kq);
+                Bs[kq][r] = v.x; Bs[kq + 1][r] = v.y; Bs[kq + 2][r] = v.z; Bs[kq + 3][r] = v.w;
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < GL_TM * GL_TK; idx += 256) {
+                const int r = idx / GL_TK, k = idx % GL_TK, d = d0 + k;
+                float xv = 0.0f, wv = 0.0f;
+                if (d < d_end) {
+                    if (t0 + r < T) {
+                        if (FP8) {
+                            __nv_fp8_e4m3 q;
+                            q.__x = static_cast<const uint8_t*>(x_)[(size_t)(t0 + r) * D + d];
+                            xv = __fmul_rn(float(q), xs[(size_t)(t0 + r) * (D / 128) + d / 128]);
                         } else {
-                            v[i] = static_cast<const float*>(x_)[(size_t)t * D + d];
+                            xv = static_cast<const float*>(x_)[(size_t)(t0 + r) * D + d];
                         }
                     }
+                    if (e0 + r < E) wv = wg[(size_t)(e0 + r) * D + d];
                 }
+                As[k][r] = xv;
+                Bs[k][r] = wv;
             }
-#pragma unroll
-            for (int i = 0; i < 4; i++) As[lk + i][lr] = v[i];
-        }
-        {   // experts
-            int e = e0 + lr;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (e < E) {
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    int d = d0 + lk + i;
-                    if (d < d_end) v[i] = wg[(size_t)e * D + d];
-                }
-            }
-#pragma unroll
-            for (int i = 0; i < 4; i++) Bs[lk + i][lr] = v[i];
         }
         __syncthreads();
         const int kmax = min(GL_TK, d_end - d0);
+#pragma unroll 4
         for (int k = 0; k < kmax; k++) {
-            float a[4], b[4];
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[k][ty * 8]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[k][ty * 8 + 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[k][tx * 8]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[k][tx * 8 + 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-            for (int i = 0; i < 4; i++) a[i] = As[k][ty * 4 + i];
+            for (int i = 0; i < 8; i++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) b[j] = Bs[k][tx * 4 + j];
-#pragma unroll
-            for (int i = 0; i < 4; i++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) {
+                for (int j = 0; j < 8; j++) {
                     if (FP8) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
                     else     acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(a[i], b[j]));
                 }
@@ -98,12 +129,12 @@ gate_logits_kernel(const void* __restrict__ x_, const float* __restrict__ xs, co
         __syncthreads();
     }
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        int t = t0 + ty * 4 + i;
+    for (int i = 0; i < 8; i++) {
+        const int t = t0 + ty * 8 + i;
         if (t >= T) continue;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            int e = e0 + tx * 4 + j;
+        for (int j = 0; j < 8; j++) {
+            const int e = e0 + tx * 8 + j;
             if (e < E) partials[((size_t)c * T + t) * E + e] = acc[i][j];
         }
     }
@@ -254,18 +285,31 @@ __device__ __forceinline__ bool pair_selects(const int* __restrict__ ids, int p,
     return true;
 }
 
+// One block per expert.  The expert's first row (= rows owned by lower experts) comes from the
+// router's histogram when it is given, otherwise from a counting pass; ranks inside the expert are
+// assigned by a block scan over (token, slot) pairs in ascending order, four pairs per thread.
+// CHECK_DUP: a token that lists the expert twice counts once (ids supplied from outside).
+template <bool CHECK_DUP>
 __global__ void __launch_bounds__(256)
-permute_kernel(const int* __restrict__ ids, int TK, int K, int E, int* __restrict__ counts,
-               int* __restrict__ offsets, int* __restrict__ row_pair) {
+permute_kernel(const int* __restrict__ ids, int TK, int K, int E, const int* __restrict__ counts_in,
+               int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ row_pair) {
     __shared__ int warp_sums[8];
     __shared__ int s_base;
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // pass 1: rows owned by lower experts
+    auto selects = [&](int p, int id, int want) -> bool {
+        if (id != want) return false;
+        if (CHECK_DUP) return pair_selects(ids, p, K, want);
+        return true;
+    };
     int lt = 0;
-    for (int p = threadIdx.x; p < TK; p += 256) {
-        int id = ids[p];
-        if (id >= 0 && id < e && pair_selects(ids, p, K, id)) lt++;
+    if (counts_in) {
+        for (int i = threadIdx.x; i < e; i += 256) lt += counts_in[i];
+    } else {
+        for (int p = threadIdx.x; p < TK; p += 256) {
+            int id = ids[p];
+            if (id >= 0 && id < e && selects(p, id, id)) lt++;
+        }
     }
     for (int o = 16; o > 0; o >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, o);
     if (lane == 0) warp_sums[warp] = lt;
@@ -277,22 +321,44 @@ permute_kernel(const int* __restrict__ ids, int TK, int K, int E, int* __restric
     }
     __syncthreads();
     const int base = s_base;
-    // pass 2: stable ranks of this expert's pairs (ascending pair id = ascending token)
+    const bool vec = (TK % 4 == 0) && ((reinterpret_cast<uintptr_t>(ids) & 15) == 0);
     int running = 0;
-    for (int p0 = 0; p0 < TK; p0 += 256) {
-        int p = p0 + threadIdx.x;
-        bool f = (p < TK) && pair_selects(ids, p, K, e);
-        unsigned bal = __ballot_sync(0xffffffffu, f);
+    for (int p0 = 0; p0 < TK; p0 += 1024) {
+        const int p = p0 + threadIdx.x * 4;
+        int v[4] = {-1, -1, -1, -1};
+        if (vec) {
+            if (p < TK) {
+                const int4 q = *reinterpret_cast<const int4*>(ids + p);
+                v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if (p + i < TK) v[i] = ids[p + i];
+        }
+        bool f[4];
+        int c = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) { f[i] = (p + i < TK) && selects(p + i, v[i], e); c += f[i] ? 1 : 0; }
+        int incl = c;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += n;
+        }
         __syncthreads();                      // previous iteration's readers are done
-        if (lane == 0) warp_sums[warp] = __popc(bal);
+        if (lane == 31) warp_sums[warp] = incl;
         __syncthreads();
         int before = 0, total = 0;
         for (int w = 0; w < 8; w++) {
-            int v = warp_sums[w];
-            if (w < warp) before += v;
-            total += v;
+            int n = warp_sums[w];
+            if (w < warp) before += n;
+            total += n;
         }
-        if (f) row_pair[base + running + before + __popc(bal & ((1u << lane) - 1))] = p;
+        int pos = base + running + before + incl - c;
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (f[i]) row_pair[pos++] = p + i;
         running += total;
     }
     if (threadIdx.x == 0) {
@@ -311,8 +377,15 @@ int launch_gate_logits(const void* x, const float* xs, const float* wg, float* p
                        bool fp8, cudaStream_t stream) {
     int chunk = fp8 ? MOE_GATE_CHUNK : D;
     dim3 grid(ceil_div(T, GL_TM), ceil_div(E, GL_TN), moe_gate_chunks(D, fp8));
-    if (fp8) gate_logits_kernel<true><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
-    else     gate_logits_kernel<false><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
+    const bool vec = (D % 16 == 0) && (chunk % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(wg) & 15) == 0);
+    if (fp8) {
+        if (vec) gate_logits_kernel<true, true><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
+        else     gate_logits_kernel<true, false><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
+    } else {
+        if (vec) gate_logits_kernel<false, true><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
+        else     gate_logits_kernel<false, false><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
+    }
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -334,9 +407,10 @@ int launch_route_select(const float* partials, int n_chunks, const float* bias, 
     return B200_OK;
 }
 
-int launch_permute(const int* ids, int T, int K, int E, int* counts, int* offsets, int* row_pair,
-                   cudaStream_t stream) {
-    permute_kernel<<<E, 256, 0, stream>>>(ids, T * K, K, E, counts, offsets, row_pair);
+int launch_permute(const int* ids, int T, int K, int E, const int* counts_in, bool trusted, int* counts,
+                   int* offsets, int* row_pair, cudaStream_t stream) {
+    if (trusted) permute_kernel<false><<<E, 256, 0, stream>>>(ids, T * K, K, E, counts_in, counts, offsets, row_pair);
+    else         permute_kernel<true><<<E, 256, 0, stream>>>(ids, T * K, K, E, counts_in, counts, offsets, row_pair);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -406,7 +480,7 @@ int b200_moe_permute(b200_ws*, const int* expert_ids, int T, int K, int E, int* 
                      int* row_pair, b200_stream_t stream) {
     if (!expert_ids || !counts || !offsets || !row_pair) return B200_BAD_ARG;
     if (T <= 0 || K <= 0 || E <= 0) return B200_BAD_SHAPE;
-    return launch_permute(expert_ids, T, K, E, counts, offsets, row_pair, stream);
+    return launch_permute(expert_ids, T, K, E, nullptr, false, counts, offsets, row_pair, stream);
 }
 
 }  // extern "C"

@@ -142,3 +142,21 @@ def test_reference_test_driver_passes(b200, cuda):
     print(r.stdout[-2000:])
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "13 / 13 passed" in r.stdout
+
+
+def test_permute_counts_a_token_once_per_expert(b200, cuda):
+    """Ids supplied from outside may list an expert twice for a token; like the reference's gather
+    (kernels/moe/naive_moe.cu:156-161, `break` at the first match) the token then owns one row."""
+    rng = np.random.default_rng(21)
+    T, K, E = 70, 3, 5
+    ids = rng.integers(0, E, (T, K)).astype(np.int32)            # with repetitions inside a token
+    ids[3] = -1                                                   # and slots that select nothing
+    assert any(len(set(r)) < K for r in ids.tolist())
+    counts = torch.empty(E, dtype=torch.int32, device=cuda)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=cuda)
+    row_pair = torch.full((T * K,), -1, dtype=torch.int32, device=cuda)
+    b200.moe_permute(_dev(ids, cuda), T, K, E, counts, offsets, row_pair)
+    oc, oo, orp = oracle.permute(ids, E)
+    assert np.array_equal(counts.cpu().numpy(), oc)
+    assert np.array_equal(offsets.cpu().numpy(), oo)
+    assert np.array_equal(row_pair.cpu().numpy()[: oo[E]], orp)
