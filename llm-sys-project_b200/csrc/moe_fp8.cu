@@ -347,7 +347,7 @@ bool g_prof_created = false;
 long long g_prof_calls = 0;      // layer calls recorded since profiling was enabled
 
 struct Fp8Scratch {
-    float* partials; int* ids; float* wts; int* counts; int* offsets; int* row_pair;
+    float* partials; int* ids; float* wts; int* hist; int* counts; int* offsets; int* row_pair;
     uint8_t* sq; float* ss; int* row_tok; float* row_w; uint8_t* act_q; float* act_s;
 };
 
@@ -358,6 +358,7 @@ void carve_fp8(WsCarver& c, const b200_moe_fp8_config* cfg, bool with_route, Fp8
     s.partials = with_route ? c.take<float>((size_t)moe_gate_chunks((int)D, true) * T * E) : nullptr;
     s.ids = c.take<int>(TK);
     s.wts = c.take<float>(TK);
+    s.hist = c.take<int>(E);
     s.counts = c.take<int>(E);
     s.offsets = c.take<int>(E + 1);
     s.row_pair = c.take<int>(TK);
@@ -382,12 +383,13 @@ int check_fp8_cfg(const b200_moe_fp8_config* cfg) {
 
 // permute + sort + GEMM1 (+ GEMM2) on given routing
 int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float* xs, const int* ids,
-                const float* wts, const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s,
+                const float* wts, const int* hist, const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s,
                 float* out, const b200_moe_fp8_config* cfg, bool do_gemm2, cudaStream_t stream) {
     const int T = cfg->num_tokens, E = cfg->num_experts, K = cfg->top_k, D = cfg->hidden_dim,
               I = cfg->intermediate_dim;
     const long long TK = (long long)T * K;
-    int st = launch_permute(ids, T, K, E, s.counts, s.offsets, s.row_pair, stream);
+    // ids from this library's router are trusted (hist given); ids from outside get the duplicate check
+    int st = launch_permute(ids, T, K, E, hist, hist != nullptr, s.counts, s.offsets, s.row_pair, stream);
     if (st) return st;
     sort_rows_fp8_kernel<<<(unsigned)TK, 128, 0, stream>>>(xq, xs, s.row_pair, s.offsets, wts, E, K, D, s.sq, s.ss,
                                                            s.row_tok, s.row_w);
@@ -483,7 +485,7 @@ int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* xs, const 
     if (st) return st;
     WsCarver cv(ws->base);
     carve_fp8(cv, cfg, false, s);
-    return run_experts(ws, s, xq, xs, expert_ids, expert_w, w1q, w1s, w2q, w2s, out, cfg, true, stream);
+    return run_experts(ws, s, xq, xs, expert_ids, expert_w, nullptr, w1q, w1s, w2q, w2s, out, cfg, true, stream);
 }
 
 int b200_moe_fp8_forward(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w, const float* bias,
@@ -507,10 +509,11 @@ int b200_moe_fp8_forward(b200_ws* ws, const uint8_t* xq, const float* xs, const 
     const int nch = moe_gate_chunks(D, true);
     st = launch_gate_logits(xq, xs, gate_w, s.partials, T, E, D, true, stream);
     if (st) return st;
-    st = launch_route_select(s.partials, nch, bias, s.ids, s.wts, nullptr, nullptr, T, E, K, cfg->scoring,
+    B200_CUDA_TRY(cudaMemsetAsync(s.hist, 0, sizeof(int) * E, stream));
+    st = launch_route_select(s.partials, nch, bias, s.ids, s.wts, s.hist, nullptr, T, E, K, cfg->scoring,
                              cfg->n_group, cfg->topk_group, cfg->routed_scale, stream);
     if (st) return st;
-    return run_experts(ws, s, xq, xs, s.ids, s.wts, w1q, w1s, w2q, w2s, out, cfg, true, stream);
+    return run_experts(ws, s, xq, xs, s.ids, s.wts, s.hist, w1q, w1s, w2q, w2s, out, cfg, true, stream);
 }
 
 int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
@@ -534,7 +537,7 @@ int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const float* xs, co
     B200_CUDA_TRY(cudaMemsetAsync(dummy_w, 0, sizeof(float) * TK, stream));
     B200_CUDA_TRY(cudaMemsetAsync(s.act_q, 0, TK * cfg->intermediate_dim, stream));
     B200_CUDA_TRY(cudaMemsetAsync(s.act_s, 0, sizeof(float) * TK * (cfg->intermediate_dim / 128), stream));
-    st = run_experts(ws, s, xq, xs, expert_ids, dummy_w, w1q, w1s, nullptr, nullptr, nullptr, cfg, false, stream);
+    st = run_experts(ws, s, xq, xs, expert_ids, dummy_w, nullptr, w1q, w1s, nullptr, nullptr, nullptr, cfg, false, stream);
     if (st) return st;
     B200_CUDA_TRY(cudaMemcpyAsync(act_q, s.act_q, TK * cfg->intermediate_dim, cudaMemcpyDeviceToDevice, stream));
     B200_CUDA_TRY(cudaMemcpyAsync(act_s, s.act_s, sizeof(float) * TK * (cfg->intermediate_dim / 128),
