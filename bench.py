@@ -144,6 +144,7 @@ def build_moe(b200, torch, dev, world, rank):
     del x
     layer = b200.MoeFp8Layer(gate_w, bias, w1q, w1s, w2q, w2s, c["K"], b200.SCORE_SIGMOID_GROUPED, c["n_group"],
                              c["topk_group"], c["routed_scale"])
+    layer.pack()          # pre-tiled weights for the grouped GEMMs (the row-major copy stays for the CPU check)
     return layer, xq, xs
 
 

@@ -151,6 +151,22 @@ B200_API int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* x
                                   const float* expert_w, const uint8_t* w1q, const float* w1s,
                                   const uint8_t* w2q, const float* w2s, float* out,
                                   const b200_moe_fp8_config* cfg, b200_stream_t stream);
+/* Weight pre-tiling for the grouped GEMMs (no reference counterpart).  DRAM delivers random 128-byte
+ * pieces at well under half the rate of 1 KB+ contiguous pieces, and a row-major weight tile is made of
+ * 128-byte pieces 7 KB apart; the packed form stores each (expert, n tile, K block) tile as one
+ * contiguous 32 KB block.  which = 1: w1q [E,2I,D]; which = 2: w2q [E,D,I]; packed has the same size.
+ * Scales are unchanged.  The *_packed entry points take packed weights and are otherwise identical to
+ * b200_moe_fp8_forward / b200_moe_fp8_experts. */
+B200_API int b200_moe_fp8_pack_weights(int which, const uint8_t* src, uint8_t* packed, int E, int D, int I,
+                                       b200_stream_t stream);
+B200_API int b200_moe_fp8_forward_packed(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w,
+                                         const float* bias, const uint8_t* w1p, const float* w1s,
+                                         const uint8_t* w2p, const float* w2s, float* out,
+                                         const b200_moe_fp8_config* cfg, b200_stream_t stream);
+B200_API int b200_moe_fp8_experts_packed(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                                         const float* expert_w, const uint8_t* w1p, const float* w1s,
+                                         const uint8_t* w2p, const float* w2s, float* out,
+                                         const b200_moe_fp8_config* cfg, b200_stream_t stream);
 /* Stage access for parity tests: runs permute + GEMM1 and copies the requantised
  * activations of sorted rows out (act_q [rows,I], act_s [rows,I/128], rows = T*K upper bound). */
 B200_API int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,

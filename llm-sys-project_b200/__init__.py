@@ -49,7 +49,8 @@ EXPORTED_SYMBOLS = [
     "b200_moe_forward_f32", "b200_moe_gate_f32", "b200_moe_permute", "b200_moe_gather_f32", "b200_gemm_f32",
     "b200_swiglu_f32", "b200_moe_scatter_f32",
     "b200_quant_act_1x128", "b200_quant_weight_128x128", "b200_moe_route_fp8", "b200_moe_fp8_forward",
-    "b200_moe_fp8_experts", "b200_moe_fp8_gemm1_stage", "b200_moe_fp8_profile", "b200_moe_fp8_profile_read",
+    "b200_moe_fp8_experts", "b200_moe_fp8_pack_weights", "b200_moe_fp8_forward_packed",
+    "b200_moe_fp8_experts_packed", "b200_moe_fp8_gemm1_stage", "b200_moe_fp8_profile", "b200_moe_fp8_profile_read",
     "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
     "b200_dsa_softmax_f32", "b200_dsa_output_proj_f32",
     "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128", "b200_umma_selftest",
@@ -171,6 +172,24 @@ def moe_fp8_forward(xq, xs, gate_w, bias, w1q, w1s, w2q, w2s, out, cfg, stream=N
 def moe_fp8_experts(xq, xs, expert_ids, expert_w, w1q, w1s, w2q, w2s, out, cfg, stream=None):
     _check(lib().b200_moe_fp8_experts(None, _p(xq), _p(xs), _p(expert_ids), _p(expert_w), _p(w1q), _p(w1s),
                                       _p(w2q), _p(w2s), _p(out), C.byref(cfg), _stream(stream)), "moe_fp8_experts")
+
+
+def moe_fp8_pack_weights(which, src, packed, E, D, I, stream=None):
+    """which = 1: w1q [E,2I,D]; which = 2: w2q [E,D,I].  `packed` is a uint8 buffer of the same size."""
+    _check(lib().b200_moe_fp8_pack_weights(int(which), _p(src), _p(packed), E, D, I, _stream(stream)),
+           "moe_fp8_pack_weights")
+
+
+def moe_fp8_forward_packed(xq, xs, gate_w, bias, w1p, w1s, w2p, w2s, out, cfg, stream=None):
+    _check(lib().b200_moe_fp8_forward_packed(None, _p(xq), _p(xs), _p(gate_w), _p(bias), _p(w1p), _p(w1s), _p(w2p),
+                                             _p(w2s), _p(out), C.byref(cfg), _stream(stream)),
+           "moe_fp8_forward_packed")
+
+
+def moe_fp8_experts_packed(xq, xs, expert_ids, expert_w, w1p, w1s, w2p, w2s, out, cfg, stream=None):
+    _check(lib().b200_moe_fp8_experts_packed(None, _p(xq), _p(xs), _p(expert_ids), _p(expert_w), _p(w1p), _p(w1s),
+                                             _p(w2p), _p(w2s), _p(out), C.byref(cfg), _stream(stream)),
+           "moe_fp8_experts_packed")
 
 
 def moe_fp8_gemm1_stage(xq, xs, expert_ids, w1q, w1s, act_q, act_s, offsets, row_pair, cfg, stream=None):

@@ -31,7 +31,8 @@ constexpr int VCHUNK_BYTES = TKV * 128;            // 8192  (64 rows x 64 column
 constexpr int V_STAGE_BYTES = 4 * VCHUNK_BYTES;    // 32768
 constexpr int P_CHUNK_BYTES = HPC * 16;            // 1024
 constexpr int P_BYTES = 8 * P_CHUNK_BYTES;         // 8192
-constexpr int THREADS = 288;
+constexpr int THREADS = 320;                       // warps 0-3 softmax, 4 MMA/relay, 5-8 gather, 9 L2 prefetch
+constexpr int PF_TILES = 6;                        // how far ahead of the gather the L2 prefetch runs
 constexpr uint32_t O_COL = 0, S_COL = 256;
 
 struct Smem {
@@ -54,6 +55,7 @@ struct Smem {
     uint64_t mx_bar;                     // local, 128
     uint32_t tmem_base;
     int abort_flag;
+    int progress;                        // tile the gather producers are working on
     float xchg[2][128];
 };
 constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + 2 * K_STAGE_BYTES + 2 * V_STAGE_BYTES + P_BYTES + sizeof(Smem);
@@ -175,6 +177,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
         ptx::mbar_init(&sm->o_done, 1);
         ptx::mbar_init(&sm->mx_bar, 128);
         sm->abort_flag = 0;
+        sm->progress = 0;
         ptx::fence_mbar_init();
     }
     if (warp == 4) {
@@ -187,7 +190,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
     ptx::tc_fence_after();
     const uint32_t tmem = sm->tmem_base;
 
-    if (warp >= 5) {
+    if (warp == 9) {
+        // ===================== L2 prefetcher =====================
+        // The gather can keep at most two tiles in flight (shared memory is full), which is not enough to
+        // cover DRAM latency.  This warp runs PF_TILES ahead and pulls the rows the gather will ask for
+        // into L2 with bulk prefetches (whole 1 KB / 128 B / 256 B pieces, fire and forget).
+        volatile int* progress = &sm->progress;
+        for (int jj = 0; jj < nt; jj++) {
+            const uint64_t t0 = ptx::globaltimer_ns();
+            while (*progress + PF_TILES < jj) {
+                if (*abort_flag || ptx::globaltimer_ns() - t0 > B200_WAIT_LIMIT_NS) { jj = nt; break; }
+                __nanosleep(200);
+            }
+            if (jj >= nt) break;
+            const int* ids = p.idx + (size_t)b * p.S + (size_t)(t_begin + jj) * TKV;
+            const long long idk = ids[rank * KROWS + lane];
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kc + idk * DC), "r"(DC * 2) : "memory");
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kp + idk * DP), "r"(DP * 2) : "memory");
+#pragma unroll
+            for (int x = 0; x < 2; x++) {
+                const long long idv = ids[lane + 32 * x];
+                const __nv_bfloat16* vr = p.v + idv * DC + 128 * (int)rank;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vr), "r"(256) : "memory");
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vr + 256), "r"(256) : "memory");
+            }
+        }
+    } else if (warp >= 5) {
         // ===================== gather producers (128 threads per CTA) =====================
         const int pt = threadIdx.x - 160;
         // Q: this CTA's 64 heads x 72 sixteen-byte chunks; heads >= H are zero
@@ -231,6 +259,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
 #pragma unroll
             for (int x = 0; x < 16; x++) vid[x] = vid_n[x];
             load_ids(j + 1, kid_n, vid_n);
+            if (pt == 0) sm->progress = j;
             const int j16 = pt & 7;
             if (!ptx::mbar_wait(&sm->k_empty[st], par, abort_flag)) goto done;
 #pragma unroll

@@ -31,7 +31,7 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;            // 16384
 constexpr int B_BYTES = BN * BK;            // 32768
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int NUM_EPI_THREADS = 256;
+constexpr int NUM_EPI_WARPS = 8;             // one barrier arrival per warp, one polling lane per warp
 constexpr int GEMM_THREADS = 384;          // warpgroups 0,1: promotion/epilogue; warpgroup 2: TMA + MMA warps
 constexpr int MAX_E = 1024;
 
@@ -46,9 +46,13 @@ struct GemmSmem {
     int total_tiles;
     int tile_prefix[MAX_E + 1];
     float amax[2][2][BM];   // [tile parity][warpgroup][row]
+    alignas(16) float stage[8][32][20]; // per promotion warp: 32 rows x 16 columns (+4 pad) for the scatter-add transpose
 };
 
 constexpr size_t GEMM_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(GemmSmem);
+
+constexpr int TRACE_CAP = 512;
+long long* g_gemm_trace = nullptr;
 
 struct GemmParams {
     const float* a_scale;      // [rows, nkb]
@@ -61,6 +65,8 @@ struct GemmParams {
     float* out;                // MODE 2 out [T, D]
     int* status;
     int E, D, I;
+    long long* trace;          // optional timeline buffer [6][TRACE_CAP] of clock64 stamps of CTA 0 (debug aid)
+    int packed;                // weights pre-tiled: one contiguous 256 x 128-byte block per (expert, n tile, K block)
     long long total_rows;      // capacity of the sorted row buffers
 };
 
@@ -89,8 +95,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         for (int s = 0; s < STAGES; s++) { ptx::mbar_init(&sm->full[s], 1); ptx::mbar_init(&sm->empty[s], 1); }
         for (int a = 0; a < 2; a++) {
             ptx::mbar_init(&sm->tmem_full[a], 1);
-            ptx::mbar_init(&sm->tmem_empty[a], NUM_EPI_THREADS);
-            ptx::mbar_init(&sm->amax_bar[a], NUM_EPI_THREADS);
+            ptx::mbar_init(&sm->tmem_empty[a], NUM_EPI_WARPS);
+            ptx::mbar_init(&sm->amax_bar[a], NUM_EPI_WARPS);
         }
         sm->abort_flag = 0;
         int acc = 0;
@@ -143,7 +149,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       if (warp == 8) {
         // ===================== TMA producer =====================
         if (lane == 0) {
-            int s = 0; uint32_t ph = 0;
+            int s = 0; uint32_t ph = 0; int tr = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 int e, m_tile, n_tile, cnt;
                 locate(tile, e, m_tile, n_tile, cnt);
@@ -151,11 +157,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const long long wrow0 = (long long)e * w_rows;
                 for (int kb = 0; kb < nkb; kb++) {
                     if (!ptx::mbar_wait(&sm->empty[s], ph ^ 1, abort_flag)) goto done;
+                    if (p.trace && blockIdx.x == 0 && tr < TRACE_CAP) p.trace[0 * TRACE_CAP + tr++] = clock64();
                     uint8_t* a_dst = tiles + (size_t)s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
                     ptx::mbar_expect_tx(&sm->full[s], STAGE_BYTES);
                     ptx::tma_load_2d(a_dst, &tmap_a, &sm->full[s], kb * BK, row0);
-                    if (MODE == 1) {
+                    if (p.packed) {
+                        // the tile's K block is one contiguous 32 KB piece of the packed weights
+                        ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], 0, (((e * NT + n_tile) * nkb) + kb) * BN);
+                    } else if (MODE == 1) {
                         // accumulator columns: [gate j0..+63 | up j0..+63 | gate j0+64..+127 | up j0+64..+127]
                         const int j0 = n_tile * 128;
                         ptx::tma_load_2d(b_dst + 0 * 8192, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + j0));
@@ -175,11 +185,13 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::make_idesc(0, 0, 0, 0, BM, BN);
             int s = 0; uint32_t ph = 0;
-            int acc = 0; uint32_t acc_ph = 0;
+            int acc = 0; uint32_t acc_ph = 0; int tr = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 for (int kb = 0; kb < nkb; kb++) {
                     if (!ptx::mbar_wait(&sm->tmem_empty[acc], acc_ph ^ 1, abort_flag)) goto done;
+                    if (p.trace && blockIdx.x == 0 && tr < TRACE_CAP) p.trace[1 * TRACE_CAP + tr] = clock64();
                     if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
+                    if (p.trace && blockIdx.x == 0 && tr < TRACE_CAP) p.trace[2 * TRACE_CAP + tr++] = clock64();
                     ptx::tc_fence_after();
                     const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
                     const uint32_t b_addr = a_addr + A_BYTES;
@@ -201,17 +213,27 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     } else {
         // ===================== promotion + epilogue (warps 0-7) =====================
         ptx::setmaxnreg_inc<232>();
+        // one lane polls the barrier, the warp follows (256 pollers and 256 arrivals per K block on one
+        // shared-memory word cost more than the promotion itself)
+        auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+            int ok = 1;
+            if (lane == 0) ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();
+            return ok != 0;
+        };
         const int wg = warp >> 2;                         // column half of the accumulator
         const int row = (warp & 3) * 32 + lane;           // TMEM lane = tile row
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         int acc = 0; uint32_t acc_ph = 0;
-        int tile_par = 0; uint32_t amax_ph[2] = {0, 0};
+        int tile_par = 0; uint32_t amax_ph[2] = {0, 0}; int tr = 0;
         const int nkb_w = Kdim / 128;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             int e, m_tile, n_tile, cnt;
             locate(tile, e, m_tile, n_tile, cnt);
             const long long grow = (long long)p.offsets[e] + m_tile * BM + row;   // sorted row
             const bool row_ok = (m_tile * BM + row) < cnt;
+            const bool warp_valid = (m_tile * BM + (warp & 3) * 32) < cnt;    // any valid row in this warp's 32
             const float* a_sc = p.a_scale + (grow < p.total_rows ? grow : 0) * nkb;
             const float* w_sc0;
             const float* w_sc1;
@@ -238,7 +260,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     w0_n = w_sc0[kb + 1];
                     w1_n = w_sc1[kb + 1];
                 }
-                if (!ptx::mbar_wait(&sm->tmem_full[acc], acc_ph, abort_flag)) goto done;
+                if (!warp_wait(&sm->tmem_full[acc], acc_ph)) goto done;
+                const bool trc = p.trace && blockIdx.x == 0 && threadIdx.x == 0 && tr < TRACE_CAP;
+                if (trc) p.trace[3 * TRACE_CAP + tr] = clock64();
                 ptx::tc_fence_after();
                 const uint32_t t0 = tmem_base + lane_addr + acc * BN + wg * 128;
                 uint32_t ra[32], rb[32];
@@ -253,39 +277,47 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 ptx::tmem_ld_32x32(t0 + 96, rb);
                 ptx::tc_wait_ld();
                 ptx::tc_fence_before();
-                ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
+                if (trc) p.trace[4 * TRACE_CAP + tr] = clock64();
 #pragma unroll
                 for (int i = 0; i < 32; i++) accv[64 + i] += __uint_as_float(ra[i]) * s1;
 #pragma unroll
                 for (int i = 0; i < 32; i++) accv[96 + i] += __uint_as_float(rb[i]) * s1;
+                if (trc) p.trace[5 * TRACE_CAP + tr] = clock64();
+                tr++;
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
 
             if (MODE == 1) {
-                // SwiGLU on 64 activation columns, 1x128 requantisation shared with the other warpgroup
+                // SwiGLU on 64 activation columns, 1x128 requantisation shared with the other warpgroup.
+                // Fast exp / reciprocal: the result is rounded to e4m3 next, an ulp of fp32 does not matter.
                 float amax = 0.0f;
+                if (warp_valid) {
 #pragma unroll
-                for (int i = 0; i < 64; i++) {
-                    float g = accv[i], u = accv[64 + i];
-                    float a = __fdiv_rn(g, 1.0f + expf(-g)) * u;
-                    accv[i] = a;
-                    amax = fmaxf(amax, fabsf(a));
+                    for (int i = 0; i < 64; i++) {
+                        const float g = accv[i], u = accv[64 + i];
+                        const float a = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        accv[i] = a;
+                        amax = fmaxf(amax, fabsf(a));
+                    }
                 }
                 sm->amax[tile_par][wg][row] = amax;
-                ptx::mbar_arrive(&sm->amax_bar[tile_par]);
-                if (!ptx::mbar_wait(&sm->amax_bar[tile_par], amax_ph[tile_par], abort_flag)) goto done;
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&sm->amax_bar[tile_par]);
+                if (!warp_wait(&sm->amax_bar[tile_par], amax_ph[tile_par])) goto done;
                 amax_ph[tile_par] ^= 1;
                 amax = fmaxf(amax, sm->amax[tile_par][wg ^ 1][row]);
-                const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
                 if (row_ok) {
+                    const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+                    const float inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 1.0f;
                     uint32_t packed[16];
 #pragma unroll
                     for (int i = 0; i < 16; i++) {
                         uint32_t wv = 0;
 #pragma unroll
                         for (int b = 0; b < 4; b++) {
-                            uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(accv[i * 4 + b], scale),
-                                                                         __NV_SATFINITE, __NV_E4M3);
+                            uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(accv[i * 4 + b] * inv, __NV_SATFINITE, __NV_E4M3);
                             wv |= q << (8 * b);
                         }
                         packed[i] = wv;
@@ -297,15 +329,31 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     if (wg == 0) p.act_s[grow * (p.I / 128) + n_tile] = scale;
                 }
                 tile_par ^= 1;
-            } else {
-                if (row_ok) {
-                    const int tok = p.row_tok[grow];
-                    const float w = p.row_w[grow];
-                    float* dst = p.out + (size_t)tok * p.D + n_tile * 256 + wg * 128;
+            } else if (warp_valid) {
+                // out[token] += w * acc.  The accumulator row of a lane is transposed through shared memory
+                // 16 columns at a time so that one red instruction covers 8 rows x 64 contiguous bytes
+                // instead of 32 rows x 16 bytes (4 times fewer memory requests).
+                const int tok = row_ok ? p.row_tok[grow] : -1;
+                const float w = row_ok ? p.row_w[grow] : 0.0f;
+                float (*st)[20] = sm->stage[warp];
+                float* const out_col = p.out + n_tile * 256 + wg * 128;
+                const int sub_row = lane >> 2, seg = lane & 3;
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        red_add_v4(dst + 4 * i, w * accv[4 * i], w * accv[4 * i + 1], w * accv[4 * i + 2],
-                                   w * accv[4 * i + 3]);
+                for (int pass = 0; pass < 8; pass++) {
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        *reinterpret_cast<float4*>(&st[lane][q * 4]) =
+                            make_float4(w * accv[pass * 16 + q * 4], w * accv[pass * 16 + q * 4 + 1],
+                                        w * accv[pass * 16 + q * 4 + 2], w * accv[pass * 16 + q * 4 + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (int k = 0; k < 4; k++) {
+                        const int r = 8 * k + sub_row;
+                        const int tok_r = __shfl_sync(0xffffffffu, tok, r);
+                        const float4 v = *reinterpret_cast<const float4*>(&st[r][seg * 4]);
+                        if (tok_r >= 0) red_add_v4(out_col + (size_t)tok_r * p.D + pass * 16 + seg * 4, v.x, v.y, v.z, v.w);
+                    }
                 }
             }
         }
@@ -346,6 +394,30 @@ cudaEvent_t g_prof_ev[PROF_SLOTS][4];
 bool g_prof_created = false;
 long long g_prof_calls = 0;      // layer calls recorded since profiling was enabled
 
+__global__ void pack_weights_kernel(int which, const uint8_t* __restrict__ src, uint8_t* __restrict__ packed, int E,
+                                    int D, int I, long long chunks) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= chunks) return;
+    const int Kdim = which == 1 ? D : I;
+    const int nkb = Kdim / 128;
+    const int NT = which == 1 ? I / 128 : D / 256;
+    const int c16 = (int)(i & 7);
+    const int r = (int)((i >> 3) & 255);
+    long long t = i >> 11;
+    const int kb = (int)(t % nkb); t /= nkb;
+    const int nt = (int)(t % NT);
+    const int e = (int)(t / NT);
+    long long row;
+    if (which == 1) {
+        const int j0 = nt * 128, q = r >> 6, rr = r & 63;
+        row = (long long)e * 2 * I + ((q & 1) ? I : 0) + j0 + ((q >> 1) ? 64 : 0) + rr;
+    } else {
+        row = (long long)e * D + nt * 256 + r;
+    }
+    const uint4 v = *reinterpret_cast<const uint4*>(src + row * Kdim + (long long)kb * 128 + c16 * 16);
+    *reinterpret_cast<uint4*>(packed + i * 16) = v;
+}
+
 struct Fp8Scratch {
     float* partials; int* ids; float* wts; int* hist; int* counts; int* offsets; int* row_pair;
     uint8_t* sq; float* ss; int* row_tok; float* row_w; uint8_t* act_q; float* act_s;
@@ -384,7 +456,7 @@ int check_fp8_cfg(const b200_moe_fp8_config* cfg) {
 // permute + sort + GEMM1 (+ GEMM2) on given routing
 int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float* xs, const int* ids,
                 const float* wts, const int* hist, const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s,
-                float* out, const b200_moe_fp8_config* cfg, bool do_gemm2, cudaStream_t stream) {
+                float* out, const b200_moe_fp8_config* cfg, bool do_gemm2, bool packed, cudaStream_t stream) {
     const int T = cfg->num_tokens, E = cfg->num_experts, K = cfg->top_k, D = cfg->hidden_dim,
               I = cfg->intermediate_dim;
     const long long TK = (long long)T * K;
@@ -406,12 +478,15 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     }
     CUtensorMap ta, tb;
     GemmParams p{};
+    p.trace = g_gemm_trace;
     p.offsets = s.offsets; p.E = E; p.D = D; p.I = I; p.status = ws->d_status; p.total_rows = TK;
 
     // GEMM1
     st = b200_make_tmap_u8_sw128(&ta, s.sq, (unsigned long long)TK, D, 128);
     if (st) return st;
-    st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, 64);
+    p.packed = packed ? 1 : 0;
+    if (packed) st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I * (D / 128), 128, 256);
+    else        st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, 64);
     if (st) return st;
     p.a_scale = s.ss; p.w_scale = w1s; p.act_q = s.act_q; p.act_s = s.act_s;
     if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][0], stream));
@@ -424,8 +499,10 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     // GEMM2
     st = b200_make_tmap_u8_sw128(&ta, s.act_q, (unsigned long long)TK, I, 128);
     if (st) return st;
-    st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D, I, 256);
+    if (packed) st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D * (I / 128), 128, 256);
+    else        st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D, I, 256);
     if (st) return st;
+    if (p.trace) p.trace += 6 * TRACE_CAP;      // second half of the buffer for GEMM2
     p.a_scale = s.act_s; p.w_scale = w2s; p.row_tok = s.row_tok; p.row_w = s.row_w; p.out = out;
     B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)T * D, stream));
     if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][2], stream));
@@ -439,6 +516,9 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
 }  // namespace
 
 extern "C" {
+
+// Debug aid (not in the public header): timeline stamps of CTA 0 of the next grouped GEMM launches.
+__attribute__((visibility("default"))) void b200_debug_gemm_trace(long long* dev_buf) { g_gemm_trace = dev_buf; }
 
 int b200_moe_fp8_profile(int enable) {
     if (enable && !g_prof_created) {
@@ -470,9 +550,10 @@ int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms, int* calls) {
     return B200_OK;
 }
 
-int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
-                         const float* expert_w, const uint8_t* w1q, const float* w1s, const uint8_t* w2q,
-                         const float* w2s, float* out, const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+static int experts_impl(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                        const float* expert_w, const uint8_t* w1q, const float* w1s, const uint8_t* w2q,
+                        const float* w2s, float* out, const b200_moe_fp8_config* cfg, bool packed,
+                        b200_stream_t stream) {
     int st = check_fp8_cfg(cfg);
     if (st) return st;
     if (!xq || !xs || !expert_ids || !expert_w || !w1q || !w1s || !w2q || !w2s || !out) return B200_BAD_ARG;
@@ -485,12 +566,24 @@ int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* xs, const 
     if (st) return st;
     WsCarver cv(ws->base);
     carve_fp8(cv, cfg, false, s);
-    return run_experts(ws, s, xq, xs, expert_ids, expert_w, nullptr, w1q, w1s, w2q, w2s, out, cfg, true, stream);
+    return run_experts(ws, s, xq, xs, expert_ids, expert_w, nullptr, w1q, w1s, w2q, w2s, out, cfg, true, packed, stream);
 }
 
-int b200_moe_fp8_forward(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w, const float* bias,
-                         const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s, float* out,
-                         const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                         const float* expert_w, const uint8_t* w1q, const float* w1s, const uint8_t* w2q,
+                         const float* w2s, float* out, const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+    return experts_impl(ws, xq, xs, expert_ids, expert_w, w1q, w1s, w2q, w2s, out, cfg, false, stream);
+}
+
+int b200_moe_fp8_experts_packed(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                                const float* expert_w, const uint8_t* w1p, const float* w1s, const uint8_t* w2p,
+                                const float* w2s, float* out, const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+    return experts_impl(ws, xq, xs, expert_ids, expert_w, w1p, w1s, w2p, w2s, out, cfg, true, stream);
+}
+
+static int forward_impl(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w, const float* bias,
+                        const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s, float* out,
+                        const b200_moe_fp8_config* cfg, bool packed, b200_stream_t stream) {
     int st = check_fp8_cfg(cfg);
     if (st) return st;
     if (!xq || !xs || !gate_w || !w1q || !w1s || !w2q || !w2s || !out) return B200_BAD_ARG;
@@ -513,7 +606,38 @@ int b200_moe_fp8_forward(b200_ws* ws, const uint8_t* xq, const float* xs, const 
     st = launch_route_select(s.partials, nch, bias, s.ids, s.wts, s.hist, nullptr, T, E, K, cfg->scoring,
                              cfg->n_group, cfg->topk_group, cfg->routed_scale, stream);
     if (st) return st;
-    return run_experts(ws, s, xq, xs, s.ids, s.wts, s.hist, w1q, w1s, w2q, w2s, out, cfg, true, stream);
+    return run_experts(ws, s, xq, xs, s.ids, s.wts, s.hist, w1q, w1s, w2q, w2s, out, cfg, true, packed, stream);
+}
+
+int b200_moe_fp8_forward(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w, const float* bias,
+                         const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s, float* out,
+                         const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+    return forward_impl(ws, xq, xs, gate_w, bias, w1q, w1s, w2q, w2s, out, cfg, false, stream);
+}
+
+int b200_moe_fp8_forward_packed(b200_ws* ws, const uint8_t* xq, const float* xs, const float* gate_w,
+                                const float* bias, const uint8_t* w1p, const float* w1s, const uint8_t* w2p,
+                                const float* w2s, float* out, const b200_moe_fp8_config* cfg, b200_stream_t stream) {
+    return forward_impl(ws, xq, xs, gate_w, bias, w1p, w1s, w2p, w2s, out, cfg, true, stream);
+}
+
+// Weight pre-tiling.  which = 1: w1 [E,2I,D] -> tiles of 256 accumulator rows (gate j0..+63, up j0..+63,
+// gate j0+64..+127, up j0+64..+127 for j0 = 128 * n_tile); which = 2: w2 [E,D,I] -> tiles of 256 rows.
+// packed[(((e * NT + n_tile) * nkb + kb) * 256 + r) * 128 + b] = src[e][row(n_tile, r)][kb * 128 + b].
+int b200_moe_fp8_pack_weights(int which, const uint8_t* src, uint8_t* packed, int E, int D, int I,
+                              b200_stream_t stream) {
+    if (!src || !packed) return B200_BAD_ARG;
+    if (which != 1 && which != 2) return B200_BAD_ARG;
+    if (E <= 0 || D <= 0 || I <= 0 || D % 256 || I % 128) return B200_BAD_SHAPE;
+    const int Kdim = which == 1 ? D : I;
+    const int NT = which == 1 ? I / 128 : D / 256;
+    const long long chunks = (long long)E * NT * (Kdim / 128) * 256 * 8;     // 16-byte chunks
+    long long blocks = (chunks + 255) / 256;
+    if (blocks > 0x7fffffffLL) return B200_UNSUPPORTED;
+    pack_weights_kernel<<<(unsigned)blocks, 256, 0, stream>>>(which, src, packed, E, D, I, chunks);
+    b200_count_launch(1);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
 }
 
 int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
@@ -537,7 +661,7 @@ int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const float* xs, co
     B200_CUDA_TRY(cudaMemsetAsync(dummy_w, 0, sizeof(float) * TK, stream));
     B200_CUDA_TRY(cudaMemsetAsync(s.act_q, 0, TK * cfg->intermediate_dim, stream));
     B200_CUDA_TRY(cudaMemsetAsync(s.act_s, 0, sizeof(float) * TK * (cfg->intermediate_dim / 128), stream));
-    st = run_experts(ws, s, xq, xs, expert_ids, dummy_w, nullptr, w1q, w1s, nullptr, nullptr, nullptr, cfg, false, stream);
+    st = run_experts(ws, s, xq, xs, expert_ids, dummy_w, nullptr, w1q, w1s, nullptr, nullptr, nullptr, cfg, false, false, stream);
     if (st) return st;
     B200_CUDA_TRY(cudaMemcpyAsync(act_q, s.act_q, TK * cfg->intermediate_dim, cudaMemcpyDeviceToDevice, stream));
     B200_CUDA_TRY(cudaMemcpyAsync(act_s, s.act_s, sizeof(float) * TK * (cfg->intermediate_dim / 128),

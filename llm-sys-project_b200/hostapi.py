@@ -4,7 +4,7 @@ brings the result back (the end-to-end path the benchmark times)."""
 import torch
 
 from . import (DsaConfig, MoeFp8Config, SCORE_SIGMOID_GROUPED, dsa_forward_bf16, moe_fp8_experts,
-               moe_fp8_forward, moe_route_fp8)
+               moe_fp8_experts_packed, moe_fp8_forward, moe_fp8_forward_packed, moe_fp8_pack_weights, moe_route_fp8)
 
 
 class MoeFp8Layer:
@@ -18,7 +18,21 @@ class MoeFp8Layer:
         self.I = w2q.shape[-1]
         self.K = top_k
         self.scoring, self.n_group, self.topk_group, self.routed_scale = scoring, n_group, topk_group, routed_scale
+        self.w1p = self.w2p = None
         self._dev = {}
+
+    def pack(self, free_unpacked=False):
+        """Pre-tile the weights (one contiguous 32 KB block per tile and K block) so the grouped GEMMs
+        stream them at full DRAM rate.  One-time cost; the results do not change."""
+        E_local = self.w1q.shape[0]
+        self.w1p = torch.empty_like(self.w1q)
+        self.w2p = torch.empty_like(self.w2q)
+        moe_fp8_pack_weights(1, self.w1q, self.w1p, E_local, self.D, self.I)
+        moe_fp8_pack_weights(2, self.w2q, self.w2p, E_local, self.D, self.I)
+        if free_unpacked:
+            torch.cuda.current_stream().synchronize()
+            self.w1q = self.w2q = None
+        return self
 
     def cfg(self, T, E=None, K=None):
         return MoeFp8Config(T, self.E if E is None else E, self.K if K is None else K, self.D, self.I, self.scoring,
@@ -28,7 +42,11 @@ class MoeFp8Layer:
         T = xq.shape[0]
         if out is None:
             out = torch.empty((T, self.D), dtype=torch.float32, device=xq.device)
-        moe_fp8_forward(xq, xs, self.gate_w, self.bias, self.w1q, self.w1s, self.w2q, self.w2s, out, self.cfg(T))
+        if self.w1p is not None:
+            moe_fp8_forward_packed(xq, xs, self.gate_w, self.bias, self.w1p, self.w1s, self.w2p, self.w2s, out,
+                                   self.cfg(T))
+        else:
+            moe_fp8_forward(xq, xs, self.gate_w, self.bias, self.w1q, self.w1s, self.w2q, self.w2s, out, self.cfg(T))
         return out
 
     def route(self, xq, xs):
@@ -43,9 +61,13 @@ class MoeFp8Layer:
         re[r] and is scaled by rw[r] (one slot per row)."""
         R = rq.shape[0]
         y = torch.empty((R, self.D), dtype=torch.float32, device=rq.device)
-        E_local = self.w1q.shape[0]
-        moe_fp8_experts(rq, rs, re.reshape(R, 1), rw.reshape(R, 1), self.w1q, self.w1s, self.w2q, self.w2s, y,
-                        self.cfg(R, E=E_local, K=1))
+        E_local = self.w1s.shape[0]
+        if self.w1p is not None:
+            moe_fp8_experts_packed(rq, rs, re.reshape(R, 1), rw.reshape(R, 1), self.w1p, self.w1s, self.w2p, self.w2s, y,
+                                   self.cfg(R, E=E_local, K=1))
+        else:
+            moe_fp8_experts(rq, rs, re.reshape(R, 1), rw.reshape(R, 1), self.w1q, self.w1s, self.w2q, self.w2s, y,
+                            self.cfg(R, E=E_local, K=1))
         return y
 
     def forward_host(self, xq_host, xs_host, out_host):

@@ -163,3 +163,34 @@ def test_fp8_bad_shapes(b200, cuda):
     with pytest.raises(b200.B200Error) as ei:
         b200.moe_fp8_forward(t, f, f, f, t, f, t, f, f, b200.MoeFp8Config(4, 4, 2, 200, 128, 1, 1, 1, 1.0))
     assert ei.value.status == b200.B200_BAD_SHAPE
+
+
+def test_packed_weights_layout_and_equivalence(b200, cuda):
+    """Pre-tiled weights: the layout is what the header states, and the layer gives the same result."""
+    rng = np.random.default_rng(9)
+    T, E, K, D, I = 150, 4, 2, 512, 256
+    x, wg, bias, w1, w2, xq, xs, w1q, w1s, w2q, w2s = _layer(rng, T, E, D, I)
+    d = {k: _dev(v, cuda) for k, v in dict(xq=xq, xs=xs, wg=wg, bias=bias, w1q=w1q, w1s=w1s, w2q=w2q, w2s=w2s).items()}
+    w1p, w2p = torch.empty_like(d["w1q"]), torch.empty_like(d["w2q"])
+    b200.moe_fp8_pack_weights(1, d["w1q"], w1p, E, D, I)
+    b200.moe_fp8_pack_weights(2, d["w2q"], w2p, E, D, I)
+    # layout: [e][n tile][K block][256 rows][128 bytes]
+    p1 = w1p.cpu().numpy().reshape(E, I // 128, D // 128, 256, 128)
+    e, nt, kb = 2, 1, 3
+    j0 = nt * 128
+    rows = np.concatenate([np.arange(j0, j0 + 64), I + np.arange(j0, j0 + 64), np.arange(j0 + 64, j0 + 128),
+                           I + np.arange(j0 + 64, j0 + 128)])
+    assert np.array_equal(p1[e, nt, kb], w1q[e][rows][:, kb * 128:(kb + 1) * 128])
+    p2 = w2p.cpu().numpy().reshape(E, D // 256, I // 128, 256, 128)
+    assert np.array_equal(p2[3, 1, 1], w2q[3][256:512, 128:256])
+    cfg = b200.MoeFp8Config(T, E, K, D, I, b200.SCORE_SIGMOID_GROUPED, 2, 1, 2.5)
+    out_a = torch.empty((T, D), dtype=torch.float32, device=cuda)
+    out_b = torch.empty_like(out_a)
+    b200.moe_fp8_forward(d["xq"], d["xs"], d["wg"], d["bias"], d["w1q"], d["w1s"], d["w2q"], d["w2s"], out_a, cfg)
+    b200.moe_fp8_forward_packed(d["xq"], d["xs"], d["wg"], d["bias"], w1p, d["w1s"], w2p, d["w2s"], out_b, cfg)
+    torch.cuda.synchronize()
+    assert b200.device_status() == 0
+    assert torch.allclose(out_a, out_b, rtol=1e-5, atol=1e-6)      # same products, scatter-add order may differ
+    ids, wts = oracle.route_grouped(xq, xs, wg, bias, K, 2, 1, 2.5)
+    ref = oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, ids, wts, np.arange(T, dtype=np.int32))
+    assert not (np.abs(out_b.cpu().numpy() - ref) > ATOL + RTOL * np.abs(ref)).any()
