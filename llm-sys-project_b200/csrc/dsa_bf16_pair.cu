@@ -4,7 +4,8 @@
 // re-cut so that a 64-row tile of selected K/V rows can be double-buffered next to a resident Q:
 // two CTAs of a cluster work on one (query, row-range) item.  Every MMA spans the pair:
 //     S[128 heads, 64 rows]   = Q * K_tile^T        M = 128 (64 heads per CTA), N = 64 (32 rows per CTA)
-//     O[128 heads, 512 cols] += P * V_tile          two MMAs of N = 256 (128 columns per CTA each)
+//     O[128 heads, 512 cols] += P * V_tile          two MMAs of N = 256 (128 columns per CTA each; CTA r
+//                                                   supplies and owns output columns [256 r, 256 r + 256))
 // so each CTA keeps only its 64 heads of Q (72 KB), gathers only half of the K rows (32 x 1152 B) and
 // half of the V columns (64 x 512 B) per tile, and nothing is computed or fetched twice.
 // TMEM per CTA: O 256 columns (lanes 0-63: first 128 columns of each 256-wide MMA, lanes 64-127: the
@@ -31,8 +32,7 @@ constexpr int VCHUNK_BYTES = TKV * 128;            // 8192  (64 rows x 64 column
 constexpr int V_STAGE_BYTES = 4 * VCHUNK_BYTES;    // 32768
 constexpr int P_CHUNK_BYTES = HPC * 16;            // 1024
 constexpr int P_BYTES = 8 * P_CHUNK_BYTES;         // 8192
-constexpr int THREADS = 320;                       // warps 0-3 softmax, 4 MMA/relay, 5-8 gather, 9 L2 prefetch
-constexpr int PF_TILES = 6;                        // how far ahead of the gather the L2 prefetch runs
+constexpr int THREADS = 288;                       // warps 0-3 softmax, 4 MMA/relay, 5-8 gather
 constexpr uint32_t O_COL = 0, S_COL = 256;
 
 struct Smem {
@@ -55,7 +55,6 @@ struct Smem {
     uint64_t mx_bar;                     // local, 128
     uint32_t tmem_base;
     int abort_flag;
-    int progress;                        // tile the gather producers are working on
     float xchg[2][128];
 };
 constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + 2 * K_STAGE_BYTES + 2 * V_STAGE_BYTES + P_BYTES + sizeof(Smem);
@@ -177,7 +176,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
         ptx::mbar_init(&sm->o_done, 1);
         ptx::mbar_init(&sm->mx_bar, 128);
         sm->abort_flag = 0;
-        sm->progress = 0;
         ptx::fence_mbar_init();
     }
     if (warp == 4) {
@@ -190,32 +188,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
     ptx::tc_fence_after();
     const uint32_t tmem = sm->tmem_base;
 
-    if (warp == 9) {
-        // ===================== L2 prefetcher =====================
-        // The gather can keep at most two tiles in flight (shared memory is full), which is not enough to
-        // cover DRAM latency.  This warp runs PF_TILES ahead and pulls the rows the gather will ask for
-        // into L2 with bulk prefetches (whole 1 KB / 128 B / 256 B pieces, fire and forget).
-        volatile int* progress = &sm->progress;
-        for (int jj = 0; jj < nt; jj++) {
-            const uint64_t t0 = ptx::globaltimer_ns();
-            while (*progress + PF_TILES < jj) {
-                if (*abort_flag || ptx::globaltimer_ns() - t0 > B200_WAIT_LIMIT_NS) { jj = nt; break; }
-                __nanosleep(200);
-            }
-            if (jj >= nt) break;
-            const int* ids = p.idx + (size_t)b * p.S + (size_t)(t_begin + jj) * TKV;
-            const long long idk = ids[rank * KROWS + lane];
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kc + idk * DC), "r"(DC * 2) : "memory");
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kp + idk * DP), "r"(DP * 2) : "memory");
-#pragma unroll
-            for (int x = 0; x < 2; x++) {
-                const long long idv = ids[lane + 32 * x];
-                const __nv_bfloat16* vr = p.v + idv * DC + 128 * (int)rank;
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vr), "r"(256) : "memory");
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(vr + 256), "r"(256) : "memory");
-            }
-        }
-    } else if (warp >= 5) {
+    if (warp >= 5) {
         // ===================== gather producers (128 threads per CTA) =====================
         const int pt = threadIdx.x - 160;
         // Q: this CTA's 64 heads x 72 sixteen-byte chunks; heads >= H are zero
@@ -239,53 +212,71 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
         // Row ids of the next tile are fetched one tile ahead; the copies of a unit signal its
         // barrier by themselves when they land, so this thread never waits for data and up to two
         // whole tiles (both stages) are in flight.
-        auto load_ids = [&](int j, long long (&k2)[2], long long (&v16)[16]) {
+        // DRAM serves 1 KB of a row fetched in one go at more than twice the rate of the same bytes
+        // fetched as scattered 128-byte pieces, so a warp instruction always covers 512 contiguous bytes
+        // of one row and the two halves of a Kc row are issued back to back.  Warp w of the four gather
+        // warps owns K rows 8w..8w+7 and V rows w, w+4, ...; row ids are fetched one tile ahead.
+        const int gw = pt >> 5;                                   // gather warp 0..3
+        auto load_ids = [&](int j, long long (&k8)[8], long long (&kp2)[2], long long (&v16)[16]) {
             if (j < nt) {
                 const int* ids = p.idx + (size_t)b * p.S + (size_t)(t_begin + j) * TKV;
-                k2[0] = ids[rank * KROWS + (pt >> 3)];
-                k2[1] = ids[rank * KROWS + (pt >> 3) + 16];
 #pragma unroll
-                for (int x = 0; x < 16; x++) v16[x] = ids[(pt >> 5) + 4 * x];
+                for (int x = 0; x < 8; x++) k8[x] = ids[rank * KROWS + 8 * gw + x];
+                kp2[0] = ids[rank * KROWS + 8 * gw + (lane >> 3)];
+                kp2[1] = ids[rank * KROWS + 8 * gw + (lane >> 3) + 4];
+#pragma unroll
+                for (int x = 0; x < 16; x++) v16[x] = ids[gw + 4 * x];
             }
         };
-        long long kid[2] = {0, 0}, vid[16], kid_n[2] = {0, 0}, vid_n[16];
+        long long kid[8], kpid[2] = {0, 0}, vid[16], kid_n[8], kpid_n[2] = {0, 0}, vid_n[16];
 #pragma unroll
         for (int x = 0; x < 16; x++) { vid[x] = 0; vid_n[x] = 0; }
-        load_ids(0, kid_n, vid_n);
+#pragma unroll
+        for (int x = 0; x < 8; x++) { kid[x] = 0; kid_n[x] = 0; }
+        load_ids(0, kid_n, kpid_n, vid_n);
         for (int j = 0; j < nt; j++) {
             const int st = j & 1;
             const uint32_t par = (uint32_t)(((j >> 1) & 1) ^ 1);
-            kid[0] = kid_n[0]; kid[1] = kid_n[1];
+#pragma unroll
+            for (int x = 0; x < 8; x++) kid[x] = kid_n[x];
+            kpid[0] = kpid_n[0]; kpid[1] = kpid_n[1];
 #pragma unroll
             for (int x = 0; x < 16; x++) vid[x] = vid_n[x];
-            load_ids(j + 1, kid_n, vid_n);
-            if (pt == 0) sm->progress = j;
-            const int j16 = pt & 7;
+            load_ids(j + 1, kid_n, kpid_n, vid_n);
             if (!ptx::mbar_wait(&sm->k_empty[st], par, abort_flag)) goto done;
+            {
+                const uint32_t kst = ptx::smem_u32(sK) + st * K_STAGE_BYTES;
+                // Kc: row r = 8 gw + x, 16-byte chunk ch = lane (+32): slot ch/8, position (ch%8) ^ (r%8)
 #pragma unroll
-            for (int c = 0; c < KBLK; c++) {
-                const uint32_t slot = ptx::smem_u32(sK) + st * K_STAGE_BYTES + c * KSLOT_BYTES;
+                for (int x = 0; x < 8; x++) {
+                    const int r = 8 * gw + x;
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        const int ch = lane + 32 * hf;
+                        ptx::cp_async_16(kst + (ch >> 3) * KSLOT_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4),
+                                         p.kc + kid[x] * DC + ch * 8);
+                    }
+                }
+                // Kp (128 bytes per row, slot 8): four rows per instruction
 #pragma unroll
                 for (int x = 0; x < 2; x++) {
-                    const int r = (pt >> 3) + 16 * x;
-                    const __nv_bfloat16* src = (c < 8) ? p.kc + kid[x] * DC + c * 64 + j16 * 8
-                                                       : p.kp + kid[x] * DP + j16 * 8;
-                    ptx::cp_async_16(slot + r * 128 + ((j16 ^ (r & 7)) << 4), src);
+                    const int r = 8 * gw + (lane >> 3) + 4 * x, j16 = lane & 7;
+                    ptx::cp_async_16(kst + 8 * KSLOT_BYTES + r * 128 + ((j16 ^ (r & 7)) << 4), p.kp + kpid[x] * DP + j16 * 8);
                 }
             }
             ptx::cp_async_arrive_noinc(&sm->k_full[st]);
             {
                 if (!ptx::mbar_wait(&sm->v_empty[st], par, abort_flag)) goto done;
                 const uint32_t vbase = ptx::smem_u32(sV) + st * V_STAGE_BYTES;
-                // this CTA's 512 bytes of a V row: columns 256*piece + 128*rank + [0,128), piece = 0,1
-                const int j32 = pt & 31, piece = j32 >> 4, cc = (j32 >> 3) & 1, v16 = j32 & 7;
-                const int col = 256 * piece + 128 * (int)rank + 64 * cc + 8 * v16;
-                const uint32_t chunk = vbase + (2 * piece + cc) * VCHUNK_BYTES;
+                // this CTA's 512 contiguous bytes of a V row: columns [256 rank, 256 rank + 256);
+                // 64-column chunk q = lane / 8 (MMA q/2, half q%2)
+                const int q = lane >> 3, v16 = lane & 7;
+                const uint32_t chunk = vbase + q * VCHUNK_BYTES;
 #pragma unroll
                 for (int x = 0; x < 16; x++) {
-                    const int r = (pt >> 5) + 4 * x;
+                    const int r = gw + 4 * x;
                     ptx::cp_async_16(chunk + (r >> 3) * 1024 + (r & 7) * 128 + ((v16 ^ (r & 7)) << 4),
-                                     p.v + vid[x] * DC + col);
+                                     p.v + vid[x] * DC + 256 * (int)rank + lane * 8);
                 }
                 ptx::cp_async_arrive_noinc(&sm->v_full[st]);
             }
@@ -448,9 +439,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
 #pragma unroll
                 for (int i = 0; i < 32; i++) o[i] = 0;
             }
-            // TMEM column c0 of this lane = output column 256*(c0/128) + 128*hh + c0%128
+            // TMEM column c0 of this lane = output column 256*hh + c0 (lanes 64-127 hold the peer's V columns)
             if (head < p.H || !direct) {
-                float4* d4 = reinterpret_cast<float4*>(row + 256 * (c0 >> 7) + 128 * hh + (c0 & 127));
+                float4* d4 = reinterpret_cast<float4*>(row + 256 * hh + c0);
 #pragma unroll
                 for (int i = 0; i < 8; i++)
                     d4[i] = make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
