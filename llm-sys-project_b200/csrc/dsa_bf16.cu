@@ -346,7 +346,7 @@ __global__ void __launch_bounds__(128) dsa_merge_kernel(const float* __restrict_
 
 int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, const void* kp, const void* v,
                          const int* idx, float* out, float* part_o, float* part_ml, int* status, int Q, int H, int S,
-                         int NS, int tiles_per_split, cudaStream_t stream);
+                         int NS, int tiles_per_split, int tile_rows, cudaStream_t stream);
 
 extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
                                      const uint16_t* kp, const uint16_t* v, const int* idx, float* out,
@@ -366,14 +366,19 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
     if (!ws) ws = b200_default_ws();
     if (!ws) return B200_CUDA_ERROR;
 
-    // The CTA-pair kernel (64-row tiles, double-buffered) handles every shape with S % 64 == 0; the
-    // single-CTA kernel (32-row tiles) takes the rest.  B200_DSA_SINGLE_CTA=1 forces the latter.
+    // The CTA-pair kernels take every shape with S % 64 == 0 (128-row tiles when S % 128 == 0, else
+    // 64-row tiles); the single-CTA kernel (32-row tiles) takes the rest.  B200_DSA_SINGLE_CTA=1 forces
+    // the latter, B200_DSA_TILE64=1 the 64-row pair kernel (both for comparison runs).
     static const bool force_single = getenv("B200_DSA_SINGLE_CTA") != nullptr;
+    static const bool force_tile64 = getenv("B200_DSA_TILE64") != nullptr;
     const bool use_pair = (S % 64 == 0) && !force_single;
+    const int pair_tile = (S % 128 == 0 && !force_tile64) ? 128 : 64;
     // split the selected rows so that the grid covers the machine about once
-    const int nt_total = S / (use_pair ? 64 : TKV);
+    const int nt_total = S / (use_pair ? pair_tile : TKV);
     int NS = 1;
     if (2 * Q < ws->sm_count) NS = ws->sm_count / (2 * Q);
+    static const int forced_splits = getenv("B200_DSA_SPLITS") ? atoi(getenv("B200_DSA_SPLITS")) : 0;   // tuning aid
+    if (forced_splits > 0) NS = forced_splits;
     if (NS > nt_total) NS = nt_total;
     if (NS > 64) NS = 64;
     if (NS < 1) NS = 1;
@@ -393,7 +398,7 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
     }
     if (use_pair) {
         int st = b200_launch_dsa_pair(q_nope, q_pe, kc, kp, v, idx, out, part_o, part_ml, ws->d_status, Q, H, S, NS, tps,
-                                      stream);
+                                      pair_tile, stream);
         if (st) return st;
         if (NS > 1) {
             dsa_merge_kernel<<<dim3(H, Q), 128, 0, stream>>>(part_o, part_ml, out, H, NS);

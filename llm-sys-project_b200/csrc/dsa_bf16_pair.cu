@@ -66,6 +66,7 @@ struct Params {
     int* status;
     int H, S, NS, tiles_per_split;
     float sl2;
+    long long* trace;   // optional [10][64] clock64 stamps of cluster 0 (debug aid)
 };
 
 // ---- cluster-scope helpers --------------------------------------------------------------------
@@ -244,6 +245,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             for (int x = 0; x < 16; x++) vid[x] = vid_n[x];
             load_ids(j + 1, kid_n, kpid_n, vid_n);
             if (!ptx::mbar_wait(&sm->k_empty[st], par, abort_flag)) goto done;
+            if (p.trace && rank == 0 && pt == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64) p.trace[8 * 64 + j] = clock64();
             {
                 const uint32_t kst = ptx::smem_u32(sK) + st * K_STAGE_BYTES;
                 // Kc: row r = 8 gw + x, 16-byte chunk ch = lane (+32): slot ch/8, position (ch%8) ^ (r%8)
@@ -267,6 +269,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             ptx::cp_async_arrive_noinc(&sm->k_full[st]);
             {
                 if (!ptx::mbar_wait(&sm->v_empty[st], par, abort_flag)) goto done;
+                if (p.trace && rank == 0 && pt == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64) p.trace[9 * 64 + j] = clock64();
                 const uint32_t vbase = ptx::smem_u32(sV) + st * V_STAGE_BYTES;
                 // this CTA's 512 contiguous bytes of a V row: columns [256 rank, 256 rank + 256);
                 // 64-column chunk q = lane / 8 (MMA q/2, half q%2)
@@ -308,6 +311,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                 if (!ptx::mbar_wait(&sm->v_full[st], par, abort_flag)) return false;
                 if (!forward_or_wait(&sm->pv_peer[st], par)) return false;
                 if (!leader) return true;
+                if (p.trace && blockIdx.y == 0 && blockIdx.z == 0 && i < 64) p.trace[2 * 64 + i] = clock64();
                 ptx::tc_fence_after();
 #pragma unroll
                 for (int inst = 0; inst < 2; inst++) {
@@ -321,6 +325,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                 }
                 commit_both(&sm->v_empty[st]);
                 commit_both(&sm->p_empty);
+                if (p.trace && blockIdx.y == 0 && blockIdx.z == 0 && i < 64) p.trace[3 * 64 + i] = clock64();
                 return true;
             };
             if (!ptx::mbar_wait(&sm->q_full, 0, abort_flag)) goto done;
@@ -330,6 +335,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                 if (!ptx::mbar_wait(&sm->s_empty[st], par ^ 1, abort_flag)) goto done;   // passes at once on first use
                 if (!ptx::mbar_wait(&sm->k_full[st], par, abort_flag)) goto done;
                 if (!forward_or_wait(&sm->qk_peer[st], par)) goto done;
+                if (leader && p.trace && blockIdx.y == 0 && blockIdx.z == 0 && j < 64) p.trace[0 * 64 + j] = clock64();
                 if (leader) {
                     ptx::tc_fence_after();
 #pragma unroll
@@ -344,6 +350,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                     }
                     commit_both(&sm->k_empty[st]);
                     commit_both(&sm->s_full[st]);
+                    if (p.trace && blockIdx.y == 0 && blockIdx.z == 0 && j < 64) p.trace[1 * 64 + j] = clock64();
                 }
                 if (j > 0 && !issue_pv(j - 1)) goto done;
             }
@@ -361,6 +368,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
         for (int j = 0; j < nt; j++) {
             const int sb = j & 1;
             if (!ptx::mbar_wait(&sm->s_full[sb], (uint32_t)((j >> 1) & 1), abort_flag)) goto done;
+            const bool trc = p.trace && rank == 0 && blockIdx.y == 0 && blockIdx.z == 0 && t == 0 && j < 64;
+            if (trc) p.trace[4 * 64 + j] = clock64();
             ptx::tc_fence_after();
             uint32_t r[32];
             ptx::tmem_ld_32x32(tmem + lane_addr + S_COL + sb * 32, r);
@@ -375,6 +384,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             ptx::mbar_arrive(&sm->mx_bar);
             if (!ptx::mbar_wait(&sm->mx_bar, (uint32_t)(j & 1), abort_flag)) goto done;
             tmax = fmaxf(tmax, sm->xchg[sb][t ^ 64]);
+            if (trc) p.trace[5 * 64 + j] = clock64();
             const bool need = tmax > m + thr;
             const float m_new = need ? tmax : m;
             const float corr = need ? exp2f((m - m_new) * p.sl2) : 1.0f;
@@ -389,6 +399,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                 pk[i] = *reinterpret_cast<uint32_t*>(&h2);
             }
             if (!ptx::mbar_wait(&sm->p_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
+            if (trc) p.trace[6 * 64 + j] = clock64();
             ptx::tc_fence_after();
             if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
@@ -413,6 +424,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before();
             ptx::mbar_arrive(&sm->p_full);
+            if (trc) p.trace[7 * 64 + j] = clock64();
             l = l * corr + rowsum;
             m = m_new;
         }
@@ -462,16 +474,408 @@ done:
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
 }
 
+
+// =================================================================================================
+// 128-row tiles.  tcgen05.mma has a minimum issue interval of a few tens of nanoseconds whatever its
+// shape, so the 36 K-steps of Q K^T cost the same for 64 rows as for 128: with 64-row tiles the tensor
+// pipe, not HBM, bounded the kernel.  Here a tile is 128 selected rows (N = 128 for Q K^T, eight
+// K-steps per P V half), which leaves room for one K stage (72 KB) and one V stage (64 KB) per CTA next
+// to Q (72 KB) and P (16 KB).  The K stage refills while P V of the previous tile and the softmax run,
+// the V stage while Q K^T of the next tile runs; K and V have their own gather warps so that neither
+// waits behind the other's free-slot barrier.
+namespace t128 {
+
+constexpr int TKV = 128, KROWS = 64;
+constexpr int KSLOT_BYTES = KROWS * 128;           // 8192: 64 rows of one 128-byte column block
+constexpr int K_STAGE_BYTES = KBLK * KSLOT_BYTES;  // 73728
+constexpr int VCHUNK_BYTES = TKV * 128;            // 16384 (128 rows x 64 columns)
+constexpr int V_STAGE_BYTES = 4 * VCHUNK_BYTES;    // 65536
+constexpr int P_BYTES = 16 * P_CHUNK_BYTES;        // 16384
+constexpr uint32_t S_COL = 256;                    // two score buffers of 64 columns
+constexpr int NKW = 4, NVW = 4;                    // gather warps for K rows and for V rows
+constexpr int NPROD = 32 * (NKW + NVW);
+constexpr int THREADS128 = 160 + NPROD;            // warps 0-3 softmax, 4 MMA/relay, then K and V gather warps
+
+struct Smem {
+    uint64_t q_full;          // all gather threads
+    uint64_t k_full, v_full;  // the K gather threads, the V gather threads
+    uint64_t s_empty[2];      // 128 softmax threads
+    uint64_t p_full;          // 128 softmax threads
+    uint64_t qk_peer, pv_peer;   // twins in the leader: one arrival per tile from the peer's relay thread
+    uint64_t k_empty, v_empty, s_full[2], p_empty, o_done;   // tcgen05.commit, both CTAs
+    uint64_t mx_bar;          // 128 softmax threads
+    uint32_t tmem_base;
+    int abort_flag;
+    float xchg[2][128];
+};
+constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + K_STAGE_BYTES + V_STAGE_BYTES + P_BYTES + sizeof(Smem);
+static_assert(SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_decode_pair128_kernel(const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sQ = base;
+    uint8_t* sK = sQ + Q_BYTES;
+    uint8_t* sV = sK + K_STAGE_BYTES;
+    uint8_t* sP = sV + V_STAGE_BYTES;
+    Smem* sm = reinterpret_cast<Smem*>(sP + P_BYTES);
+    volatile int* abort_flag = &sm->abort_flag;
+
+    const uint32_t rank = cluster_rank();          // 0 = leader
+    const int sp = blockIdx.y, b = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nt_total = p.S / TKV;
+    const int t_begin = sp * p.tiles_per_split;
+    const int nt = max(0, min(nt_total, t_begin + p.tiles_per_split) - t_begin);
+    const bool tracing = p.trace && rank == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    if (tracing && threadIdx.x == 0) p.trace[10 * 64 + 4] = (long long)ptx::globaltimer_ns();
+
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&sm->q_full, NPROD);
+        ptx::mbar_init(&sm->k_full, 32 * NKW);
+        ptx::mbar_init(&sm->v_full, 32 * NVW);
+        for (int s = 0; s < 2; s++) {
+            ptx::mbar_init(&sm->s_empty[s], 128);
+            ptx::mbar_init(&sm->s_full[s], 1);
+        }
+        ptx::mbar_init(&sm->p_full, 128);
+        ptx::mbar_init(&sm->qk_peer, 1);
+        ptx::mbar_init(&sm->pv_peer, 1);
+        ptx::mbar_init(&sm->k_empty, 1);
+        ptx::mbar_init(&sm->v_empty, 1);
+        ptx::mbar_init(&sm->p_empty, 1);
+        ptx::mbar_init(&sm->o_done, 1);
+        ptx::mbar_init(&sm->mx_bar, 128);
+        sm->abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 4) {
+        tmem_alloc2(&sm->tmem_base, 512);
+        tmem_relinquish2();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                            // peer's barriers are initialised before anyone signals them
+    ptx::tc_fence_after();
+    const uint32_t tmem = sm->tmem_base;
+    // Launched with programmatic stream serialisation: everything above overlaps the tail of the
+    // previous kernel in the stream; nothing below reads or writes global memory before that kernel
+    // has completed.  (Both instructions are no-ops under an ordinary launch.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    if (warp >= 5) {
+        // ===================== gather producers: NKW warps for K rows, NVW warps for V rows =====================
+        const int pt = threadIdx.x - 160;
+        // Q: this CTA's 64 heads x 72 sixteen-byte chunks; heads >= H are zero
+        for (int i = pt; i < HPC * 72; i += NPROD) {
+            const int r = i / 72, ch = i - r * 72;
+            const int h = (int)rank * HPC + r;
+            const uint32_t dst = ptx::smem_u32(sQ) + (ch >> 3) * Q_BLK_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4);
+            if (h < p.H) {
+                const __nv_bfloat16* src = (ch < 64) ? p.q_nope + ((size_t)b * p.H + h) * DC + ch * 8
+                                                     : p.q_pe + ((size_t)b * p.H + h) * DP + (ch - 64) * 8;
+                ptx::cp_async_16(dst, src);
+            } else {
+                asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
+            }
+        }
+        ptx::cp_async_commit();
+        ptx::cp_async_wait<0>();
+        ptx::fence_proxy_async_smem();
+        ptx::mbar_arrive(&sm->q_full);
+
+        // A warp instruction always covers 512 contiguous bytes of one row (DRAM serves such pieces at
+        // more than twice the rate of scattered 128-byte ones).  Each lane fetches the ids of the rows
+        // its warp owns one tile ahead and hands them round by shuffle; the copies of a tile signal its
+        // barrier by themselves when they land, so these threads never wait for data.
+        const int* ids = p.idx + (size_t)b * p.S + (size_t)t_begin * TKV;
+        if (pt < 32 * NKW) {
+            constexpr int RPW = KROWS / NKW;                      // K rows per warp
+            const int kw = pt >> 5;                               // rows RPW kw .. RPW kw + RPW - 1 of this CTA's 64
+            const int my = (int)rank * KROWS + RPW * kw + (lane % RPW);
+            int id_n = (nt > 0) ? ids[my] : 0;
+            const uint32_t kst = ptx::smem_u32(sK);
+            for (int j = 0; j < nt; j++) {
+                const int id = id_n;
+                if (j + 1 < nt) id_n = ids[(size_t)(j + 1) * TKV + my];
+                if (!ptx::mbar_wait(&sm->k_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
+                if (tracing && pt == 0 && j < 64) p.trace[8 * 64 + j] = clock64();
+                // Kc: row r, 16-byte chunk ch = lane (+32): slot ch/8, position (ch%8) ^ (r%8)
+#pragma unroll 8
+                for (int x = 0; x < RPW; x++) {
+                    const size_t rid = (size_t)__shfl_sync(0xffffffffu, id, x);
+                    const int r = RPW * kw + x;
+#pragma unroll
+                    for (int hf = 0; hf < 2; hf++) {
+                        const int ch = lane + 32 * hf;
+                        ptx::cp_async_16(kst + (ch >> 3) * KSLOT_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4),
+                                         p.kc + rid * DC + ch * 8);
+                    }
+                }
+                // Kp (128 bytes per row, slot 8): four rows per instruction
+#pragma unroll
+                for (int x = 0; x < RPW / 4; x++) {
+                    const int rr = 4 * x + (lane >> 3), j16 = lane & 7;
+                    const size_t rid = (size_t)__shfl_sync(0xffffffffu, id, rr);
+                    const int r = RPW * kw + rr;
+                    ptx::cp_async_16(kst + 8 * KSLOT_BYTES + r * 128 + ((j16 ^ (r & 7)) << 4), p.kp + rid * DP + j16 * 8);
+                }
+                ptx::cp_async_arrive_noinc(&sm->k_full);
+                // pull the next tile's rows into L2 while this tile is on its way
+                if (j + 1 < nt && lane < RPW) {
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kc + (size_t)id_n * DC), "r"(DC * 2) : "memory");
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kp + (size_t)id_n * DP), "r"(DP * 2) : "memory");
+                }
+            }
+        } else {
+            constexpr int VPW = TKV / NVW;                        // V rows per warp (32 or 64)
+            const int vw = (pt - 32 * NKW) >> 5;                  // V rows vw, vw + NVW, ... of the tile's 128
+            const int my0 = vw + NVW * lane, my1 = (VPW > 32) ? vw + NVW * (lane + 32) : my0;
+            int id0_n = 0, id1_n = 0;
+            if (nt > 0) { id0_n = ids[my0]; id1_n = ids[my1]; }
+            // this CTA's 512 contiguous bytes of a V row: columns [256 rank, 256 rank + 256);
+            // 64-column chunk q = lane / 8 (MMA q/2, half q%2)
+            const int q = lane >> 3, v16 = lane & 7;
+            const uint32_t chunk = ptx::smem_u32(sV) + q * VCHUNK_BYTES;
+            for (int j = 0; j < nt; j++) {
+                const int id0 = id0_n, id1 = id1_n;
+                if (j + 1 < nt) {
+                    id0_n = ids[(size_t)(j + 1) * TKV + my0];
+                    id1_n = ids[(size_t)(j + 1) * TKV + my1];
+                }
+                if (!ptx::mbar_wait(&sm->v_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
+                if (tracing && pt == 32 * NKW && j < 64) p.trace[9 * 64 + j] = clock64();
+#pragma unroll 8
+                for (int x = 0; x < VPW; x++) {
+                    const size_t rid = (size_t)__shfl_sync(0xffffffffu, (x < 32) ? id0 : id1, x & 31);
+                    const int r = vw + NVW * x;
+                    ptx::cp_async_16(chunk + (r >> 3) * 1024 + (r & 7) * 128 + ((v16 ^ (r & 7)) << 4),
+                                     p.v + rid * DC + 256 * (int)rank + lane * 8);
+                }
+                ptx::cp_async_arrive_noinc(&sm->v_full);
+                if (j + 1 < nt) {
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v + (size_t)id0_n * DC + 256 * (int)rank), "r"(512) : "memory");
+                    if (VPW > 32)
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v + (size_t)id1_n * DC + 256 * (int)rank), "r"(512) : "memory");
+                }
+            }
+        }
+        ptx::cp_async_commit();
+        ptx::cp_async_wait<0>();           // nothing of this thread is in flight when the CTA winds down
+    } else if (warp == 4) {
+        // ===================== MMA issuer (leader) / barrier relay (peer) =====================
+        if (lane == 0 && nt > 0) {
+            const bool leader = (rank == 0);
+            constexpr uint32_t idesc_qk = ptx::make_idesc(1, 1, 0, 0, HEADS, TKV);
+            constexpr uint32_t idesc_pv = ptx::make_idesc(1, 1, 0, 1, HEADS, 256);
+            const uint32_t q_addr = ptx::smem_u32(sQ), k_addr = ptx::smem_u32(sK), v_addr = ptx::smem_u32(sV),
+                           p_addr = ptx::smem_u32(sP);
+            auto forward_or_wait = [&](uint64_t* peer, uint32_t par_peer) -> bool {
+                ptx::fence_proxy_async_smem();
+                if (leader) return mbar_wait_cluster(peer, par_peer, abort_flag);
+                mbar_arrive_cta(peer, 0);
+                return true;
+            };
+            auto issue_pv = [&](int i) -> bool {
+                const uint32_t par = (uint32_t)(i & 1);
+                if (!ptx::mbar_wait(&sm->p_full, par, abort_flag)) return false;
+                if (!ptx::mbar_wait(&sm->v_full, par, abort_flag)) return false;
+                if (!forward_or_wait(&sm->pv_peer, par)) return false;
+                if (!leader) return true;
+                if (tracing && i < 64) p.trace[2 * 64 + i] = clock64();
+                ptx::tc_fence_after();
+#pragma unroll
+                for (int inst = 0; inst < 2; inst++) {
+#pragma unroll
+                    for (int ks = 0; ks < 8; ks++) {
+                        uint64_t ad = ptx::make_smem_desc(p_addr + ks * 2 * P_CHUNK_BYTES, P_CHUNK_BYTES, 128, 0);
+                        uint64_t bd = ptx::make_smem_desc(v_addr + 2 * inst * VCHUNK_BYTES + ks * 2048, VCHUNK_BYTES, 1024, 2);
+                        mma2_f16(tmem + O_COL + 128 * inst, ad, bd, idesc_pv, (i > 0 || ks > 0) ? 1u : 0u);
+                    }
+                }
+                commit_both(&sm->v_empty);
+                commit_both(&sm->p_empty);
+                if (tracing && i < 64) p.trace[3 * 64 + i] = clock64();
+                return true;
+            };
+            if (tracing) { p.trace[10 * 64 + 0] = clock64(); p.trace[10 * 64 + 1] = (long long)ptx::globaltimer_ns(); }
+            if (!ptx::mbar_wait(&sm->q_full, 0, abort_flag)) goto done;
+            for (int j = 0; j < nt; j++) {
+                const int sb = j & 1;
+                if (!ptx::mbar_wait(&sm->s_empty[sb], (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag)) goto done;
+                if (!ptx::mbar_wait(&sm->k_full, (uint32_t)(j & 1), abort_flag)) goto done;
+                if (!forward_or_wait(&sm->qk_peer, (uint32_t)(j & 1))) goto done;
+                if (leader) {
+                    if (tracing && j < 64) p.trace[0 * 64 + j] = clock64();
+                    ptx::tc_fence_after();
+#pragma unroll
+                    for (int c = 0; c < KBLK; c++) {
+#pragma unroll
+                        for (int k4 = 0; k4 < 4; k4++) {
+                            uint64_t ad = ptx::make_smem_desc(q_addr + c * Q_BLK_BYTES + k4 * 32, 16, 1024, 2);
+                            uint64_t bd = ptx::make_smem_desc(k_addr + c * KSLOT_BYTES + k4 * 32, 16, 1024, 2);
+                            mma2_f16(tmem + S_COL + sb * 64, ad, bd, idesc_qk, (c > 0 || k4 > 0) ? 1u : 0u);
+                        }
+                    }
+                    commit_both(&sm->k_empty);
+                    commit_both(&sm->s_full[sb]);
+                    if (tracing && j < 64) p.trace[1 * 64 + j] = clock64();
+                }
+                if (j > 0 && !issue_pv(j - 1)) goto done;
+            }
+            if (!issue_pv(nt - 1)) goto done;
+            if (leader) commit_both(&sm->o_done);
+            if (tracing) { p.trace[10 * 64 + 2] = clock64(); p.trace[10 * 64 + 3] = (long long)ptx::globaltimer_ns(); }
+        }
+    } else {
+        // ===================== softmax / correction / epilogue (warps 0-3 of each CTA) =====================
+        const int t = threadIdx.x;                       // TMEM lane
+        const int hl = t & 63, hh = t >> 6;              // local head, half of the tile / of the columns held here
+        const int head = (int)rank * HPC + hl;
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        float m = -1e30f, l = 0.0f;
+        const float thr = 8.0f / p.sl2;
+        for (int j = 0; j < nt; j++) {
+            const int sb = j & 1;
+            if (!ptx::mbar_wait(&sm->s_full[sb], (uint32_t)((j >> 1) & 1), abort_flag)) goto done;
+            const bool trc = tracing && t == 0 && j < 64;
+            if (trc) p.trace[4 * 64 + j] = clock64();
+            ptx::tc_fence_after();
+            uint32_t r[64];
+            ptx::tmem_ld_32x64(tmem + lane_addr + S_COL + sb * 64, r);
+            ptx::tc_wait_ld();
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&sm->s_empty[sb]);
+            float tmax = -FLT_MAX;
+#pragma unroll
+            for (int i = 0; i < 64; i++) tmax = fmaxf(tmax, __uint_as_float(r[i]));
+            // the other half of this head's 128 scores lives in lane t ^ 64
+            sm->xchg[sb][t] = tmax;
+            ptx::mbar_arrive(&sm->mx_bar);
+            if (!ptx::mbar_wait(&sm->mx_bar, (uint32_t)(j & 1), abort_flag)) goto done;
+            tmax = fmaxf(tmax, sm->xchg[sb][t ^ 64]);
+            if (trc) p.trace[5 * 64 + j] = clock64();
+            const bool need = tmax > m + thr;
+            const float m_new = need ? tmax : m;
+            const float corr = need ? exp2f((m - m_new) * p.sl2) : 1.0f;
+            float rowsum = 0.0f;
+            uint32_t pk[32];
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                float p0 = exp2f((__uint_as_float(r[2 * i]) - m_new) * p.sl2);
+                float p1 = exp2f((__uint_as_float(r[2 * i + 1]) - m_new) * p.sl2);
+                rowsum += p0 + p1;
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                pk[i] = *reinterpret_cast<uint32_t*>(&h2);
+            }
+            if (!ptx::mbar_wait(&sm->p_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
+            if (trc) p.trace[6 * 64 + j] = clock64();
+            ptx::tc_fence_after();
+            if (j > 0 && __any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < 256; c0 += 32) {
+                    uint32_t o[32];
+                    ptx::tmem_ld_32x32(tmem + lane_addr + O_COL + c0, o);
+                    ptx::tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    ptx::tmem_st_32x32(tmem + lane_addr + O_COL + c0, o);
+                }
+                ptx::tc_wait_st();
+            }
+            // P[hl, 64*hh + 0..63]: 16-byte chunk ch = 8*hh + q at ch*1024 + hl*16
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                const uint32_t dst = ptx::smem_u32(sP) + (8 * hh + q) * P_CHUNK_BYTES + hl * 16;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[4 * q]), "r"(pk[4 * q + 1]),
+                             "r"(pk[4 * q + 2]), "r"(pk[4 * q + 3])
+                             : "memory");
+            }
+            ptx::fence_proxy_async_smem();
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&sm->p_full);
+            if (trc) p.trace[7 * 64 + j] = clock64();
+            l = l * corr + rowsum;
+            m = m_new;
+        }
+        if (nt > 0) {
+            if (!ptx::mbar_wait(&sm->o_done, 0, abort_flag)) goto done;
+            ptx::tc_fence_after();
+        }
+        // total row sum = this lane's half + the partner lane's half
+        sm->xchg[nt & 1][t] = l;
+        ptx::mbar_arrive(&sm->mx_bar);
+        if (!ptx::mbar_wait(&sm->mx_bar, (uint32_t)(nt & 1), abort_flag)) goto done;
+        l += sm->xchg[nt & 1][t ^ 64];
+        const bool direct = (p.NS == 1);
+        const float inv = (direct && l > 0.0f) ? 1.0f / l : 1.0f;
+        // Rows of this warp: heads 32 (warp & 1) .. +31 of this CTA, output columns 256 hh + [0, 256).
+        // Each 32-column chunk goes through a padded staging tile (the K stage is free by now) so that
+        // a store instruction writes four full 128-byte lines instead of 32 scattered 16-byte pieces.
+        float* wrow0 = direct ? p.out + ((size_t)b * p.H + (int)rank * HPC + 32 * (warp & 1)) * DC
+                              : p.part_o + (((size_t)b * p.NS + sp) * HEADS + (int)rank * HPC + 32 * (warp & 1)) * DC;
+        const int rows_ok = direct ? max(0, min(32, p.H - ((int)rank * HPC + 32 * (warp & 1)))) : 32;
+        float* stg = reinterpret_cast<float*>(sK) + warp * (32 * 36);
+#pragma unroll 1
+        for (int c0 = 0; c0 < 256; c0 += 32) {
+            uint32_t o[32];
+            if (nt > 0) {
+                ptx::tmem_ld_32x32(tmem + lane_addr + O_COL + c0, o);
+                ptx::tc_wait_ld();
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) o[i] = 0;
+            }
+            // TMEM column c0 of this lane = output column 256*hh + c0 (lanes 64-127 hold the peer's V columns)
+            float4* s4 = reinterpret_cast<float4*>(stg + lane * 36);
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                s4[i] = make_float4(__uint_as_float(o[4 * i]) * inv, __uint_as_float(o[4 * i + 1]) * inv,
+                                    __uint_as_float(o[4 * i + 2]) * inv, __uint_as_float(o[4 * i + 3]) * inv);
+            __syncwarp();
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int r = 4 * k + (lane >> 3), c4 = lane & 7;
+                const float4 v4 = *reinterpret_cast<const float4*>(stg + r * 36 + 4 * c4);
+                if (r < rows_ok) *reinterpret_cast<float4*>(wrow0 + (size_t)r * DC + 256 * hh + c0 + 4 * c4) = v4;
+            }
+            __syncwarp();
+        }
+        if (tracing && t == 0) p.trace[10 * 64 + 5] = (long long)ptx::globaltimer_ns();
+        if (!direct && hh == 0) {
+            float* ml = p.part_ml + (((size_t)b * p.NS + sp) * HEADS + head) * 2;
+            ml[0] = (nt > 0) ? m * p.sl2 : -1e30f;
+            ml[1] = l;
+        }
+    }
+done:
+    ptx::tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                  // the pair's MMAs and TMEM reads are over in both CTAs
+    if (warp == 4) tmem_dealloc2(tmem, 512);
+    if (tracing && threadIdx.x == 0) p.trace[10 * 64 + 6] = (long long)ptx::globaltimer_ns();
+    if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
+}
+
+}  // namespace t128
+
 }  // namespace pair
 
-// Host side: called by b200_dsa_forward_bf16 when the shape suits the pair kernel (S % 64 == 0).
+long long* g_dsa_trace = nullptr;
+extern "C" __attribute__((visibility("default"))) void b200_debug_dsa_trace(long long* dev_buf) { g_dsa_trace = dev_buf; }
+
+// Host side: called by b200_dsa_forward_bf16 with tile_rows = 128 (S % 128 == 0) or 64 (S % 64 == 0);
+// tiles_per_split counts tiles of that size.
 int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, const void* kp, const void* v,
                          const int* idx, float* out, float* part_o, float* part_ml, int* status, int Q, int H, int S,
-                         int NS, int tiles_per_split, cudaStream_t stream) {
+                         int NS, int tiles_per_split, int tile_rows, cudaStream_t stream) {
     static bool attr_done = false;
     if (!attr_done) {
         B200_CUDA_TRY(cudaFuncSetAttribute(pair::dsa_decode_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)pair::SMEM_BYTES));
+        B200_CUDA_TRY(cudaFuncSetAttribute(pair::t128::dsa_decode_pair128_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pair::t128::SMEM_BYTES));
         attr_done = true;
     }
     pair::Params p;
@@ -483,7 +887,22 @@ int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, c
     p.idx = idx; p.out = out; p.part_o = part_o; p.part_ml = part_ml; p.status = status;
     p.H = H; p.S = S; p.NS = NS; p.tiles_per_split = tiles_per_split;
     p.sl2 = 1.4426950408889634f / sqrtf((float)(pair::DC + pair::DP));
-    pair::dsa_decode_pair_kernel<<<dim3(2, NS, Q), pair::THREADS, pair::SMEM_BYTES, stream>>>(p);
+    p.trace = g_dsa_trace;
+    if (tile_rows == 128) {
+        static const bool no_pdl = getenv("B200_DSA_NO_PDL") != nullptr;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2, NS, Q);
+        cfg.blockDim = dim3(pair::t128::THREADS128);
+        cfg.dynamicSmemBytes = pair::t128::SMEM_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = no_pdl ? 0 : 1;
+        B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::t128::dsa_decode_pair128_kernel, p));
+    } else
+        pair::dsa_decode_pair_kernel<<<dim3(2, NS, Q), pair::THREADS, pair::SMEM_BYTES, stream>>>(p);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
