@@ -352,8 +352,9 @@ def build_dsa(b200, torch, dev, seed):
 def dsa_bytes():
     c = DSA
     e = 2
+    # selected K/V rows and queries in bf16, output in fp32, 32-bit row indices
     return (c["B"] * c["S"] * (2 * c["Dc"] + c["Dp"]) * e + c["B"] * c["H"] * (c["Dc"] + c["Dp"]) * e
-            + c["B"] * c["H"] * c["Dc"] * e + 4 * c["B"] * c["S"])
+            + c["B"] * c["H"] * c["Dc"] * 4 + 4 * c["B"] * c["S"])
 
 
 def bench_dsa(b200, torch, oracle, dev, args, sampler, do_cpu):
