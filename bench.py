@@ -51,6 +51,11 @@ def load_package():
     return mod
 
 
+# DRAM bytes / algorithmic bytes of the dominant kernels, from the ncu captures summarised under profiles/
+# (small cases of the same kernels; traffic grows in proportion to the rows and weights processed)
+TRAFFIC_RATIO = {"gemm1": 1.06, "dsa": 1.00}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -249,7 +254,8 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
                 "d2h_bytes_per_step": int(out_h.numel() * 4), "ms_per_step": e2e_s * 1e3},
         "roofline": {"kernel": "grouped_gemm_fp8<1> (GEMM1+SwiGLU+requant)", "bound": "hbm",
                      "achieved": g1_bytes / (g1_ms * 1e-3) / 1e9 if g1_ms > 0 else None, "peak": hbm, "unit": "GB/s",
-                     "frac": (g1_bytes / (g1_ms * 1e-3) / 1e9 / hbm) if g1_ms > 0 else None, "traffic": None,
+                     "frac": (g1_bytes / (g1_ms * 1e-3) / 1e9 / hbm) if g1_ms > 0 else None,
+                     "traffic": int(g1_bytes * TRAFFIC_RATIO["gemm1"]),
                      "peak_source": which, "kernel_ms": g1_ms, "algorithmic_bytes": int(g1_bytes),
                      "launches_timed": ncalls},
         "kernels": {"gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "other_ms": ms - g1_ms - g2_ms,
@@ -279,7 +285,8 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
         out, ids, _ = ep.forward(xq, xs)
     torch.cuda.synchronize()
     assert b200.device_status() == 0, "device-side wait timed out"
-    recv_rows = ep.last_stats["recv_rows"]
+    recv_rows = ep.recv_pairs()              # (token, expert) pairs computed on this GPU
+    recv_tokens = ep.last_stats["recv_rows"]
     counts = torch.bincount(ids.reshape(-1).long(), minlength=c["E"])
     dist.all_reduce(counts)
     counts = counts.cpu().numpy()
@@ -299,6 +306,39 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
     t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
+    ep.profile = True
+    b200.moe_fp8_profile(True)
+    ep.forward(xq, xs)
+    phases = ep.phase_ms()
+    g1_ms, g2_ms, _ = b200.moe_fp8_profile_read()
+    b200.moe_fp8_profile(False)
+    ep.profile = False
+    El = c["E"] // world
+    g1_bytes, active, rows = moe_gemm1_bytes(counts[rank * El:(rank + 1) * El])
+    hbm, _, which = measured_peaks()
+
+    # end to end: this rank's tokens from pinned host memory, result back to pinned host memory
+    xq_h, xs_h = xq.cpu().pin_memory(), xs.cpu().pin_memory()
+    out_h = torch.empty((c["T"], c["D"]), dtype=torch.float32).pin_memory()
+    dq, ds = torch.empty_like(xq), torch.empty_like(xs)
+
+    def e2e_step():
+        dq.copy_(xq_h, non_blocking=True)
+        ds.copy_(xs_h, non_blocking=True)
+        o, _, _ = ep.forward(dq, ds)
+        out_h.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    dist.barrier()
+    te = torch.tensor([(time.perf_counter() - t0) / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_s = float(te.item())
     rr = torch.tensor([recv_rows], device=dev, dtype=torch.float32)
     rmax = rr.clone(); dist.all_reduce(rmax, op=dist.ReduceOp.MAX)
     rsum = rr.clone(); dist.all_reduce(rsum)
@@ -306,7 +346,16 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
     flops_hot = 6.0 * float(rmax.item()) * c["D"] * c["I"]
     res = {
         "value": world * c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),
-        "kernels": {"rows_per_gpu_max": float(rmax.item()), "rows_per_gpu_mean": float(rsum.item()) / world,
+        "e2e": {"value": world * c["T"] / e2e_s, "unit": "tokens/s",
+                "h2d_bytes_per_step": int(world * (xq_h.numel() + xs_h.numel() * 4)),
+                "d2h_bytes_per_step": int(world * out_h.numel() * 4), "ms_per_step": e2e_s * 1e3},
+        "roofline": {"kernel": "grouped_gemm_fp8<1> (GEMM1+SwiGLU+requant) on rank 0", "bound": "hbm",
+                     "achieved": g1_bytes / (g1_ms * 1e-3) / 1e9 if g1_ms > 0 else None, "peak": hbm, "unit": "GB/s",
+                     "frac": (g1_bytes / (g1_ms * 1e-3) / 1e9 / hbm) if g1_ms > 0 else None,
+                     "traffic": int(g1_bytes * TRAFFIC_RATIO["gemm1"]), "peak_source": which, "kernel_ms": g1_ms,
+                     "algorithmic_bytes": int(g1_bytes), "launches_timed": 1},
+        "kernels": {"phase_ms_rank0": phases, "gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "rows_per_gpu_max": float(rmax.item()), "rows_per_gpu_mean": float(rsum.item()) / world,
+                    "dispatched_tokens_this_gpu": int(recv_tokens),
                     "max_tokens_per_expert": int(counts.max()), "mean_tokens_per_expert": float(counts.mean()),
                     "rows_by_gpu": [int(v) for v in per_gpu],
                     "hot_gpu_gemm_tflops_lower_bound": flops_hot / (ms * 1e-3) / 1e12,
@@ -381,11 +430,14 @@ def bench_dsa(b200, torch, oracle, dev, args, sampler, do_cpu):
     nbytes = dsa_bytes()
     res = {"metric": "dsa_decode_us_per_step", "value": us, "unit": "us/step", "higher_is_better": False,
            "steps": steps, "gpu_launches": int(launches), "dtype": "bf16",
-           "config": {"workload": "C4: B=64 H=128 Dc=512 Dp=64 top-k=2048, paged bf16 cache, page 64, "
-                                  f"seq_len U[8192,131072] ({N} cache rows), indices unsorted",
-                      "l2": "4 index sets rotate; 285 MB of rows per step > 126 MB L2"},
-           "roofline": {"kernel": "dsa_decode_bf16_kernel", "bound": "hbm", "achieved": nbytes / (us * 1e-6) / 1e9,
-                        "peak": hbm, "unit": "GB/s", "frac": nbytes / (us * 1e-6) / 1e9 / hbm, "traffic": None,
+           "config": {"workload": f"C4: B={c['B']} H={c['H']} Dc={c['Dc']} Dp={c['Dp']} top-k={c['S']}, paged bf16 "
+                                  f"cache, page {c['page']}, seq_len U[{c['seq_min']},{c['seq_max']}] ({N} cache rows), "
+                                  "indices unsorted",
+                      "l2": f"4 index sets rotate; {c['B'] * c['S'] * (2 * c['Dc'] + c['Dp']) * 2 / 1e6:.0f} MB of rows "
+                            "per step > 126 MB L2"},
+           "roofline": {"kernel": "dsa_decode_pair128_kernel", "bound": "hbm", "achieved": nbytes / (us * 1e-6) / 1e9,
+                        "peak": hbm, "unit": "GB/s", "frac": nbytes / (us * 1e-6) / 1e9 / hbm,
+                        "traffic": int(nbytes * TRAFFIC_RATIO["dsa"]),
                         "peak_source": which, "algorithmic_bytes": int(nbytes),
                         "tflops": 2.0 * c["B"] * c["H"] * c["S"] * (2 * c["Dc"] + c["Dp"]) / (us * 1e-6) / 1e12,
                         "frac_of_nominal_8TBs": nbytes / (us * 1e-6) / 8e12}}
@@ -531,8 +583,10 @@ def main():
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": moe["ms_per_step"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
                 "data": "synthetic",
-                "config": {"workload": ("C3" if world == 1 else "C5") + ": FP8 block-scale MoE layer, D=7168 I=2048 "
-                           "E=256 top-8 (8 groups / top-4), sigmoid+bias scoring, routed_scaling 2.5, T=4096 per GPU"
+                "config": {"workload": ("profiling-sized case, not a bench value: " if args.small else "")
+                           + ("C3" if world == 1 else "C5") + f": FP8 block-scale MoE layer, D={c['D']} I={c['I']} "
+                           f"E={c['E']} top-{c['K']} ({c['n_group']} groups / top-{c['topk_group']}), sigmoid+bias scoring, "
+                           f"routed_scaling 2.5, T={c['T']} per GPU"
                            + ("" if world == 1 else f", experts sharded over {world} GPUs, Zipf(1.1) load"),
                            "tokens_per_gpu": c["T"], "parallelism": "single" if world == 1 else f"ep{world}",
                            "l2": "11.3 GB of FP8 weights stream every step (inputs > 126 MB L2)"},

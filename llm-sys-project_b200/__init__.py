@@ -53,6 +53,7 @@ EXPORTED_SYMBOLS = [
     "b200_moe_fp8_experts_packed", "b200_moe_fp8_gemm1_stage", "b200_moe_fp8_profile", "b200_moe_fp8_profile_read",
     "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
     "b200_dsa_softmax_f32", "b200_dsa_output_proj_f32",
+    "b200_ep_plan", "b200_ep_sum_rows",
     "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128", "b200_umma_selftest",
 ]
 
@@ -196,6 +197,20 @@ def moe_fp8_gemm1_stage(xq, xs, expert_ids, w1q, w1s, act_q, act_s, offsets, row
     _check(lib().b200_moe_fp8_gemm1_stage(None, _p(xq), _p(xs), _p(expert_ids), _p(w1q), _p(w1s), _p(act_q),
                                           _p(act_s), _p(offsets), _p(row_pair), C.byref(cfg), _stream(stream)),
            "moe_fp8_gemm1_stage")
+
+
+def ep_plan(expert_ids, expert_w, experts_per_rank, world, send_tok, pos, send_counts, slot_ids, slot_w, stream=None):
+    T, K = expert_ids.shape
+    _check(lib().b200_ep_plan(_p(expert_ids), _p(expert_w), T, K, int(experts_per_rank), int(world), _p(send_tok),
+                              _p(pos), _p(send_counts), _p(slot_ids), _p(slot_w), _stream(stream)), "ep_plan")
+
+
+def ep_sum_rows(back, pos, world, out, stream=None):
+    """back [R,D] fp32 or bf16; pos [world,T] int32; out [T,D] fp32."""
+    import torch
+    T, D = out.shape
+    _check(lib().b200_ep_sum_rows(_p(back), 1 if back.dtype == torch.bfloat16 else 0, _p(pos), int(world), T, D,
+                                  _p(out), _stream(stream)), "ep_sum_rows")
 
 
 def moe_fp8_profile(enable):

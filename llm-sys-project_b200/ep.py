@@ -2,9 +2,19 @@
 torch.distributed process group (rank g owns experts [g*E/W, (g+1)*E/W)); tokens stay on
 their source rank.  One step is
 
-    route (local kernel) -> counts all-to-all -> dispatch all-to-all (FP8 rows, 1x128
-    scales, local expert id, router weight) -> grouped expert GEMMs on the owner (CUDA
-    library, one "token" per received row, K = 1) -> combine all-to-all -> per-token sum.
+    route (local kernel)
+    -> counts all-to-all
+    -> dispatch all-to-all: every token goes ONCE to each rank that owns at least one of its
+       selected experts (FP8 row, 1x128 scales, its K slots with local expert ids, -1 for slots
+       owned elsewhere, and the router weights)
+    -> grouped expert GEMMs on the owner (CUDA library; slots with id -1 are skipped), which
+       also sums the owner's contributions per token
+    -> combine all-to-all: one partial output row per (token, owner rank)
+    -> per-token sum of the partial rows on the source rank.
+
+Sending a token once per owner rank instead of once per selected expert cuts the dispatch
+volume by the number of its experts that share a rank, and summing on the owner cuts the
+combine volume (the large one: D fp32 per row) by the same factor.
 
 The reference has no multi-GPU path; the oracle for this one is the single-GPU layer on
 the concatenated tokens.  The collectives are torch.distributed (NCCL over NVLink on GPUs,
@@ -16,21 +26,28 @@ import torch.distributed as dist
 
 
 def dispatch_plan(ids, experts_per_rank, world):
-    """ids [T,K] global expert ids -> (order, send_counts).
+    """ids [T,K] global expert ids -> (send_tok, send_rank, send_counts).
 
-    ``order`` lists the (token,slot) pairs t*K+k grouped by destination rank, stable in
-    pair order inside a destination; ``send_counts[r]`` is the number of pairs going to r."""
-    dest = torch.div(ids.reshape(-1), experts_per_rank, rounding_mode="floor").to(torch.int64)
-    order = torch.argsort(dest, stable=True)
-    send_counts = torch.bincount(dest, minlength=world)
-    return order, send_counts
+    Row i of the dispatch carries token ``send_tok[i]`` to rank ``send_rank[i]``; rows are
+    grouped by destination rank and ascending in token inside a destination.
+    ``send_counts[r]`` is the number of rows going to rank r."""
+    T, K = ids.shape
+    dest = torch.div(ids.to(torch.int64), experts_per_rank, rounding_mode="floor")        # [T,K]
+    need = torch.zeros((world, T), dtype=torch.bool, device=ids.device)
+    tok = torch.arange(T, device=ids.device).repeat_interleave(K)
+    need[dest.reshape(-1), tok] = True
+    flat = need.reshape(-1).nonzero(as_tuple=False).squeeze(1)
+    send_rank = torch.div(flat, T, rounding_mode="floor")
+    send_tok = flat - send_rank * T
+    send_counts = need.sum(dim=1)
+    return send_tok, send_rank, send_counts
 
 
 class ExpertParallelMoe:
     def __init__(self, group, num_experts, top_k, route_fn, expert_fn, combine_dtype=torch.float32):
         """route_fn(xq, xs) -> (ids [T,K] int32, wts [T,K] f32) with global expert ids.
-        expert_fn(rq [R,D] u8, rs [R,D/128] f32, re [R] int32 local ids, rw [R] f32) -> y [R,D] f32
-        (already multiplied by the router weight)."""
+        expert_fn(rq [R,D] u8, rs [R,D/128] f32, rid [R,K] int32 local ids or -1, rw [R,K] f32)
+        -> y [R,D] f32: per received row the weighted sum over its valid slots."""
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -43,6 +60,26 @@ class ExpertParallelMoe:
         self.expert_fn = expert_fn
         self.combine_dtype = combine_dtype
         self.last_stats = {}
+        self._last_rid = None
+        self.profile = False          # record CUDA events between the phases of a step (GPU only)
+        self._marks = []
+
+    def recv_pairs(self):
+        """Number of (token, expert) pairs this rank computed in the last step (synchronises)."""
+        return int((self._last_rid >= 0).sum().item())
+
+    def _mark(self, name, ref):
+        if self.profile and ref.is_cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
+    def phase_ms(self):
+        """Milliseconds per phase of the last profiled step (synchronises)."""
+        if len(self._marks) < 2:
+            return {}
+        torch.cuda.synchronize()
+        return {b[0]: a[1].elapsed_time(b[1]) for a, b in zip(self._marks[:-1], self._marks[1:])}
 
     def _a2a(self, send, send_counts, recv_counts):
         out = send.new_empty((int(sum(recv_counts)),) + tuple(send.shape[1:]))
@@ -53,28 +90,65 @@ class ExpertParallelMoe:
     def forward(self, xq, xs):
         T, D = xq.shape
         K = self.K
+        self._marks = []
+        self._mark("start", xq)
         ids, wts = self.route_fn(xq, xs)
-        order, send_counts_t = dispatch_plan(ids, self.E_local, self.world)
-        recv_counts_t = torch.empty_like(send_counts_t)
-        dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
-        send_counts = send_counts_t.tolist()
-        recv_counts = recv_counts_t.tolist()
-        pair_tok = torch.div(order, K, rounding_mode="floor")
-        flat_ids = ids.reshape(-1)[order]
-        send_e = (flat_ids - torch.div(flat_ids, self.E_local, rounding_mode="floor") * self.E_local).to(torch.int32)
-        send_w = wts.reshape(-1)[order].contiguous()
-        rq = self._a2a(xq.index_select(0, pair_tok), send_counts, recv_counts)
-        rs = self._a2a(xs.index_select(0, pair_tok), send_counts, recv_counts)
-        re = self._a2a(send_e.contiguous(), send_counts, recv_counts)
-        rw = self._a2a(send_w, send_counts, recv_counts)
+        self._mark("route", xq)
+        if xq.is_cuda:
+            # one kernel: rows per destination rank, their slots in local numbering, row of (rank, token)
+            from . import ep_plan
+            W = self.world
+            send_tok_all = torch.empty((W * T,), dtype=torch.int32, device=xq.device)
+            pos = torch.empty((W, T), dtype=torch.int32, device=xq.device)
+            send_counts_t = torch.empty((W,), dtype=torch.int32, device=xq.device)
+            slot_ids = torch.empty((W * T, K), dtype=torch.int32, device=xq.device)
+            slot_w = torch.empty((W * T, K), dtype=torch.float32, device=xq.device)
+            ep_plan(ids, wts, self.E_local, W, send_tok_all, pos, send_counts_t, slot_ids, slot_w)
+            both = torch.empty((2, W), dtype=torch.int32, device=xq.device)
+            both[0] = send_counts_t
+            dist.all_to_all_single(both[1], send_counts_t, group=self.group)
+            both_h = both.tolist()                                   # the step's one host synchronisation
+            send_counts, recv_counts = both_h[0], both_h[1]
+            Rs = sum(send_counts)
+            send_tok = send_tok_all[:Rs]
+            send_id, send_w = slot_ids[:Rs], slot_w[:Rs]
+        else:
+            pos = None
+            send_tok, send_rank, send_counts_t = dispatch_plan(ids, self.E_local, self.world)
+            recv_counts_t = torch.empty_like(send_counts_t)
+            dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
+            send_counts = send_counts_t.tolist()
+            recv_counts = recv_counts_t.tolist()
+            # the K slots of every dispatched row, in the destination's local numbering
+            row_ids = ids.index_select(0, send_tok).to(torch.int64)
+            lo = (send_rank * self.E_local).unsqueeze(1)
+            mine = (row_ids >= lo) & (row_ids < lo + self.E_local)
+            send_id = torch.where(mine, row_ids - lo, torch.full_like(row_ids, -1)).to(torch.int32)
+            send_w = torch.where(mine, wts.index_select(0, send_tok),
+                                 torch.zeros((), dtype=wts.dtype, device=wts.device))
+        self._mark("plan+counts", xq)
+        rq = self._a2a(xq.index_select(0, send_tok), send_counts, recv_counts)
+        rs = self._a2a(xs.index_select(0, send_tok), send_counts, recv_counts)
+        rid = self._a2a(send_id.contiguous(), send_counts, recv_counts)
+        rw = self._a2a(send_w.contiguous(), send_counts, recv_counts)
+        self._mark("dispatch", xq)
         R = rq.shape[0]
         self.last_stats = {"recv_rows": R, "send_counts": send_counts, "recv_counts": recv_counts}
+        self._last_rid = rid
         if R > 0:
-            y = self.expert_fn(rq, rs, re, rw)
+            y = self.expert_fn(rq, rs, rid, rw)
         else:
             y = torch.zeros((0, D), dtype=torch.float32, device=xq.device)
+        self._mark("experts", xq)
         y = y.to(self.combine_dtype)
-        back = self._a2a(y, recv_counts, send_counts)            # rows come back in `order` order
-        out = torch.zeros((T, D), dtype=torch.float32, device=xq.device)
-        out.index_add_(0, pair_tok, back.to(torch.float32))
+        back = self._a2a(y, recv_counts, send_counts)            # rows come back in dispatch order
+        self._mark("combine", xq)
+        if pos is not None:
+            from . import ep_sum_rows
+            out = torch.empty((T, D), dtype=torch.float32, device=xq.device)
+            ep_sum_rows(back, pos, self.world, out)
+        else:
+            out = torch.zeros((T, D), dtype=torch.float32, device=xq.device)
+            out.index_add_(0, send_tok, back.to(torch.float32))
+        self._mark("sum", xq)
         return out, ids, wts

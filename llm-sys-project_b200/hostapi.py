@@ -56,18 +56,18 @@ class MoeFp8Layer:
         moe_route_fp8(xq, xs, self.gate_w, self.bias, ids, wts, self.cfg(T))
         return ids, wts
 
-    def local_experts(self, rq, rs, re, rw):
-        """Expert FFN for rows already dispatched to this rank: row r goes through local expert
-        re[r] and is scaled by rw[r] (one slot per row)."""
-        R = rq.shape[0]
+    def local_experts(self, rq, rs, rid, rw):
+        """Expert FFN for rows already dispatched to this rank: slot k of row r goes through local
+        expert rid[r,k] scaled by rw[r,k]; slots with rid < 0 belong to other ranks and are skipped.
+        Returns the per-row sum over the valid slots."""
+        R, K = rid.shape
         y = torch.empty((R, self.D), dtype=torch.float32, device=rq.device)
         E_local = self.w1s.shape[0]
         if self.w1p is not None:
-            moe_fp8_experts_packed(rq, rs, re.reshape(R, 1), rw.reshape(R, 1), self.w1p, self.w1s, self.w2p, self.w2s, y,
-                                   self.cfg(R, E=E_local, K=1))
+            moe_fp8_experts_packed(rq, rs, rid, rw, self.w1p, self.w1s, self.w2p, self.w2s, y,
+                                   self.cfg(R, E=E_local, K=K))
         else:
-            moe_fp8_experts(rq, rs, re.reshape(R, 1), rw.reshape(R, 1), self.w1q, self.w1s, self.w2q, self.w2s, y,
-                            self.cfg(R, E=E_local, K=1))
+            moe_fp8_experts(rq, rs, rid, rw, self.w1q, self.w1s, self.w2q, self.w2s, y, self.cfg(R, E=E_local, K=K))
         return y
 
     def forward_host(self, xq_host, xs_host, out_host):

@@ -49,26 +49,32 @@ def _worker(rank, world, port, ret):
         ids, wts = oracle.route_grouped(xq.numpy(), xs.numpy(), wg, bias, K, 4, 2, 2.5)
         return torch.from_numpy(ids), torch.from_numpy(wts)
 
-    def expert_fn(rq, rs, re, rw):
+    def expert_fn(rq, rs, rid, rw):
         R = rq.shape[0]
-        ids = re.numpy().reshape(R, 1).astype(np.int32)
+        ids = rid.numpy().astype(np.int32)
+        w = rw.numpy().astype(np.float32)
+        valid = ids >= 0
+        # slots owned by other ranks: any local expert with weight zero contributes nothing
+        ids = np.where(valid, ids, 0).astype(np.int32)
+        w = np.where(valid, w, 0.0).astype(np.float32)
         y = oracle.moe_fp8_experts(rq.numpy(), rs.numpy(), w1q[lo:lo + El], w1s[lo:lo + El], w2q[lo:lo + El],
-                                   w2s[lo:lo + El], ids, rw.numpy().reshape(R, 1), np.arange(R, dtype=np.int32))
+                                   w2s[lo:lo + El], ids, w, np.arange(R, dtype=np.int32))
         return torch.from_numpy(y)
 
     ep = b200.ExpertParallelMoe(dist.group.WORLD, E, K, route_fn, expert_fn)
     xq, xs = _tokens(rank)
     out, ids, wts = ep.forward(torch.from_numpy(xq), torch.from_numpy(xs))
-    ret[rank] = (out.numpy(), ids.numpy(), ep.last_stats["recv_rows"])
+    ret[rank] = (out.numpy(), ids.numpy(), ep.recv_pairs(), ep.last_stats["recv_rows"])
     dist.barrier()
     dist.destroy_process_group()
 
 
 def test_dispatch_plan(b200):
-    ids = torch.tensor([[0, 5], [7, 2], [4, 1]], dtype=torch.int32)
-    order, counts = b200.dispatch_plan(ids, 4, 2)
-    assert counts.tolist() == [3, 3]
-    assert order.tolist() == [0, 3, 5, 1, 2, 4]       # stable inside a destination
+    ids = torch.tensor([[0, 5], [7, 6], [1, 2]], dtype=torch.int32)
+    tok, rank, counts = b200.dispatch_plan(ids, 4, 2)
+    assert counts.tolist() == [2, 2]                  # token 0 -> both ranks, token 1 -> rank 1, token 2 -> rank 0
+    assert tok.tolist() == [0, 2, 0, 1]               # grouped by rank, ascending in token
+    assert rank.tolist() == [0, 0, 1, 1]
 
 
 def test_two_rank_ep_matches_single_rank():
@@ -84,8 +90,9 @@ def test_two_rank_ep_matches_single_rank():
         xq, xs = _tokens(rank)
         ids, wts = oracle.route_grouped(xq, xs, wg, bias, K, 4, 2, 2.5)
         ref = oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, ids, wts, np.arange(T, dtype=np.int32))
-        out, got_ids, recv = ret[rank]
+        out, got_ids, pairs, rows = ret[rank]
         assert np.array_equal(got_ids, ids)
         assert np.allclose(out, ref, rtol=1e-5, atol=1e-6)      # only the summation order over slots differs
-        total_recv += recv
+        assert rows <= world * T                                # a token goes to a rank at most once
+        total_recv += pairs
     assert total_recv == world * T * K

@@ -1,5 +1,5 @@
 """Expert-parallel layer on the GPU with a one-rank NCCL group: dispatch, local grouped GEMMs
-(one slot per received row) and combine must reproduce the plain single-GPU layer."""
+(K slots per received token) and combine must reproduce the plain single-GPU layer."""
 import os
 
 import numpy as np
@@ -39,7 +39,7 @@ def test_ep_world1_matches_plain_layer(b200, cuda):
         assert b200.device_status() == 0
         oi, ow = oracle.route_grouped(xq, xs, wg, bias, K, 4, 2, 2.5)
         assert np.array_equal(ids.cpu().numpy(), oi)
-        assert ep.last_stats["recv_rows"] == T * K
+        assert ep.last_stats["recv_rows"] == T and ep.recv_pairs() == T * K
         got = out.cpu().numpy()
         assert np.allclose(got, plain, rtol=1e-4, atol=1e-5)          # same kernels, other summation order
         ref = oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, oi, ow, np.arange(T, dtype=np.int32))
@@ -47,3 +47,52 @@ def test_ep_world1_matches_plain_layer(b200, cuda):
     finally:
         if created:
             dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("T,K,E,W", [(37, 2, 8, 2), (300, 8, 64, 8), (1500, 4, 48, 4), (5, 3, 6, 1)])
+def test_ep_plan_kernel_matches_host_plan(b200, cuda, T, K, E, W):
+    """The dispatch-plan kernel and the torch plan used on CPU produce the same rows, bit for bit."""
+    rng = np.random.default_rng(T + K)
+    ids = np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.int32)
+    wts = rng.uniform(0.1, 1, (T, K)).astype(np.float32)
+    epr = E // W
+    tok, rank, counts = b200.dispatch_plan(torch.from_numpy(ids), epr, W)
+    d_ids, d_w = torch.from_numpy(ids).to(cuda), torch.from_numpy(wts).to(cuda)
+    send_tok = torch.full((W * T,), -7, dtype=torch.int32, device=cuda)
+    pos = torch.full((W, T), -7, dtype=torch.int32, device=cuda)
+    cnt = torch.zeros((W,), dtype=torch.int32, device=cuda)
+    sid = torch.full((W * T, K), -7, dtype=torch.int32, device=cuda)
+    sw = torch.full((W * T, K), -7.0, dtype=torch.float32, device=cuda)
+    b200.ep_plan(d_ids, d_w, epr, W, send_tok, pos, cnt, sid, sw)
+    torch.cuda.synchronize()
+    assert cnt.cpu().tolist() == counts.tolist()
+    Rs = int(counts.sum())
+    assert send_tok[:Rs].cpu().tolist() == tok.tolist()
+    lo = (rank * epr).numpy()[:, None]
+    row_ids = ids[tok.numpy()]
+    mine = (row_ids >= lo) & (row_ids < lo + epr)
+    assert np.array_equal(sid[:Rs].cpu().numpy(), np.where(mine, row_ids - lo, -1))
+    assert np.array_equal(sw[:Rs].cpu().numpy(), np.where(mine, wts[tok.numpy()], 0.0).astype(np.float32))
+    want_pos = np.full((W, T), -1, dtype=np.int32)
+    want_pos[rank.numpy(), tok.numpy()] = np.arange(Rs)
+    assert np.array_equal(pos.cpu().numpy(), want_pos)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ep_sum_rows_kernel(b200, cuda, dtype):
+    rng = np.random.default_rng(5)
+    W, T, D = 3, 41, 512
+    need = rng.random((W, T)) < 0.6
+    Rs = int(need.sum())
+    pos = np.full((W, T), -1, dtype=np.int32)
+    pos[need] = np.arange(Rs)
+    back = torch.from_numpy(rng.normal(0, 1, (Rs, D)).astype(np.float32)).to(dtype)
+    out = torch.full((T, D), 9.0, dtype=torch.float32, device=cuda)
+    b200.ep_sum_rows(back.to(cuda), torch.from_numpy(pos).to(cuda), W, out)
+    want = np.zeros((T, D), dtype=np.float32)
+    b32 = back.to(torch.float32).numpy()
+    for r in range(W):                      # rank order, fp32 accumulation: bit-exact
+        for t in range(T):
+            if pos[r, t] >= 0:
+                want[t] += b32[pos[r, t]]
+    assert np.array_equal(out.cpu().numpy(), want)
