@@ -35,6 +35,8 @@ if ROOT not in sys.path:
 MOE = dict(T=4096, E=256, K=8, D=7168, I=2048, n_group=8, topk_group=4, routed_scale=2.5)
 DSA = dict(B=64, H=128, Dc=512, Dp=64, S=2048, page=64, seq_min=8192, seq_max=131072)
 ZIPF_S, ZIPF_BETA = 1.1, 0.08
+# expert e lives on GPU e mod N: a group's 32 experts (and a run of hot ones) spread over all GPUs
+EP_PLACEMENT = "strided"
 RTOL, ATOL = 2e-2, 1e-2
 
 
@@ -280,7 +282,7 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
     c = MOE
     layer, xq, xs = build_moe(b200, torch, dev, world, rank)
     ep = b200.ExpertParallelMoe(dist.group.WORLD, c["E"], c["K"], layer.route, layer.local_experts,
-                                combine_dtype=torch.bfloat16)
+                                combine_dtype=torch.bfloat16, placement=EP_PLACEMENT)
     for _ in range(max(args.warmup, 3)):
         out, ids, _ = ep.forward(xq, xs)
     torch.cuda.synchronize()
@@ -314,7 +316,8 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
     b200.moe_fp8_profile(False)
     ep.profile = False
     El = c["E"] // world
-    g1_bytes, active, rows = moe_gemm1_bytes(counts[rank * El:(rank + 1) * El])
+    g1_bytes, active, rows = moe_gemm1_bytes(counts[rank::world] if EP_PLACEMENT == "strided"
+                                             else counts[rank * El:(rank + 1) * El])
     hbm, _, which = measured_peaks()
 
     # end to end: this rank's tokens from pinned host memory, result back to pinned host memory
@@ -342,7 +345,7 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
     rr = torch.tensor([recv_rows], device=dev, dtype=torch.float32)
     rmax = rr.clone(); dist.all_reduce(rmax, op=dist.ReduceOp.MAX)
     rsum = rr.clone(); dist.all_reduce(rsum)
-    per_gpu = counts.reshape(world, -1).sum(1)
+    per_gpu = counts.reshape(-1, world).sum(0) if EP_PLACEMENT == "strided" else counts.reshape(world, -1).sum(1)
     flops_hot = 6.0 * float(rmax.item()) * c["D"] * c["I"]
     res = {
         "value": world * c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),
@@ -587,7 +590,7 @@ def main():
                            + ("C3" if world == 1 else "C5") + f": FP8 block-scale MoE layer, D={c['D']} I={c['I']} "
                            f"E={c['E']} top-{c['K']} ({c['n_group']} groups / top-{c['topk_group']}), sigmoid+bias scoring, "
                            f"routed_scaling 2.5, T={c['T']} per GPU"
-                           + ("" if world == 1 else f", experts sharded over {world} GPUs, Zipf(1.1) load"),
+                           + ("" if world == 1 else f", experts sharded over {world} GPUs ({EP_PLACEMENT} placement), Zipf(1.1) load"),
                            "tokens_per_gpu": c["T"], "parallelism": "single" if world == 1 else f"ep{world}",
                            "l2": "11.3 GB of FP8 weights stream every step (inputs > 126 MB L2)"},
                 "clocks": clocks, "gpu_launches": moe.get("gpu_launches", 0)}

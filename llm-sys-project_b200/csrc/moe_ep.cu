@@ -1,9 +1,10 @@
 // Expert-parallel helpers around the collectives (the reference has no multi-GPU path; these serve the
 // expert-sharded layer that sits on top of b200_moe_fp8_experts).
 //
-//   ep_plan_kernel      one block per destination rank: which tokens have at least one selected expert on
-//                       that rank, in ascending token order (stable), with their K slots rewritten to the
-//                       rank's local expert numbering (-1 and weight 0 for slots owned elsewhere).
+//   ep_plan_kernel      one block per destination rank (experts placed contiguously or strided over the
+//                       ranks): which tokens have at least one selected expert on that rank, in ascending
+//                       token order (stable), with their K slots rewritten to the rank's local expert
+//                       numbering (-1 and weight 0 for slots owned elsewhere).
 //   ep_sum_rows_kernel  out[t] = sum over ranks (in rank order) of the partial row that came back for
 //                       (t, rank); no atomics, no zero-fill pass.
 #include <cuda_bf16.h>
@@ -15,18 +16,22 @@ void b200_count_launch(int n);
 namespace {
 
 __global__ void __launch_bounds__(1024)
-ep_plan_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int T, int K, int epr, int W,
+ep_plan_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int T, int K, int epr, int W, int strided,
                int* __restrict__ send_tok, int* __restrict__ pos, int* __restrict__ send_counts,
                int* __restrict__ slot_ids, float* __restrict__ slot_w) {
     __shared__ int warp_sums[32];
     __shared__ int s_base;
     const int r = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // contiguous placement: expert e lives on rank e / epr as local expert e % epr;
+    // strided placement: on rank e % W as local expert e / W (spreads runs of hot experts over the ranks)
+    auto owner = [&](int id) -> int { return strided ? id % W : id / epr; };
+    auto local = [&](int id) -> int { return strided ? id / W : id % epr; };
     auto rank_mask = [&](int t) -> unsigned long long {
         unsigned long long m = 0;
         for (int k = 0; k < K; k++) {
             const int id = ids[(size_t)t * K + k];
-            if (id >= 0 && id / epr < W) m |= 1ull << (id / epr);
+            if (id >= 0 && id < epr * W) m |= 1ull << owner(id);
         }
         return m;
     };
@@ -66,8 +71,8 @@ ep_plan_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int T
                 send_tok[p] = t;
                 for (int k = 0; k < K; k++) {
                     const int id = ids[(size_t)t * K + k];
-                    const bool mine = id >= 0 && id / epr == r;
-                    slot_ids[(size_t)p * K + k] = mine ? id - r * epr : -1;
+                    const bool mine = id >= 0 && id < epr * W && owner(id) == r;
+                    slot_ids[(size_t)p * K + k] = mine ? local(id) : -1;
                     slot_w[(size_t)p * K + k] = mine ? wts[(size_t)t * K + k] : 0.0f;
                 }
             }
@@ -118,12 +123,13 @@ ep_sum_rows_kernel(const void* __restrict__ back, const int* __restrict__ pos, i
 extern "C" {
 
 int b200_ep_plan(const int* expert_ids, const float* expert_w, int T, int K, int experts_per_rank, int world,
-                 int* send_tok, int* pos, int* send_counts, int* slot_ids, float* slot_w, cudaStream_t stream) {
+                 int strided, int* send_tok, int* pos, int* send_counts, int* slot_ids, float* slot_w,
+                 cudaStream_t stream) {
     if (!expert_ids || !expert_w || !send_tok || !pos || !send_counts || !slot_ids || !slot_w) return B200_BAD_ARG;
     if (T <= 0 || K <= 0 || experts_per_rank <= 0) return B200_BAD_SHAPE;
     if (world <= 0 || world > 64) return B200_UNSUPPORTED;
-    ep_plan_kernel<<<world, 1024, 0, stream>>>(expert_ids, expert_w, T, K, experts_per_rank, world, send_tok, pos,
-                                               send_counts, slot_ids, slot_w);
+    ep_plan_kernel<<<world, 1024, 0, stream>>>(expert_ids, expert_w, T, K, experts_per_rank, world, strided ? 1 : 0,
+                                               send_tok, pos, send_counts, slot_ids, slot_w);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;

@@ -1,6 +1,6 @@
-"""Expert-parallel MoE layer: experts are split contiguously over the ranks of a
-torch.distributed process group (rank g owns experts [g*E/W, (g+1)*E/W)); tokens stay on
-their source rank.  One step is
+"""Expert-parallel MoE layer: experts are split over the ranks of a torch.distributed process
+group, contiguously (rank g owns experts [g*E/W, (g+1)*E/W)) or strided (rank g owns experts
+g, g+W, ...); tokens stay on their source rank.  One step is
 
     route (local kernel)
     -> counts all-to-all
@@ -25,14 +25,24 @@ import torch
 import torch.distributed as dist
 
 
-def dispatch_plan(ids, experts_per_rank, world):
+def expert_owner(ids, experts_per_rank, world, strided=False):
+    """Owner rank and local expert id of global expert ids: contiguous placement (expert e on rank
+    e // experts_per_rank) or strided (expert e on rank e % world, which spreads runs of hot experts)."""
+    ids = ids.to(torch.int64)
+    if strided:
+        return ids % world, torch.div(ids, world, rounding_mode="floor")
+    owner = torch.div(ids, experts_per_rank, rounding_mode="floor")
+    return owner, ids - owner * experts_per_rank
+
+
+def dispatch_plan(ids, experts_per_rank, world, strided=False):
     """ids [T,K] global expert ids -> (send_tok, send_rank, send_counts).
 
     Row i of the dispatch carries token ``send_tok[i]`` to rank ``send_rank[i]``; rows are
     grouped by destination rank and ascending in token inside a destination.
     ``send_counts[r]`` is the number of rows going to rank r."""
     T, K = ids.shape
-    dest = torch.div(ids.to(torch.int64), experts_per_rank, rounding_mode="floor")        # [T,K]
+    dest, _ = expert_owner(ids, experts_per_rank, world, strided)                          # [T,K]
     need = torch.zeros((world, T), dtype=torch.bool, device=ids.device)
     tok = torch.arange(T, device=ids.device).repeat_interleave(K)
     need[dest.reshape(-1), tok] = True
@@ -44,8 +54,11 @@ def dispatch_plan(ids, experts_per_rank, world):
 
 
 class ExpertParallelMoe:
-    def __init__(self, group, num_experts, top_k, route_fn, expert_fn, combine_dtype=torch.float32):
-        """route_fn(xq, xs) -> (ids [T,K] int32, wts [T,K] f32) with global expert ids.
+    def __init__(self, group, num_experts, top_k, route_fn, expert_fn, combine_dtype=torch.float32,
+                 placement="contiguous"):
+        """placement: "contiguous" (rank g owns experts [g*E/W, (g+1)*E/W)) or "strided" (rank g owns experts
+        g, g+W, g+2W, ... in that local order).
+        route_fn(xq, xs) -> (ids [T,K] int32, wts [T,K] f32) with global expert ids.
         expert_fn(rq [R,D] u8, rs [R,D/128] f32, rid [R,K] int32 local ids or -1, rw [R,K] f32)
         -> y [R,D] f32: per received row the weighted sum over its valid slots."""
         self.group = group
@@ -59,6 +72,9 @@ class ExpertParallelMoe:
         self.route_fn = route_fn
         self.expert_fn = expert_fn
         self.combine_dtype = combine_dtype
+        if placement not in ("contiguous", "strided"):
+            raise ValueError("placement must be 'contiguous' or 'strided'")
+        self.strided = placement == "strided"
         self.last_stats = {}
         self._last_rid = None
         self.profile = False          # record CUDA events between the phases of a step (GPU only)
@@ -103,7 +119,7 @@ class ExpertParallelMoe:
             send_counts_t = torch.empty((W,), dtype=torch.int32, device=xq.device)
             slot_ids = torch.empty((W * T, K), dtype=torch.int32, device=xq.device)
             slot_w = torch.empty((W * T, K), dtype=torch.float32, device=xq.device)
-            ep_plan(ids, wts, self.E_local, W, send_tok_all, pos, send_counts_t, slot_ids, slot_w)
+            ep_plan(ids, wts, self.E_local, W, send_tok_all, pos, send_counts_t, slot_ids, slot_w, strided=self.strided)
             both = torch.empty((2, W), dtype=torch.int32, device=xq.device)
             both[0] = send_counts_t
             dist.all_to_all_single(both[1], send_counts_t, group=self.group)
@@ -114,16 +130,16 @@ class ExpertParallelMoe:
             send_id, send_w = slot_ids[:Rs], slot_w[:Rs]
         else:
             pos = None
-            send_tok, send_rank, send_counts_t = dispatch_plan(ids, self.E_local, self.world)
+            send_tok, send_rank, send_counts_t = dispatch_plan(ids, self.E_local, self.world, self.strided)
             recv_counts_t = torch.empty_like(send_counts_t)
             dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
             send_counts = send_counts_t.tolist()
             recv_counts = recv_counts_t.tolist()
             # the K slots of every dispatched row, in the destination's local numbering
-            row_ids = ids.index_select(0, send_tok).to(torch.int64)
-            lo = (send_rank * self.E_local).unsqueeze(1)
-            mine = (row_ids >= lo) & (row_ids < lo + self.E_local)
-            send_id = torch.where(mine, row_ids - lo, torch.full_like(row_ids, -1)).to(torch.int32)
+            row_ids = ids.index_select(0, send_tok)
+            owner, local = expert_owner(row_ids, self.E_local, self.world, self.strided)
+            mine = owner == send_rank.unsqueeze(1)
+            send_id = torch.where(mine, local, torch.full_like(local, -1)).to(torch.int32)
             send_w = torch.where(mine, wts.index_select(0, send_tok),
                                  torch.zeros((), dtype=wts.dtype, device=wts.device))
         self._mark("plan+counts", xq)

@@ -4,6 +4,7 @@ import os
 import sys
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -33,7 +34,7 @@ def _tokens(rank):
     return oracle.quant_act(rng.normal(0, 1, (T, D)).astype(np.float32))
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, placement):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle
@@ -43,7 +44,7 @@ def _worker(rank, world, port, ret):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     wg, bias, w1q, w1s, w2q, w2s = _weights()
     El = E // world
-    lo = rank * El
+    mine = slice(rank * El, (rank + 1) * El) if placement == "contiguous" else slice(rank, E, world)
 
     def route_fn(xq, xs):
         ids, wts = oracle.route_grouped(xq.numpy(), xs.numpy(), wg, bias, K, 4, 2, 2.5)
@@ -57,11 +58,11 @@ def _worker(rank, world, port, ret):
         # slots owned by other ranks: any local expert with weight zero contributes nothing
         ids = np.where(valid, ids, 0).astype(np.int32)
         w = np.where(valid, w, 0.0).astype(np.float32)
-        y = oracle.moe_fp8_experts(rq.numpy(), rs.numpy(), w1q[lo:lo + El], w1s[lo:lo + El], w2q[lo:lo + El],
-                                   w2s[lo:lo + El], ids, w, np.arange(R, dtype=np.int32))
+        y = oracle.moe_fp8_experts(rq.numpy(), rs.numpy(), np.ascontiguousarray(w1q[mine]), np.ascontiguousarray(w1s[mine]),
+                                   np.ascontiguousarray(w2q[mine]), np.ascontiguousarray(w2s[mine]), ids, w, np.arange(R, dtype=np.int32))
         return torch.from_numpy(y)
 
-    ep = b200.ExpertParallelMoe(dist.group.WORLD, E, K, route_fn, expert_fn)
+    ep = b200.ExpertParallelMoe(dist.group.WORLD, E, K, route_fn, expert_fn, placement=placement)
     xq, xs = _tokens(rank)
     out, ids, wts = ep.forward(torch.from_numpy(xq), torch.from_numpy(xs))
     ret[rank] = (out.numpy(), ids.numpy(), ep.recv_pairs(), ep.last_stats["recv_rows"])
@@ -75,15 +76,21 @@ def test_dispatch_plan(b200):
     assert counts.tolist() == [2, 2]                  # token 0 -> both ranks, token 1 -> rank 1, token 2 -> rank 0
     assert tok.tolist() == [0, 2, 0, 1]               # grouped by rank, ascending in token
     assert rank.tolist() == [0, 0, 1, 1]
+    tok, rank, counts = b200.dispatch_plan(ids, 4, 2, strided=True)      # even experts on rank 0, odd on rank 1
+    assert counts.tolist() == [3, 3]
+    assert tok.tolist() == [0, 1, 2, 0, 1, 2]
+    owner, local = b200.expert_owner(ids, 4, 2, strided=True)
+    assert owner.tolist() == [[0, 1], [1, 0], [1, 0]] and local.tolist() == [[0, 2], [3, 3], [0, 1]]
 
 
-def test_two_rank_ep_matches_single_rank():
+@pytest.mark.parametrize("placement", ["contiguous", "strided"])
+def test_two_rank_ep_matches_single_rank(placement):
     import oracle
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + os.getpid() % 2000
-    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    port = 29500 + os.getpid() % 2000 + (7 if placement == "strided" else 0)
+    mp.spawn(_worker, args=(world, port, ret, placement), nprocs=world, join=True)
     wg, bias, w1q, w1s, w2q, w2s = _weights()
     total_recv = 0
     for rank in range(world):
