@@ -365,24 +365,26 @@ done:
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
 }
 
-// Expert-sorted copy of the FP8 rows.  One block per sorted row.
+// Expert-sorted copy of the FP8 rows.  One block per sorted row, grid-stride (the number of valid
+// rows is only known on the device: slots owned by other ranks are not rows).
 __global__ void __launch_bounds__(128)
 sort_rows_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, const int* __restrict__ row_pair,
                      const int* __restrict__ offsets, const float* __restrict__ wts, int E, int K, int D,
                      uint8_t* __restrict__ sq, float* __restrict__ ss, int* __restrict__ row_tok,
                      float* __restrict__ row_w) {
-    const int r = blockIdx.x;
-    if (r >= offsets[E]) return;
-    const int pair = row_pair[r];
-    const int tok = pair / K;
-    const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)tok * D);
-    uint4* dst = reinterpret_cast<uint4*>(sq + (size_t)r * D);
-    for (int i = threadIdx.x; i < D / 16; i += blockDim.x) dst[i] = src[i];
+    const int total = offsets[E];
     const int nb = D / 128;
-    for (int i = threadIdx.x; i < nb; i += blockDim.x) ss[(size_t)r * nb + i] = xs[(size_t)tok * nb + i];
-    if (threadIdx.x == 0) {
-        row_tok[r] = tok;
-        row_w[r] = wts[pair];
+    for (int r = blockIdx.x; r < total; r += gridDim.x) {
+        const int pair = row_pair[r];
+        const int tok = pair / K;
+        const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)tok * D);
+        uint4* dst = reinterpret_cast<uint4*>(sq + (size_t)r * D);
+        for (int i = threadIdx.x; i < D / 16; i += blockDim.x) dst[i] = src[i];
+        for (int i = threadIdx.x; i < nb; i += blockDim.x) ss[(size_t)r * nb + i] = xs[(size_t)tok * nb + i];
+        if (threadIdx.x == 0) {
+            row_tok[r] = tok;
+            row_w[r] = wts[pair];
+        }
     }
 }
 
@@ -463,7 +465,8 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     // ids from this library's router are trusted (hist given); ids from outside get the duplicate check
     int st = launch_permute(ids, T, K, E, hist, hist != nullptr, s.counts, s.offsets, s.row_pair, stream);
     if (st) return st;
-    sort_rows_fp8_kernel<<<(unsigned)TK, 128, 0, stream>>>(xq, xs, s.row_pair, s.offsets, wts, E, K, D, s.sq, s.ss,
+    const unsigned sort_blocks = (unsigned)(TK < (long long)ws->sm_count * 32 ? TK : (long long)ws->sm_count * 32);
+    sort_rows_fp8_kernel<<<sort_blocks, 128, 0, stream>>>(xq, xs, s.row_pair, s.offsets, wts, E, K, D, s.sq, s.ss,
                                                            s.row_tok, s.row_w);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());

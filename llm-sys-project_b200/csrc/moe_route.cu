@@ -285,15 +285,35 @@ __device__ __forceinline__ bool pair_selects(const int* __restrict__ ids, int p,
     return true;
 }
 
-// One block per expert.  The expert's first row (= rows owned by lower experts) comes from the
-// router's histogram when it is given, otherwise from a counting pass; ranks inside the expert are
-// assigned by a block scan over (token, slot) pairs in ascending order, four pairs per thread.
-// CHECK_DUP: a token that lists the expert twice counts once (ids supplied from outside).
+// Per-expert counts of the (token, slot) pairs that select it (ids outside [0,E) and, with CHECK_DUP,
+// repeated ids of a token are not counted): shared-memory histogram per block, flushed with atomics.
 template <bool CHECK_DUP>
 __global__ void __launch_bounds__(256)
+pair_histogram_kernel(const int* __restrict__ ids, int TK, int K, int E, int* __restrict__ counts) {
+    extern __shared__ int s_hist[];
+    for (int i = threadIdx.x; i < E; i += blockDim.x) s_hist[i] = 0;
+    __syncthreads();
+    for (int p = blockIdx.x * blockDim.x + threadIdx.x; p < TK; p += gridDim.x * blockDim.x) {
+        const int id = ids[p];
+        if (id >= 0 && id < E && (!CHECK_DUP || pair_selects(ids, p, K, id))) atomicAdd(&s_hist[id], 1);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < E; i += blockDim.x)
+        if (s_hist[i]) atomicAdd(&counts[i], s_hist[i]);
+}
+
+// One block per expert.  The expert's first row (= rows owned by lower experts) comes from the
+// per-expert counts (the router's histogram, or pair_histogram_kernel for routing supplied from
+// outside); ranks inside the expert are assigned by a block scan over (token, slot) pairs in
+// ascending order, four pairs per thread, 4096 pairs per round.
+// CHECK_DUP: a token that lists the expert twice counts once (ids supplied from outside).
+constexpr int PERMUTE_THREADS = 1024;
+template <bool CHECK_DUP>
+__global__ void __launch_bounds__(PERMUTE_THREADS)
 permute_kernel(const int* __restrict__ ids, int TK, int K, int E, const int* __restrict__ counts_in,
                int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ row_pair) {
-    __shared__ int warp_sums[8];
+    constexpr int NW = PERMUTE_THREADS / 32;
+    __shared__ int warp_sums[NW];
     __shared__ int s_base;
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -303,27 +323,20 @@ permute_kernel(const int* __restrict__ ids, int TK, int K, int E, const int* __r
         return true;
     };
     int lt = 0;
-    if (counts_in) {
-        for (int i = threadIdx.x; i < e; i += 256) lt += counts_in[i];
-    } else {
-        for (int p = threadIdx.x; p < TK; p += 256) {
-            int id = ids[p];
-            if (id >= 0 && id < e && selects(p, id, id)) lt++;
-        }
-    }
+    for (int i = threadIdx.x; i < e; i += PERMUTE_THREADS) lt += counts_in[i];
     for (int o = 16; o > 0; o >>= 1) lt += __shfl_xor_sync(0xffffffffu, lt, o);
     if (lane == 0) warp_sums[warp] = lt;
     __syncthreads();
     if (threadIdx.x == 0) {
         int tot = 0;
-        for (int w = 0; w < 8; w++) tot += warp_sums[w];
+        for (int w = 0; w < NW; w++) tot += warp_sums[w];
         s_base = tot;
     }
     __syncthreads();
     const int base = s_base;
     const bool vec = (TK % 4 == 0) && ((reinterpret_cast<uintptr_t>(ids) & 15) == 0);
     int running = 0;
-    for (int p0 = 0; p0 < TK; p0 += 1024) {
+    for (int p0 = 0; p0 < TK; p0 += PERMUTE_THREADS * 4) {
         const int p = p0 + threadIdx.x * 4;
         int v[4] = {-1, -1, -1, -1};
         if (vec) {
@@ -350,7 +363,7 @@ permute_kernel(const int* __restrict__ ids, int TK, int K, int E, const int* __r
         if (lane == 31) warp_sums[warp] = incl;
         __syncthreads();
         int before = 0, total = 0;
-        for (int w = 0; w < 8; w++) {
+        for (int w = 0; w < NW; w++) {
             int n = warp_sums[w];
             if (w < warp) before += n;
             total += n;
@@ -409,8 +422,19 @@ int launch_route_select(const float* partials, int n_chunks, const float* bias, 
 
 int launch_permute(const int* ids, int T, int K, int E, const int* counts_in, bool trusted, int* counts,
                    int* offsets, int* row_pair, cudaStream_t stream) {
-    if (trusted) permute_kernel<false><<<E, 256, 0, stream>>>(ids, T * K, K, E, counts_in, counts, offsets, row_pair);
-    else         permute_kernel<true><<<E, 256, 0, stream>>>(ids, T * K, K, E, counts_in, counts, offsets, row_pair);
+    const int TK = T * K;
+    if (!counts_in) {
+        // no histogram from the router: count first (all SMs), then every expert's block knows its base
+        B200_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * (size_t)E, stream));
+        const int blocks = max(1, min((TK + 1023) / 1024, 1184));
+        if (trusted) pair_histogram_kernel<false><<<blocks, 256, sizeof(int) * (size_t)E, stream>>>(ids, TK, K, E, counts);
+        else         pair_histogram_kernel<true><<<blocks, 256, sizeof(int) * (size_t)E, stream>>>(ids, TK, K, E, counts);
+        b200_count_launch(1);
+        B200_CUDA_TRY(cudaGetLastError());
+        counts_in = counts;       // each block rewrites its own entry with the same value at the end
+    }
+    if (trusted) permute_kernel<false><<<E, PERMUTE_THREADS, 0, stream>>>(ids, TK, K, E, counts_in, counts, offsets, row_pair);
+    else         permute_kernel<true><<<E, PERMUTE_THREADS, 0, stream>>>(ids, TK, K, E, counts_in, counts, offsets, row_pair);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
