@@ -235,15 +235,30 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     g1_ms, g2_ms, ncalls = b200.moe_fp8_profile_read()
     b200.moe_fp8_profile(False)
 
-    # end to end through the host-facing layer call: pinned host in, pinned host out
+    # end to end through the host-facing layer call: pinned host in, pinned host out, every step.
+    # Synchronous call first (one step at a time), then the double-buffered call a serving loop uses:
+    # the copies of steps n-1 / n+1 run on their own streams under the kernels of step n.
     xq_h, xs_h = xq.cpu().pin_memory(), xs.cpu().pin_memory()
-    out_h = torch.empty((c["T"], c["D"]), dtype=torch.float32).pin_memory()
+    out_hs = [torch.empty((c["T"], c["D"]), dtype=torch.float32).pin_memory() for _ in range(2)]
+    out_h = out_hs[0]
     for _ in range(2):
         layer.forward_host(xq_h, xs_h, out_h)
     t0 = time.perf_counter()
     for _ in range(args.steps):
         layer.forward_host(xq_h, xs_h, out_h)
+    e2e_sync_s = (time.perf_counter() - t0) / args.steps
+    for i in range(3):
+        tk = layer.forward_host_async(xq_h, xs_h, out_hs[i % 2])
+    tk.synchronize()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        tk = layer.forward_host_async(xq_h, xs_h, out_hs[i % 2])
+    tk.synchronize()
+    torch.cuda.synchronize()
     e2e_s = (time.perf_counter() - t0) / args.steps
+    # both buffers hold a result of the same input (the scatter-add order differs from run to run)
+    e2e_same = bool(torch.allclose(out_hs[0][:64], out_hs[1][:64], rtol=1e-4, atol=1e-5))
 
     threads = oracle.max_threads()
     cpu = moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out, args.cpu_tokens, threads)
@@ -253,7 +268,11 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     res = {
         "value": c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),
         "e2e": {"value": c["T"] / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(xq_h.numel() + xs_h.numel() * 4),
-                "d2h_bytes_per_step": int(out_h.numel() * 4), "ms_per_step": e2e_s * 1e3},
+                "d2h_bytes_per_step": int(out_h.numel() * 4), "ms_per_step": e2e_s * 1e3,
+                "mode": "double-buffered host pipeline (MoeFp8Layer.forward_host_async): every step copies its "
+                        "inputs in and its result out; copies overlap the neighbouring steps' kernels",
+                "synchronous_value": c["T"] / e2e_sync_s, "synchronous_ms_per_step": e2e_sync_s * 1e3,
+                "results_agree_across_buffers": e2e_same},
         "roofline": {"kernel": "grouped_gemm_fp8<1> (GEMM1+SwiGLU+requant)", "bound": "hbm",
                      "achieved": g1_bytes / (g1_ms * 1e-3) / 1e9 if g1_ms > 0 else None, "peak": hbm, "unit": "GB/s",
                      "frac": (g1_bytes / (g1_ms * 1e-3) / 1e9 / hbm) if g1_ms > 0 else None,
@@ -320,24 +339,27 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
                                              else counts[rank * El:(rank + 1) * El])
     hbm, _, which = measured_peaks()
 
-    # end to end: this rank's tokens from pinned host memory, result back to pinned host memory
+    # end to end: this rank's tokens from pinned host memory, result back to pinned host memory, every
+    # step, through the double-buffered host pipeline (copies overlap the neighbouring steps' kernels)
     xq_h, xs_h = xq.cpu().pin_memory(), xs.cpu().pin_memory()
-    out_h = torch.empty((c["T"], c["D"]), dtype=torch.float32).pin_memory()
-    dq, ds = torch.empty_like(xq), torch.empty_like(xs)
+    out_hs = [torch.empty((c["T"], c["D"]), dtype=torch.float32).pin_memory() for _ in range(2)]
+    out_h = out_hs[0]
+    pipe = b200.HostPipeline(dev)
 
-    def e2e_step():
-        dq.copy_(xq_h, non_blocking=True)
-        ds.copy_(xs_h, non_blocking=True)
+    def ep_compute(dq, ds, do):
         o, _, _ = ep.forward(dq, ds)
-        out_h.copy_(o, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        do.copy_(o)
 
-    for _ in range(2):
-        e2e_step()
+    for i in range(3):
+        tk = pipe.submit([xq_h, xs_h], out_hs[i % 2], ep_compute)
+    tk.synchronize()
+    torch.cuda.synchronize()
     dist.barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
+    for i in range(args.steps):
+        tk = pipe.submit([xq_h, xs_h], out_hs[i % 2], ep_compute)
+    tk.synchronize()
+    torch.cuda.synchronize()
     dist.barrier()
     te = torch.tensor([(time.perf_counter() - t0) / args.steps], device=dev, dtype=torch.float64)
     dist.all_reduce(te, op=dist.ReduceOp.MAX)
@@ -351,7 +373,8 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
         "value": world * c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),
         "e2e": {"value": world * c["T"] / e2e_s, "unit": "tokens/s",
                 "h2d_bytes_per_step": int(world * (xq_h.numel() + xs_h.numel() * 4)),
-                "d2h_bytes_per_step": int(world * out_h.numel() * 4), "ms_per_step": e2e_s * 1e3},
+                "d2h_bytes_per_step": int(world * out_h.numel() * 4), "ms_per_step": e2e_s * 1e3,
+                "mode": "double-buffered host pipeline (HostPipeline around ExpertParallelMoe.forward)"},
         "roofline": {"kernel": "grouped_gemm_fp8<1> (GEMM1+SwiGLU+requant) on rank 0", "bound": "hbm",
                      "achieved": g1_bytes / (g1_ms * 1e-3) / 1e9 if g1_ms > 0 else None, "peak": hbm, "unit": "GB/s",
                      "frac": (g1_bytes / (g1_ms * 1e-3) / 1e9 / hbm) if g1_ms > 0 else None,
@@ -447,16 +470,29 @@ def bench_dsa(b200, torch, oracle, dev, args, sampler, do_cpu):
     if do_cpu:
         qn_h, qp_h = qn.cpu().pin_memory(), qp.cpu().pin_memory()
         idx_h = [i.cpu().pin_memory() for i in idx_sets]
-        out_h = torch.empty(out.shape, dtype=torch.float32).pin_memory()
+        out_hs = [torch.empty(out.shape, dtype=torch.float32).pin_memory() for _ in range(2)]
+        out_h = out_hs[0]
         for i in range(2):
             layer.forward_host(qn_h, qp_h, idx_h[i], out_h)
         t0 = time.perf_counter()
         for i in range(steps):
             layer.forward_host(qn_h, qp_h, idx_h[i % 4], out_h)
+        e2e_sync_us = (time.perf_counter() - t0) / steps * 1e6
+        for i in range(3):
+            tk = layer.forward_host_async(qn_h, qp_h, idx_h[i % 4], out_hs[i % 2])
+        tk.synchronize()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(steps):
+            tk = layer.forward_host_async(qn_h, qp_h, idx_h[i % 4], out_hs[i % 2])
+        tk.synchronize()
+        torch.cuda.synchronize()
         e2e_us = (time.perf_counter() - t0) / steps * 1e6
         res["e2e"] = {"value": e2e_us, "unit": "us/step",
                       "h2d_bytes_per_step": int(qn_h.numel() * 2 + qp_h.numel() * 2 + idx_h[0].numel() * 4),
-                      "d2h_bytes_per_step": int(out_h.numel() * 4)}
+                      "d2h_bytes_per_step": int(out_h.numel() * 4),
+                      "mode": "double-buffered host pipeline (DsaDecodeLayer.forward_host_async)",
+                      "synchronous_value": e2e_sync_us}
         # CPU oracle on a sample of queries (rows gathered on the device, computed on the host)
         nq = args.cpu_queries
         idx = idx_sets[0][:nq].long()

@@ -338,4 +338,4 @@ def umma_selftest(mode, a, b, d, N, K, stream=None):
 
 
 from .ep import ExpertParallelMoe, dispatch_plan, expert_owner  # noqa: E402,F401
-from .hostapi import MoeFp8Layer, DsaDecodeLayer  # noqa: E402,F401
+from .hostapi import MoeFp8Layer, DsaDecodeLayer, HostPipeline  # noqa: E402,F401

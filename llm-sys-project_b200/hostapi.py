@@ -1,10 +1,71 @@
 """Layer objects a serving loop would hold: weights / caches stay resident in HBM, one
 ``forward_host`` call moves a step's inputs from pinned host memory, runs the CUDA path and
-brings the result back (the end-to-end path the benchmark times)."""
+brings the result back (the end-to-end path the benchmark times).  ``forward_host_async`` is the
+same call without the final wait: steps are double-buffered on the device, so the input copy of
+step n+1 and the output copy of step n-1 run on their own streams under the kernels of step n
+(PCIe traffic, not the kernels, bounds a synchronous call)."""
 import torch
 
 from . import (DsaConfig, MoeFp8Config, SCORE_SIGMOID_GROUPED, dsa_forward_bf16, moe_fp8_experts,
                moe_fp8_experts_packed, moe_fp8_forward, moe_fp8_forward_packed, moe_fp8_pack_weights, moe_route_fp8)
+
+
+class HostPipeline:
+    """Double-buffered host <-> device staging around a device computation.
+
+    ``submit(host_inputs, host_output, compute)`` copies the pinned host inputs into the next
+    slot's device buffers on a copy-in stream, runs ``compute(*device_inputs, device_output)`` on
+    the caller's current stream once they have arrived, and copies the result to ``host_output``
+    on a copy-out stream.  A slot is reused only after its previous computation has consumed the
+    inputs and its previous output copy has finished (events, no host synchronisation).  The host
+    buffers of a step must stay untouched until ``wait(ticket)`` returns."""
+
+    def __init__(self, device, depth=2):
+        self.device = device
+        self.depth = depth
+        self.s_in = torch.cuda.Stream(device=device)
+        self.s_out = torch.cuda.Stream(device=device)
+        self.slots = {}
+        self.turn = 0
+
+    def _slot(self, key, host_inputs, host_output):
+        if key not in self.slots:
+            mk = lambda h: torch.empty(h.shape, dtype=h.dtype, device=self.device)
+            self.slots[key] = [{"in": [mk(h) for h in host_inputs], "out": mk(host_output),
+                                "consumed": None, "copied_out": None} for _ in range(self.depth)]
+        slot = self.slots[key][self.turn % self.depth]
+        self.turn += 1
+        return slot
+
+    def submit(self, host_inputs, host_output, compute):
+        key = tuple((tuple(h.shape), h.dtype) for h in host_inputs) + (tuple(host_output.shape),)
+        slot = self._slot(key, host_inputs, host_output)
+        main = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self.s_in):
+            if slot["consumed"] is not None:
+                self.s_in.wait_event(slot["consumed"])         # the slot's previous computation read its inputs
+            for d, h in zip(slot["in"], host_inputs):
+                d.copy_(h, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record(self.s_in)
+        main.wait_event(arrived)
+        if slot["copied_out"] is not None:
+            main.wait_event(slot["copied_out"])                # the slot's previous result has left the device
+        compute(*slot["in"], slot["out"])
+        done = torch.cuda.Event()
+        done.record(main)
+        slot["consumed"] = done
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(done)
+            host_output.copy_(slot["out"], non_blocking=True)
+            left = torch.cuda.Event()
+            left.record(self.s_out)
+        slot["copied_out"] = left
+        return left
+
+    @staticmethod
+    def wait(ticket):
+        ticket.synchronize()
 
 
 class MoeFp8Layer:
@@ -20,6 +81,7 @@ class MoeFp8Layer:
         self.scoring, self.n_group, self.topk_group, self.routed_scale = scoring, n_group, topk_group, routed_scale
         self.w1p = self.w2p = None
         self._dev = {}
+        self._pipe = None
 
     def pack(self, free_unpacked=False):
         """Pre-tile the weights (one contiguous 32 KB block per tile and K block) so the grouped GEMMs
@@ -87,6 +149,14 @@ class MoeFp8Layer:
         torch.cuda.current_stream().synchronize()
         return out_host
 
+    def forward_host_async(self, xq_host, xs_host, out_host):
+        """Same as forward_host but returns at once with a ticket; `HostPipeline.wait(ticket)` (or
+        `ticket.synchronize()`) returns when out_host holds the result.  Consecutive calls overlap their
+        host copies with each other's kernels."""
+        if self._pipe is None:
+            self._pipe = HostPipeline(self.gate_w.device)
+        return self._pipe.submit([xq_host, xs_host], out_host, lambda dq, ds, do: self.forward(dq, ds, do))
+
 
 class DsaDecodeLayer:
     """bf16 sparse MLA decode (dsa_forward, kernels/dsa/naive_dsa.cu:435-474) over caches resident in HBM."""
@@ -95,6 +165,7 @@ class DsaDecodeLayer:
         self.kc, self.kp, self.v = kc, kp, v
         self.page_size = page_size
         self._dev = {}
+        self._pipe = None
 
     def cfg(self, Q, H, S):
         return DsaConfig(Q, H, self.kc.shape[1], self.kp.shape[1], S, self.page_size, self.kc.shape[0])
@@ -122,3 +193,10 @@ class DsaDecodeLayer:
         out_host.copy_(do, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return out_host
+
+    def forward_host_async(self, qn_host, qp_host, idx_host, out_host):
+        """forward_host without the final wait (see MoeFp8Layer.forward_host_async)."""
+        if self._pipe is None:
+            self._pipe = HostPipeline(self.kc.device)
+        return self._pipe.submit([qn_host, qp_host, idx_host], out_host,
+                                 lambda dn, dp, di, do: self.forward(dn, dp, di, do))

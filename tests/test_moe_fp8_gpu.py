@@ -194,3 +194,28 @@ def test_packed_weights_layout_and_equivalence(b200, cuda):
     ids, wts = oracle.route_grouped(xq, xs, wg, bias, K, 2, 1, 2.5)
     ref = oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, ids, wts, np.arange(T, dtype=np.int32))
     assert not (np.abs(out_b.cpu().numpy() - ref) > ATOL + RTOL * np.abs(ref)).any()
+
+
+def test_host_pipeline_matches_synchronous_call(b200, cuda):
+    """forward_host_async (double-buffered copies on side streams) returns what forward_host returns,
+    for several different batches in flight at once."""
+    rng = np.random.default_rng(21)
+    T, E, K, D, I = 64, 8, 2, 256, 128
+    x, wg, bias, w1, w2, xq, xs, w1q, w1s, w2q, w2s = _layer(rng, T, E, D, I)
+    layer = b200.MoeFp8Layer(_dev(wg, cuda), _dev(bias, cuda), _dev(w1q, cuda), _dev(w1s, cuda), _dev(w2q, cuda),
+                             _dev(w2s, cuda), K, b200.SCORE_SIGMOID_GROUPED, 2, 1, 2.5)
+    batches = []
+    for i in range(5):
+        q, s = oracle.quant_act(rng.normal(0, 1, (T, D)).astype(np.float32))
+        batches.append((torch.from_numpy(q).pin_memory(), torch.from_numpy(s).pin_memory()))
+    want = []
+    for q, s in batches:
+        o = torch.empty((T, D), dtype=torch.float32).pin_memory()
+        layer.forward_host(q, s, o)
+        want.append(o.clone())
+    outs = [torch.empty((T, D), dtype=torch.float32).pin_memory() for _ in batches]
+    tickets = [layer.forward_host_async(q, s, o) for (q, s), o in zip(batches, outs)]
+    for t in tickets:
+        b200.HostPipeline.wait(t)
+    for w, o in zip(want, outs):
+        assert torch.allclose(w, o, rtol=1e-5, atol=1e-6)      # scatter-add order may differ between runs
