@@ -381,6 +381,115 @@ permute_kernel(const int* __restrict__ ids, int TK, int K, int E, const int* __r
     }
 }
 
+// FP8 router logits, tuned variant of the kernel above for aligned inputs (rows 16-byte aligned,
+// D % 16 == 0, chunk % 16 == 0).  Same arithmetic, hence the same bits: every logit is one fused
+// multiply-add chain over the chunk's d in ascending order.  Differences: the token tile is
+// 8 * TY rows (TY = 8..16, 16 * TY threads) so that the launcher can pick the height whose tile
+// count fills whole waves of resident CTAs, and the next k-tile is fetched into registers while
+// the current one is multiplied.
+template <int TY>
+__global__ void __launch_bounds__(16 * TY, 512 / (16 * TY))
+gate_logits_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, const float* __restrict__ wg,
+                       float* __restrict__ partials, int T, int E, int D, int chunk) {
+    constexpr int TM = 8 * TY, NT = 16 * TY, LDA = TM + 4;
+    constexpr int BREP = (GL_TN * 4 + NT - 1) / NT;          // float4 loads of the expert tile per thread
+    __shared__ __align__(16) float As[GL_TK][LDA];
+    __shared__ __align__(16) float Bs[GL_TK][GL_LD];
+    const int t0 = blockIdx.x * TM, e0 = blockIdx.y * GL_TN, c = blockIdx.z;
+    const int d_begin = c * chunk;
+    const int d_end = min(D, d_begin + chunk);
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // tx -> 8 experts, ty -> 8 tokens
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+
+    uint4 a_raw = make_uint4(0, 0, 0, 0);
+    float a_sc = 0.0f;
+    float4 b_reg[BREP];
+    const int nb = D / 128;
+    auto fetch = [&](int d0) {
+        if (threadIdx.x < TM) {
+            const int t = t0 + threadIdx.x;
+            if (t < T) {
+                a_raw = *reinterpret_cast<const uint4*>(xq + (size_t)t * D + d0);
+                a_sc = xs[(size_t)t * nb + d0 / 128];
+            } else {
+                a_raw = make_uint4(0, 0, 0, 0);
+                a_sc = 0.0f;
+            }
+        }
+#pragma unroll
+        for (int rep = 0; rep < BREP; rep++) {
+            const int idx = threadIdx.x + rep * NT, r = idx >> 2, kq = (idx & 3) * 4;
+            b_reg[rep] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (idx < GL_TN * 4 && e0 + r < E) b_reg[rep] = *reinterpret_cast<const float4*>(wg + (size_t)(e0 + r) * D + d0 + kq);
+        }
+    };
+    auto stage = [&]() {
+        if (threadIdx.x < TM) {
+            const uint8_t* b = reinterpret_cast<const uint8_t*>(&a_raw);
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                __nv_fp8_e4m3 q;
+                q.__x = b[i];
+                As[i][threadIdx.x] = __fmul_rn(float(q), a_sc);
+            }
+        }
+#pragma unroll
+        for (int rep = 0; rep < BREP; rep++) {
+            const int idx = threadIdx.x + rep * NT, r = idx >> 2, kq = (idx & 3) * 4;
+            if (idx < GL_TN * 4) {
+                Bs[kq][r] = b_reg[rep].x; Bs[kq + 1][r] = b_reg[rep].y;
+                Bs[kq + 2][r] = b_reg[rep].z; Bs[kq + 3][r] = b_reg[rep].w;
+            }
+        }
+    };
+    fetch(d_begin);
+    for (int d0 = d_begin; d0 < d_end; d0 += GL_TK) {
+        stage();
+        __syncthreads();
+        if (d0 + GL_TK < d_end) fetch(d0 + GL_TK);
+#pragma unroll 4
+        for (int k = 0; k < GL_TK; k++) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[k][ty * 8]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[k][ty * 8 + 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[k][tx * 8]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[k][tx * 8 + 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int t = t0 + ty * 8 + i;
+        if (t >= T) continue;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int e = e0 + tx * 8 + j;
+            if (e < E) partials[((size_t)c * T + t) * E + e] = acc[i][j];
+        }
+    }
+}
+
+template <int TY>
+static int gate_fp8_try(int want_ty, int& blocks_per_sm) {
+    if (want_ty != TY) return 0;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, gate_logits_fp8_kernel<TY>, 16 * TY, 0);
+    return 1;
+}
+template <int TY>
+static void gate_fp8_launch(dim3 grid, cudaStream_t stream, const void* x, const float* xs, const float* wg,
+                            float* partials, int T, int E, int D, int chunk) {
+    gate_logits_fp8_kernel<TY><<<grid, 16 * TY, 0, stream>>>(static_cast<const uint8_t*>(x), xs, wg, partials, T, E, D, chunk);
+}
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
@@ -389,12 +498,55 @@ int moe_gate_chunks(int D, bool fp8) { return fp8 ? ceil_div(D, MOE_GATE_CHUNK) 
 int launch_gate_logits(const void* x, const float* xs, const float* wg, float* partials, int T, int E, int D,
                        bool fp8, cudaStream_t stream) {
     int chunk = fp8 ? MOE_GATE_CHUNK : D;
-    dim3 grid(ceil_div(T, GL_TM), ceil_div(E, GL_TN), moe_gate_chunks(D, fp8));
+    const int n_chunks = moe_gate_chunks(D, fp8);
     const bool vec = (D % 16 == 0) && (chunk % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(wg) & 15) == 0);
+    if (fp8 && vec) {
+        // Pick the token-tile height (8 * TY rows) whose tile count wastes the least of the machine:
+        // tiles come in waves of (SMs x resident CTAs); cost ~ waves x rows per tile.
+        static int sms = 0;
+        static int occ[17] = {0};
+        if (!sms) {
+            int dev = 0;
+            B200_CUDA_TRY(cudaGetDevice(&dev));
+            B200_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+            for (int ty = 8; ty <= 16; ty++) {
+                int b = 0;
+                gate_fp8_try<8>(ty, b) || gate_fp8_try<9>(ty, b) || gate_fp8_try<10>(ty, b) || gate_fp8_try<11>(ty, b) ||
+                    gate_fp8_try<12>(ty, b) || gate_fp8_try<13>(ty, b) || gate_fp8_try<14>(ty, b) ||
+                    gate_fp8_try<15>(ty, b) || gate_fp8_try<16>(ty, b);
+                occ[ty] = b > 0 ? b : 1;
+            }
+        }
+        int best_ty = 16;
+        double best_cost = 1e300;
+        for (int ty = 16; ty >= 8; ty--) {
+            const long long tiles = (long long)ceil_div(T, 8 * ty) * ceil_div(E, GL_TN) * n_chunks;
+            const long long slots = (long long)sms * occ[ty];
+            const long long waves = (tiles + slots - 1) / slots;
+            // a wave of occ[ty] CTAs of 16*ty threads keeps the FMA pipes busy for ~ occ * ty units of time
+            const double cost = (double)waves * occ[ty] * ty;
+            if (cost < best_cost * 0.999) { best_cost = cost; best_ty = ty; }
+        }
+        dim3 grid(ceil_div(T, 8 * best_ty), ceil_div(E, GL_TN), n_chunks);
+        switch (best_ty) {
+            case 8:  gate_fp8_launch<8>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+            case 9:  gate_fp8_launch<9>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+            case 10: gate_fp8_launch<10>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+            case 11: gate_fp8_launch<11>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+            case 12: gate_fp8_launch<12>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+            case 13: gate_fp8_launch<13>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+            case 14: gate_fp8_launch<14>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+            case 15: gate_fp8_launch<15>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+            default: gate_fp8_launch<16>(grid, stream, x, xs, wg, partials, T, E, D, chunk); break;
+        }
+        b200_count_launch(1);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
+    dim3 grid(ceil_div(T, GL_TM), ceil_div(E, GL_TN), n_chunks);
     if (fp8) {
-        if (vec) gate_logits_kernel<true, true><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
-        else     gate_logits_kernel<true, false><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
+        gate_logits_kernel<true, false><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
     } else {
         if (vec) gate_logits_kernel<false, true><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
         else     gate_logits_kernel<false, false><<<grid, 256, 0, stream>>>(x, xs, wg, partials, T, E, D, chunk);
