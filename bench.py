@@ -571,8 +571,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-dsa", action="store_true")
     ap.add_argument("--skip-moe", action="store_true")
-    ap.add_argument("--cpu-tokens", type=int, default=24)
-    ap.add_argument("--cpu-queries", type=int, default=4)
+    ap.add_argument("--cpu-tokens", type=int, default=96)
+    ap.add_argument("--cpu-queries", type=int, default=16)
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized case of the same kernels (32 experts, 512 tokens; 16 queries, short caches): "
                          "inputs still exceed L2 but only ~2 GB live on the device; not a bench value")
