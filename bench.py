@@ -235,6 +235,46 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     g1_ms, g2_ms, ncalls = b200.moe_fp8_profile_read()
     b200.moe_fp8_profile(False)
 
+    # the same layer at the other token counts the workload is swept over (device-resident inputs)
+    sweep = {}
+    for Ts in (1, 16, 128, 1024):
+        if Ts >= c["T"]:
+            continue
+        xq_s, xs_s = xq[:Ts].contiguous(), xs[:Ts].contiguous()
+        out_s = torch.empty((Ts, c["D"]), dtype=torch.float32, device=dev)
+        for _ in range(3):
+            layer.forward(xq_s, xs_s, out_s)
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(10):
+            layer.forward(xq_s, xs_s, out_s)
+        s1.record()
+        torch.cuda.synchronize()
+        ms_s = s0.elapsed_time(s1) / 10
+        sweep[str(Ts)] = {"ms_per_step": ms_s, "tokens_per_s": Ts / (ms_s * 1e-3)}
+        # small batches are launch-bound from Python: the same call replayed from a CUDA graph
+        try:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                layer.forward(xq_s, xs_s, out_s)
+            torch.cuda.current_stream().wait_stream(side)
+            with torch.cuda.graph(graph):
+                layer.forward(xq_s, xs_s, out_s)
+            for _ in range(3):
+                graph.replay()
+            s0.record()
+            for _ in range(10):
+                graph.replay()
+            s1.record()
+            torch.cuda.synchronize()
+            sweep[str(Ts)]["ms_per_step_cuda_graph"] = s0.elapsed_time(s1) / 10
+            del graph
+        except Exception as exc:                      # capture is an extra, never a reason to lose the run
+            sweep[str(Ts)]["cuda_graph_error"] = str(exc)[:120]
+            torch.cuda.synchronize()
+
     # end to end through the host-facing layer call: pinned host in, pinned host out, every step.
     # Synchronous call first (one step at a time), then the double-buffered call a serving loop uses:
     # the copies of steps n-1 / n+1 run on their own streams under the kernels of step n.
@@ -279,7 +319,7 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
                      "traffic": int(g1_bytes * TRAFFIC_RATIO["gemm1"]),
                      "peak_source": which, "kernel_ms": g1_ms, "algorithmic_bytes": int(g1_bytes),
                      "launches_timed": ncalls},
-        "kernels": {"gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "other_ms": ms - g1_ms - g2_ms,
+        "kernels": {"gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "other_ms": ms - g1_ms - g2_ms, "token_sweep": sweep,
                     "layer_bytes": int(moe_layer_bytes(counts)),
                     "layer_hbm_gbs": moe_layer_bytes(counts) / (ms * 1e-3) / 1e9,
                     "layer_tflops": flops / (ms * 1e-3) / 1e12,

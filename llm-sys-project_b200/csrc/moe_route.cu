@@ -478,6 +478,56 @@ gate_logits_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__
     }
 }
 
+// FP8 router logits for decode-sized batches (T <= 32): the register-tiled kernels above would run
+// 14 CTAs of mostly padding.  Block = 32 experts x one chunk of d; thread = (expert, token slot);
+// every logit is still one fused multiply-add chain over the chunk's d in ascending order, so the
+// bits are those of the other kernels.  k-tiles of 128 d are double-buffered in shared memory.
+constexpr int GS_E = 32, GS_K = 128, GS_T = 8;
+__global__ void __launch_bounds__(GS_E * GS_T)
+gate_logits_fp8_small_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, const float* __restrict__ wg,
+                             float* __restrict__ partials, int T, int E, int D, int chunk) {
+    __shared__ float w_s[2][GS_E][GS_K + 1];
+    __shared__ float x_s[2][GS_T][GS_K];
+    const int e0 = blockIdx.x * GS_E, c = blockIdx.y;
+    const int d_begin = c * chunk, d_end = min(D, d_begin + chunk);
+    const int el = threadIdx.x & 31, ts = threadIdx.x >> 5;
+    const int nb = D / 128;
+    for (int t0 = 0; t0 < T; t0 += GS_T) {
+        auto stage = [&](int buf, int d0) {
+            // expert tile: 32 rows x 128 floats, coalesced along d; token tile: up to 8 rows, dequantised
+            for (int i = threadIdx.x; i < GS_E * GS_K; i += GS_E * GS_T) {
+                const int r = i / GS_K, k = i - r * GS_K;
+                w_s[buf][r][k] = (e0 + r < E && d0 + k < d_end) ? wg[(size_t)(e0 + r) * D + d0 + k] : 0.0f;
+            }
+            for (int i = threadIdx.x; i < GS_T * GS_K; i += GS_E * GS_T) {
+                const int r = i / GS_K, k = i - r * GS_K, t = t0 + r;
+                float v = 0.0f;
+                if (t < T && d0 + k < d_end) {
+                    __nv_fp8_e4m3 q;
+                    q.__x = xq[(size_t)t * D + d0 + k];
+                    v = __fmul_rn(float(q), xs[(size_t)t * nb + (d0 + k) / 128]);
+                }
+                x_s[buf][r][k] = v;
+            }
+        };
+        float acc = 0.0f;
+        int buf = 0;
+        stage(0, d_begin);
+        __syncthreads();
+        for (int d0 = d_begin; d0 < d_end; d0 += GS_K) {
+            if (d0 + GS_K < d_end) stage(buf ^ 1, d0 + GS_K);
+            const int kmax = min(GS_K, d_end - d0);
+#pragma unroll 8
+            for (int k = 0; k < kmax; k++) acc = __fmaf_rn(x_s[buf][ts][k], w_s[buf][el][k], acc);
+            __syncthreads();
+            buf ^= 1;
+        }
+        const int t = t0 + ts, e = e0 + el;
+        if (t < T && e < E) partials[((size_t)c * T + t) * E + e] = acc;
+        __syncthreads();
+    }
+}
+
 template <int TY>
 static int gate_fp8_try(int want_ty, int& blocks_per_sm) {
     if (want_ty != TY) return 0;
@@ -501,6 +551,14 @@ int launch_gate_logits(const void* x, const float* xs, const float* wg, float* p
     const int n_chunks = moe_gate_chunks(D, fp8);
     const bool vec = (D % 16 == 0) && (chunk % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
                      ((reinterpret_cast<uintptr_t>(wg) & 15) == 0);
+    if (fp8 && T <= 32 && D % 128 == 0) {
+        dim3 grid(ceil_div(E, GS_E), n_chunks);
+        gate_logits_fp8_small_kernel<<<grid, GS_E * GS_T, 0, stream>>>(static_cast<const uint8_t*>(x), xs, wg, partials,
+                                                                      T, E, D, chunk);
+        b200_count_launch(1);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
     if (fp8 && vec) {
         // Pick the token-tile height (8 * TY rows) whose tile count wastes the least of the machine:
         // tiles come in waves of (SMs x resident CTAs); cost ~ waves x rows per tile.
