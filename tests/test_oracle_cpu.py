@@ -36,7 +36,7 @@ def test_dsa_oracle_matches_reference_cpu(name):
     assert np.array_equal(out, DSA[f"dsa/{name}/out"])
 
 
-def test_survey_anchor_values():
+def test_reference_anchor_values():
     # values obtained by running the reference CPU code on its "medium" MoE and "small" DSA cases
     out = MOE["moe/medium/out"]
     assert abs(out.sum(dtype=np.float64) - 3.924888641e-01) < 1e-9
