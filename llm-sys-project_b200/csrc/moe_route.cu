@@ -582,8 +582,9 @@ int launch_gate_logits(const void* x, const float* xs, const float* wg, float* p
             const long long tiles = (long long)ceil_div(T, 8 * ty) * ceil_div(E, GL_TN) * n_chunks;
             const long long slots = (long long)sms * occ[ty];
             const long long waves = (tiles + slots - 1) / slots;
-            // a wave of occ[ty] CTAs of 16*ty threads keeps the FMA pipes busy for ~ occ * ty units of time
-            const double cost = (double)waves * occ[ty] * ty;
+            // a full wave of occ[ty] CTAs of 16*ty threads keeps an SM's FMA pipes busy for ~ occ * ty units of
+            // time; when everything fits in one wave an SM works through its ceil(tiles / SMs) CTAs
+            const double cost = (tiles <= slots) ? (double)((tiles + sms - 1) / sms) * ty : (double)waves * occ[ty] * ty;
             if (cost < best_cost * 0.999) { best_cost = cost; best_ty = ty; }
         }
         dim3 grid(ceil_div(T, 8 * best_ty), ceil_div(E, GL_TN), n_chunks);
