@@ -35,8 +35,9 @@ if ROOT not in sys.path:
 MOE = dict(T=4096, E=256, K=8, D=7168, I=2048, n_group=8, topk_group=4, routed_scale=2.5)
 DSA = dict(B=64, H=128, Dc=512, Dp=64, S=2048, page=64, seq_min=8192, seq_max=131072)
 ZIPF_S, ZIPF_BETA = 1.1, 0.08
-# expert e lives on GPU e mod N: a group's 32 experts (and a run of hot ones) spread over all GPUs
-EP_PLACEMENT = "strided"
+# "strided": expert e lives on GPU e mod N (a group's 32 experts and a run of hot ones spread over all GPUs);
+# "balanced": greedy placement by the expert loads of a calibration batch; "contiguous": blocks of E/N experts
+EP_PLACEMENT = os.environ.get("B200_EP_PLACEMENT", "balanced")
 RTOL, ATOL = 2e-2, 1e-2
 
 
@@ -361,8 +362,21 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
 def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
     c = MOE
     layer, xq, xs = build_moe(b200, torch, dev, world, rank)
+    placement = EP_PLACEMENT
+    if EP_PLACEMENT == "balanced":
+        # expert loads of a calibration batch (other tokens than the timed ones) decide the placement
+        xc = torch.empty((c["T"], c["D"]), dtype=torch.float32, device=dev)
+        b200.fill_normal_(xc, 9000 + rank, 1.0)
+        cq = torch.empty((c["T"], c["D"]), dtype=torch.uint8, device=dev)
+        cs = torch.empty((c["T"], c["D"] // 128), dtype=torch.float32, device=dev)
+        b200.quant_act_1x128(xc, cq, cs)
+        cal_ids, _ = layer.route(cq, cs)
+        cal = torch.bincount(cal_ids.reshape(-1).long(), minlength=c["E"])
+        dist.all_reduce(cal)
+        placement = b200.balanced_placement(cal.cpu(), world)
+        del xc, cq, cs
     ep = b200.ExpertParallelMoe(dist.group.WORLD, c["E"], c["K"], layer.route, layer.local_experts,
-                                combine_dtype=torch.bfloat16, placement=EP_PLACEMENT)
+                                combine_dtype=torch.bfloat16, placement=placement)
     for _ in range(max(args.warmup, 3)):
         out, ids, _ = ep.forward(xq, xs)
     torch.cuda.synchronize()
@@ -396,8 +410,11 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
     b200.moe_fp8_profile(False)
     ep.profile = False
     El = c["E"] // world
-    g1_bytes, active, rows = moe_gemm1_bytes(counts[rank::world] if EP_PLACEMENT == "strided"
-                                             else counts[rank * El:(rank + 1) * El])
+    if EP_PLACEMENT == "balanced":
+        local_counts = counts[placement[0].numpy() == rank]
+    else:
+        local_counts = counts[rank::world] if EP_PLACEMENT == "strided" else counts[rank * El:(rank + 1) * El]
+    g1_bytes, active, rows = moe_gemm1_bytes(local_counts)
     hbm, _, which = measured_peaks()
 
     # end to end: this rank's tokens from pinned host memory, result back to pinned host memory, every
@@ -428,7 +445,11 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
     rr = torch.tensor([recv_rows], device=dev, dtype=torch.float32)
     rmax = rr.clone(); dist.all_reduce(rmax, op=dist.ReduceOp.MAX)
     rsum = rr.clone(); dist.all_reduce(rsum)
-    per_gpu = counts.reshape(-1, world).sum(0) if EP_PLACEMENT == "strided" else counts.reshape(world, -1).sum(1)
+    if EP_PLACEMENT == "balanced":
+        own = placement[0].numpy()
+        per_gpu = np.array([counts[own == g].sum() for g in range(world)])
+    else:
+        per_gpu = counts.reshape(-1, world).sum(0) if EP_PLACEMENT == "strided" else counts.reshape(world, -1).sum(1)
     flops_hot = 6.0 * float(rmax.item()) * c["D"] * c["I"]
     res = {
         "value": world * c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),

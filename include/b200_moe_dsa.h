@@ -234,13 +234,14 @@ B200_API int b200_dsa_output_proj_f32(const float* attn, const float* g_v, float
 /* --------------------------------------------------------------------------- */
 /* Dispatch plan for `world` ranks owning experts_per_rank experts each: consecutive ones (strided = 0: expert e on
  * rank e / experts_per_rank, local id e % experts_per_rank) or every world-th one (strided = 1: expert e on rank
- * e % world, local id e / world; spreads a run of hot experts over the ranks). From the
+ * e % world, local id e / world; spreads a run of hot experts over the ranks), or any assignment given by
+ * owner_map / local_map [world * experts_per_rank] (both NULL or both set; they override `strided`). From the
  * routing (ids/weights [T,K], global ids) it writes, rank-major and ascending in token inside a
  * rank: send_tok [<= world*T] token of each dispatched row; slot_ids / slot_w [<= world*T, K] the
  * row's K slots in the destination's local numbering (-1 / 0 for slots owned elsewhere);
  * send_counts [world]; pos [world, T] the dispatched row of (rank, token) or -1. */
 B200_API int b200_ep_plan(const int* expert_ids, const float* expert_w, int T, int K, int experts_per_rank,
-                          int world, int strided, int* send_tok, int* pos, int* send_counts, int* slot_ids, float* slot_w,
+                          int world, int strided, const int* owner_map, const int* local_map, int* send_tok, int* pos, int* send_counts, int* slot_ids, float* slot_w,
                           b200_stream_t stream);
 /* out[t,:] = sum over ranks r with pos[r,t] >= 0, in rank order, of back[pos[r,t],:]; out [T,D] fp32 is
  * overwritten; back holds fp32 rows or, with back_is_bf16 != 0, bf16 rows.  D % 8 == 0. */

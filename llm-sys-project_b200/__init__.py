@@ -200,10 +200,10 @@ def moe_fp8_gemm1_stage(xq, xs, expert_ids, w1q, w1s, act_q, act_s, offsets, row
 
 
 def ep_plan(expert_ids, expert_w, experts_per_rank, world, send_tok, pos, send_counts, slot_ids, slot_w, strided=False,
-            stream=None):
+            owner_map=None, local_map=None, stream=None):
     T, K = expert_ids.shape
     _check(lib().b200_ep_plan(_p(expert_ids), _p(expert_w), T, K, int(experts_per_rank), int(world),
-                              1 if strided else 0, _p(send_tok),
+                              1 if strided else 0, _p(owner_map), _p(local_map), _p(send_tok),
                               _p(pos), _p(send_counts), _p(slot_ids), _p(slot_w), _stream(stream)), "ep_plan")
 
 
@@ -337,5 +337,5 @@ def umma_selftest(mode, a, b, d, N, K, stream=None):
            "umma_selftest")
 
 
-from .ep import ExpertParallelMoe, dispatch_plan, expert_owner  # noqa: E402,F401
+from .ep import ExpertParallelMoe, balanced_placement, dispatch_plan, expert_owner  # noqa: E402,F401
 from .hostapi import MoeFp8Layer, DsaDecodeLayer, HostPipeline  # noqa: E402,F401

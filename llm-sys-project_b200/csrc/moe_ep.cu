@@ -17,16 +17,17 @@ namespace {
 
 __global__ void __launch_bounds__(1024)
 ep_plan_kernel(const int* __restrict__ ids, const float* __restrict__ wts, int T, int K, int epr, int W, int strided,
-               int* __restrict__ send_tok, int* __restrict__ pos, int* __restrict__ send_counts,
+               const int* __restrict__ owner_map, const int* __restrict__ local_map, int* __restrict__ send_tok, int* __restrict__ pos, int* __restrict__ send_counts,
                int* __restrict__ slot_ids, float* __restrict__ slot_w) {
     __shared__ int warp_sums[32];
     __shared__ int s_base;
     const int r = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     // contiguous placement: expert e lives on rank e / epr as local expert e % epr;
-    // strided placement: on rank e % W as local expert e / W (spreads runs of hot experts over the ranks)
-    auto owner = [&](int id) -> int { return strided ? id % W : id / epr; };
-    auto local = [&](int id) -> int { return strided ? id / W : id % epr; };
+    // strided placement: on rank e % W as local expert e / W (spreads runs of hot experts over the ranks);
+    // mapped placement: owner_map[e] / local_map[e] (any assignment, e.g. balanced by measured load)
+    auto owner = [&](int id) -> int { return owner_map ? owner_map[id] : (strided ? id % W : id / epr); };
+    auto local = [&](int id) -> int { return local_map ? local_map[id] : (strided ? id / W : id % epr); };
     auto rank_mask = [&](int t) -> unsigned long long {
         unsigned long long m = 0;
         for (int k = 0; k < K; k++) {
@@ -123,13 +124,14 @@ ep_sum_rows_kernel(const void* __restrict__ back, const int* __restrict__ pos, i
 extern "C" {
 
 int b200_ep_plan(const int* expert_ids, const float* expert_w, int T, int K, int experts_per_rank, int world,
-                 int strided, int* send_tok, int* pos, int* send_counts, int* slot_ids, float* slot_w,
-                 cudaStream_t stream) {
+                 int strided, const int* owner_map, const int* local_map, int* send_tok, int* pos, int* send_counts,
+                 int* slot_ids, float* slot_w, cudaStream_t stream) {
     if (!expert_ids || !expert_w || !send_tok || !pos || !send_counts || !slot_ids || !slot_w) return B200_BAD_ARG;
     if (T <= 0 || K <= 0 || experts_per_rank <= 0) return B200_BAD_SHAPE;
     if (world <= 0 || world > 64) return B200_UNSUPPORTED;
+    if ((owner_map == nullptr) != (local_map == nullptr)) return B200_BAD_ARG;
     ep_plan_kernel<<<world, 1024, 0, stream>>>(expert_ids, expert_w, T, K, experts_per_rank, world, strided ? 1 : 0,
-                                               send_tok, pos, send_counts, slot_ids, slot_w);
+                                               owner_map, local_map, send_tok, pos, send_counts, slot_ids, slot_w);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;

@@ -25,24 +25,47 @@ import torch
 import torch.distributed as dist
 
 
-def expert_owner(ids, experts_per_rank, world, strided=False):
+def balanced_placement(counts, world):
+    """Greedy load-balanced expert placement from per-expert row counts of a calibration batch: experts
+    in descending load go to the least loaded rank that still has room (every rank gets E / world experts).
+    Returns (owner [E], local [E]) int32 tensors; rank g's local expert j is the j-th expert assigned to it."""
+    counts = torch.as_tensor(counts).to(torch.int64).cpu()
+    E = counts.numel()
+    cap = E // world
+    load = [0] * world
+    used = [0] * world
+    owner = torch.empty(E, dtype=torch.int32)
+    local = torch.empty(E, dtype=torch.int32)
+    order = sorted(range(E), key=lambda e: (-int(counts[e]), e))
+    for e in order:
+        g = min((r for r in range(world) if used[r] < cap), key=lambda r: (load[r], r))
+        owner[e], local[e] = g, used[g]
+        used[g] += 1
+        load[g] += int(counts[e])
+    return owner, local
+
+
+def expert_owner(ids, experts_per_rank, world, strided=False, maps=None):
     """Owner rank and local expert id of global expert ids: contiguous placement (expert e on rank
-    e // experts_per_rank) or strided (expert e on rank e % world, which spreads runs of hot experts)."""
+    e // experts_per_rank), strided (expert e on rank e % world, which spreads runs of hot experts) or
+    mapped (maps = (owner [E], local [E]) tensors)."""
     ids = ids.to(torch.int64)
+    if maps is not None:
+        return maps[0].to(ids.device).to(torch.int64)[ids], maps[1].to(ids.device).to(torch.int64)[ids]
     if strided:
         return ids % world, torch.div(ids, world, rounding_mode="floor")
     owner = torch.div(ids, experts_per_rank, rounding_mode="floor")
     return owner, ids - owner * experts_per_rank
 
 
-def dispatch_plan(ids, experts_per_rank, world, strided=False):
+def dispatch_plan(ids, experts_per_rank, world, strided=False, maps=None):
     """ids [T,K] global expert ids -> (send_tok, send_rank, send_counts).
 
     Row i of the dispatch carries token ``send_tok[i]`` to rank ``send_rank[i]``; rows are
     grouped by destination rank and ascending in token inside a destination.
     ``send_counts[r]`` is the number of rows going to rank r."""
     T, K = ids.shape
-    dest, _ = expert_owner(ids, experts_per_rank, world, strided)                          # [T,K]
+    dest, _ = expert_owner(ids, experts_per_rank, world, strided, maps)                    # [T,K]
     need = torch.zeros((world, T), dtype=torch.bool, device=ids.device)
     tok = torch.arange(T, device=ids.device).repeat_interleave(K)
     need[dest.reshape(-1), tok] = True
@@ -56,8 +79,9 @@ def dispatch_plan(ids, experts_per_rank, world, strided=False):
 class ExpertParallelMoe:
     def __init__(self, group, num_experts, top_k, route_fn, expert_fn, combine_dtype=torch.float32,
                  placement="contiguous"):
-        """placement: "contiguous" (rank g owns experts [g*E/W, (g+1)*E/W)) or "strided" (rank g owns experts
-        g, g+W, g+2W, ... in that local order).
+        """placement: "contiguous" (rank g owns experts [g*E/W, (g+1)*E/W)), "strided" (rank g owns experts
+        g, g+W, g+2W, ... in that local order) or a pair (owner [E], local [E]) of int32 tensors, e.g. from
+        balanced_placement(); the caller shards the weights accordingly.
         route_fn(xq, xs) -> (ids [T,K] int32, wts [T,K] f32) with global expert ids.
         expert_fn(rq [R,D] u8, rs [R,D/128] f32, rid [R,K] int32 local ids or -1, rw [R,K] f32)
         -> y [R,D] f32: per received row the weighted sum over its valid slots."""
@@ -72,9 +96,17 @@ class ExpertParallelMoe:
         self.route_fn = route_fn
         self.expert_fn = expert_fn
         self.combine_dtype = combine_dtype
-        if placement not in ("contiguous", "strided"):
-            raise ValueError("placement must be 'contiguous' or 'strided'")
+        self.maps = None
+        if isinstance(placement, (tuple, list)):
+            owner, local = placement
+            if owner.numel() != num_experts or local.numel() != num_experts:
+                raise ValueError("placement maps must have one entry per expert")
+            self.maps = (owner.to(torch.int32).contiguous(), local.to(torch.int32).contiguous())
+            placement = "mapped"
+        elif placement not in ("contiguous", "strided"):
+            raise ValueError("placement must be 'contiguous', 'strided' or (owner, local) tensors")
         self.strided = placement == "strided"
+        self._dev_maps = None
         self.last_stats = {}
         self._last_rid = None
         self.profile = False          # record CUDA events between the phases of a step (GPU only)
@@ -119,7 +151,11 @@ class ExpertParallelMoe:
             send_counts_t = torch.empty((W,), dtype=torch.int32, device=xq.device)
             slot_ids = torch.empty((W * T, K), dtype=torch.int32, device=xq.device)
             slot_w = torch.empty((W * T, K), dtype=torch.float32, device=xq.device)
-            ep_plan(ids, wts, self.E_local, W, send_tok_all, pos, send_counts_t, slot_ids, slot_w, strided=self.strided)
+            if self.maps is not None and self._dev_maps is None:
+                self._dev_maps = (self.maps[0].to(xq.device), self.maps[1].to(xq.device))
+            om, lm = self._dev_maps if self._dev_maps is not None else (None, None)
+            ep_plan(ids, wts, self.E_local, W, send_tok_all, pos, send_counts_t, slot_ids, slot_w, strided=self.strided,
+                    owner_map=om, local_map=lm)
             both = torch.empty((2, W), dtype=torch.int32, device=xq.device)
             both[0] = send_counts_t
             dist.all_to_all_single(both[1], send_counts_t, group=self.group)
@@ -130,14 +166,14 @@ class ExpertParallelMoe:
             send_id, send_w = slot_ids[:Rs], slot_w[:Rs]
         else:
             pos = None
-            send_tok, send_rank, send_counts_t = dispatch_plan(ids, self.E_local, self.world, self.strided)
+            send_tok, send_rank, send_counts_t = dispatch_plan(ids, self.E_local, self.world, self.strided, self.maps)
             recv_counts_t = torch.empty_like(send_counts_t)
             dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
             send_counts = send_counts_t.tolist()
             recv_counts = recv_counts_t.tolist()
             # the K slots of every dispatched row, in the destination's local numbering
             row_ids = ids.index_select(0, send_tok)
-            owner, local = expert_owner(row_ids, self.E_local, self.world, self.strided)
+            owner, local = expert_owner(row_ids, self.E_local, self.world, self.strided, self.maps)
             mine = owner == send_rank.unsqueeze(1)
             send_id = torch.where(mine, local, torch.full_like(local, -1)).to(torch.int32)
             send_w = torch.where(mine, wts.index_select(0, send_tok),

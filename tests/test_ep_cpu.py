@@ -11,6 +11,7 @@ import torch.multiprocessing as mp
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 T, E, K, D, I = 24, 8, 2, 256, 128
+BALANCE_COUNTS = [9, 1, 7, 3, 2, 8, 4, 6]       # calibration loads for the balanced-placement case
 
 
 def _make(seed):
@@ -44,7 +45,15 @@ def _worker(rank, world, port, ret, placement):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     wg, bias, w1q, w1s, w2q, w2s = _weights()
     El = E // world
-    mine = slice(rank * El, (rank + 1) * El) if placement == "contiguous" else slice(rank, E, world)
+    if placement == "balanced":
+        maps = b200.balanced_placement(np.array(BALANCE_COUNTS), world)
+        mine = np.zeros(El, dtype=np.int64)
+        for e in range(E):
+            if int(maps[0][e]) == rank:
+                mine[int(maps[1][e])] = e
+        placement = maps
+    else:
+        mine = slice(rank * El, (rank + 1) * El) if placement == "contiguous" else slice(rank, E, world)
 
     def route_fn(xq, xs):
         ids, wts = oracle.route_grouped(xq.numpy(), xs.numpy(), wg, bias, K, 4, 2, 2.5)
@@ -83,13 +92,28 @@ def test_dispatch_plan(b200):
     assert owner.tolist() == [[0, 1], [1, 0], [1, 0]] and local.tolist() == [[0, 2], [3, 3], [0, 1]]
 
 
-@pytest.mark.parametrize("placement", ["contiguous", "strided"])
+def test_balanced_placement():
+    import torch
+    from conftest import load_package
+    b200 = load_package()
+    counts = [100, 1, 1, 1, 50, 50, 2, 3]
+    owner, local = b200.balanced_placement(counts, 2)
+    assert sorted(owner.tolist()) == [0] * 4 + [1] * 4                  # equal number of experts per rank
+    for g in range(2):
+        assert sorted(local[owner == g].tolist()) == [0, 1, 2, 3]       # local ids are a permutation
+    load = [sum(c for c, o in zip(counts, owner.tolist()) if o == g) for g in range(2)]
+    assert max(load) <= 105                                             # of 208 rows: the hot expert does not share with the next two
+    o2, l2 = b200.expert_owner(torch.tensor([[0, 4]]), 4, 2, maps=(owner, local))
+    assert o2.tolist() == [[int(owner[0]), int(owner[4])]] and l2.tolist() == [[int(local[0]), int(local[4])]]
+
+
+@pytest.mark.parametrize("placement", ["contiguous", "strided", "balanced"])
 def test_two_rank_ep_matches_single_rank(placement):
     import oracle
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29500 + os.getpid() % 2000 + (7 if placement == "strided" else 0)
+    port = 29500 + os.getpid() % 2000 + {"contiguous": 0, "strided": 7, "balanced": 13}[placement]
     mp.spawn(_worker, args=(world, port, ret, placement), nprocs=world, join=True)
     wg, bias, w1q, w1s, w2q, w2s = _weights()
     total_recv = 0

@@ -49,7 +49,7 @@ def test_ep_world1_matches_plain_layer(b200, cuda):
             dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("strided", [False, True])
+@pytest.mark.parametrize("strided", [False, True, "mapped"])
 @pytest.mark.parametrize("T,K,E,W", [(37, 2, 8, 2), (300, 8, 64, 8), (1500, 4, 48, 4), (5, 3, 6, 1)])
 def test_ep_plan_kernel_matches_host_plan(b200, cuda, T, K, E, W, strided):
     """The dispatch-plan kernel and the torch plan used on CPU produce the same rows, bit for bit."""
@@ -57,20 +57,25 @@ def test_ep_plan_kernel_matches_host_plan(b200, cuda, T, K, E, W, strided):
     ids = np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.int32)
     wts = rng.uniform(0.1, 1, (T, K)).astype(np.float32)
     epr = E // W
-    tok, rank, counts = b200.dispatch_plan(torch.from_numpy(ids), epr, W, strided)
+    maps = None
+    if strided == "mapped":
+        maps = b200.balanced_placement(rng.integers(0, 1000, E), W)
+        strided = False
+    tok, rank, counts = b200.dispatch_plan(torch.from_numpy(ids), epr, W, strided, maps)
     d_ids, d_w = torch.from_numpy(ids).to(cuda), torch.from_numpy(wts).to(cuda)
     send_tok = torch.full((W * T,), -7, dtype=torch.int32, device=cuda)
     pos = torch.full((W, T), -7, dtype=torch.int32, device=cuda)
     cnt = torch.zeros((W,), dtype=torch.int32, device=cuda)
     sid = torch.full((W * T, K), -7, dtype=torch.int32, device=cuda)
     sw = torch.full((W * T, K), -7.0, dtype=torch.float32, device=cuda)
-    b200.ep_plan(d_ids, d_w, epr, W, send_tok, pos, cnt, sid, sw, strided=strided)
+    b200.ep_plan(d_ids, d_w, epr, W, send_tok, pos, cnt, sid, sw, strided=strided,
+                 owner_map=None if maps is None else maps[0].to(cuda), local_map=None if maps is None else maps[1].to(cuda))
     torch.cuda.synchronize()
     assert cnt.cpu().tolist() == counts.tolist()
     Rs = int(counts.sum())
     assert send_tok[:Rs].cpu().tolist() == tok.tolist()
     row_ids = ids[tok.numpy()]
-    owner, local = b200.expert_owner(torch.from_numpy(row_ids), epr, W, strided)
+    owner, local = b200.expert_owner(torch.from_numpy(row_ids), epr, W, strided, maps)
     mine = owner.numpy() == rank.numpy()[:, None]
     assert np.array_equal(sid[:Rs].cpu().numpy(), np.where(mine, local.numpy(), -1))
     assert np.array_equal(sw[:Rs].cpu().numpy(), np.where(mine, wts[tok.numpy()], 0.0).astype(np.float32))
