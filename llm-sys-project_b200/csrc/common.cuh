@@ -62,6 +62,17 @@ static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 // ---------------------------------------------------------------------------
 // Device-side PTX wrappers
 // ---------------------------------------------------------------------------
+// Function attributes (dynamic shared-memory limits) belong to a device: a process that drives several
+// GPUs has to set them once per device, not once per process.  Returns true the first time it is called
+// for the current device with a given flag array (64 entries, zero-initialised static storage).
+static inline bool b200_first_call_on_device(bool* done_by_device) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return true;
+    if (done_by_device[dev]) return false;
+    done_by_device[dev] = true;
+    return true;
+}
+
 namespace ptx {
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

@@ -407,11 +407,10 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
         }
         return B200_OK;
     }
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[64] = {false};
+    if (b200_first_call_on_device(attr_done)) {
         B200_CUDA_TRY(cudaFuncSetAttribute(dsa_decode_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)DSA_SMEM_BYTES));
-        attr_done = true;
     }
     DsaParams p;
     p.q_nope = reinterpret_cast<const __nv_bfloat16*>(q_nope);

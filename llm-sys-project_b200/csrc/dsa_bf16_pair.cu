@@ -870,13 +870,12 @@ extern "C" __attribute__((visibility("default"))) void b200_debug_dsa_trace(long
 int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, const void* kp, const void* v,
                          const int* idx, float* out, float* part_o, float* part_ml, int* status, int Q, int H, int S,
                          int NS, int tiles_per_split, int tile_rows, cudaStream_t stream) {
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[64] = {false};
+    if (b200_first_call_on_device(attr_done)) {
         B200_CUDA_TRY(cudaFuncSetAttribute(pair::dsa_decode_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)pair::SMEM_BYTES));
         B200_CUDA_TRY(cudaFuncSetAttribute(pair::t128::dsa_decode_pair128_kernel,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pair::t128::SMEM_BYTES));
-        attr_done = true;
     }
     pair::Params p;
     p.q_nope = static_cast<const __nv_bfloat16*>(q_nope);

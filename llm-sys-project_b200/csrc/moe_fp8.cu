@@ -471,13 +471,12 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
 
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[64] = {false};
+    if (b200_first_call_on_device(attr_done)) {
         B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)GEMM_SMEM_BYTES));
         B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)GEMM_SMEM_BYTES));
-        attr_done = true;
     }
     CUtensorMap ta, tb;
     GemmParams p{};
