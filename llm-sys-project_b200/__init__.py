@@ -12,7 +12,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libb200moedsa.so")
+# B200_LIBRARY points at another build of the same library (A/B runs of two builds on one machine)
+LIB_PATH = os.environ.get("B200_LIBRARY") or os.path.join(_HERE, "lib", "libb200moedsa.so")
 _lib = None
 
 (B200_OK, B200_BAD_SHAPE, B200_UNSUPPORTED, B200_CUDA_ERROR, B200_TIMEOUT, B200_NCCL_ERROR,

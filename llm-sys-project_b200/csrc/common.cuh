@@ -114,14 +114,43 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 #ifndef B200_WAIT_LIMIT_NS
 #define B200_WAIT_LIMIT_NS 2000000000ull   // 2 s
 #endif
+// Bounded wait.  The clock is not read on the way in: reading %globaltimer takes hundreds of cycles when
+// several warps of a scheduler do it at once, and a waiter that is busy reading it notices a completed
+// phase that much later.  The deadline starts at the first clock reading (every 1024 failed polls).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    uint64_t t0 = globaltimer_ns();
+    uint64_t t0 = 0;
     uint32_t it = 0;
     while (!mbar_try_wait(bar, parity)) {
+        if (((++it) & 1023u) == 0) {
+            if (*abort_flag) return false;
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > B200_WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+
+// Same, for a waiter that can afford to react late (a producer several stages ahead): it sleeps between
+// polls so that its polling does not take issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned sleep_ns) {
+    if (mbar_try_wait(bar, parity)) return true;
+    uint64_t t0 = 0;
+    uint32_t it = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(sleep_ns);
         if (((++it) & 255u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > B200_WAIT_LIMIT_NS) {
+            const uint64_t now = globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > B200_WAIT_LIMIT_NS) {
                 *abort_flag = 1;
                 return false;
             }

@@ -100,12 +100,18 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 }
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
-    uint64_t t0 = ptx::globaltimer_ns();
+    uint64_t t0 = 0;                       // the clock is read every 1024 failed polls only (see ptx::mbar_wait)
     uint32_t it = 0;
     while (!mbar_try_wait_cluster(bar, parity)) {
-        if (((++it) & 255u) == 0) {
+        if (((++it) & 1023u) == 0) {
             if (*abort_flag) return false;
-            if (ptx::globaltimer_ns() - t0 > B200_WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+            const uint64_t now = ptx::globaltimer_ns();
+            if (t0 == 0) {
+                t0 = now;
+            } else if (now - t0 > B200_WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                return false;
+            }
         }
     }
     return true;

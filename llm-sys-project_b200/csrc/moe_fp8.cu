@@ -14,8 +14,11 @@
 // GEMM structure (one CTA per SM, tiles 128 x 256 x 128 handed out round-robin, expert-major):
 //   warp 8      TMA producer: A tile (128 rows x 128 B) and B tile (256 rows x 128 B) per
 //               K block into a 4-stage shared-memory ring (128-byte swizzle, K-major).
-//   warp 9      MMA issuer: 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block into one
-//               of two 256-column TMEM accumulator stages, started fresh for every K block.
+//   warps 9,10  MMA issuers, one per 256-column TMEM accumulator stage (K blocks alternate between
+//               them): 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block, started fresh for
+//               every K block.  Everything that waits next to the promotion warps sleeps between
+//               polls: a warp that spins, or that sits in an MMA issue blocked on a full tensor
+//               queue, takes the scheduler away from the two promotion warps that share it.
 //   warps 0-7   promotion + epilogue: tcgen05.ld the K block's partial sums and fold them
 //               into fp32 registers with a_scale[row,kb] * w_scale[nblk,kb] (the scales are
 //               arbitrary fp32 values, so the scaling cannot be left to the tensor core).
@@ -34,6 +37,12 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_EPI_WARPS = 8;             // one barrier arrival per warp, one polling lane per warp
 constexpr int GEMM_THREADS = 384;          // warpgroups 0,1: promotion/epilogue; warpgroup 2: TMA + MMA warps
 constexpr int MAX_E = 1024;
+#ifndef ISSUER_SLEEP_NS
+#define ISSUER_SLEEP_NS 64
+#endif
+#ifndef MMA_ISSUE_GAP_CLK
+#define MMA_ISSUE_GAP_CLK 125
+#endif
 
 struct GemmSmem {
     uint64_t full[STAGES];
@@ -53,6 +62,7 @@ constexpr size_t GEMM_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * S
 
 constexpr int TRACE_CAP = 512;
 long long* g_gemm_trace = nullptr;
+int g_gemm_trace_warp = 0;
 
 struct GemmParams {
     const float* a_scale;      // [rows, nkb]
@@ -66,6 +76,7 @@ struct GemmParams {
     int* status;
     int E, D, I;
     long long* trace;          // optional timeline buffer [6][TRACE_CAP] of clock64 stamps of CTA 0 (debug aid)
+    int trace_warp;            // which promotion warp writes the promotion stamps
     int packed;                // weights pre-tiled: one contiguous 256 x 128-byte block per (expert, n tile, K block)
     long long total_rows;      // capacity of the sorted row buffers
 };
@@ -156,7 +167,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const int row0 = p.offsets[e] + m_tile * BM;
                 const long long wrow0 = (long long)e * w_rows;
                 for (int kb = 0; kb < nkb; kb++) {
-                    if (!ptx::mbar_wait(&sm->empty[s], ph ^ 1, abort_flag)) goto done;
+                    if (!ptx::mbar_wait_relaxed(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done;
                     if (p.trace && blockIdx.x == 0 && tr < TRACE_CAP) p.trace[0 * TRACE_CAP + tr++] = clock64();
                     uint8_t* a_dst = tiles + (size_t)s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
@@ -180,32 +191,50 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 }
             }
         }
-      } else if (warp == 9) {
-        // ===================== MMA issuer =====================
+      } else if (warp == 9 || warp == 10) {
+        // ===================== MMA issuers =====================
+        // Two issuers, one per TMEM stage (K blocks alternate between them).  The thread that issues a
+        // K block's MMAs stays tied up until they have run (in the issue of the later ones and in the
+        // commits); with a single issuer it came back to look at the other stage's "free" barrier
+        // hundreds of cycles after the promotion warps had released it.
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::make_idesc(0, 0, 0, 0, BM, BN);
+            const int role = warp - 9;                      // the TMEM stage this issuer owns
             int s = 0; uint32_t ph = 0;
-            int acc = 0; uint32_t acc_ph = 0; int tr = 0;
+            uint32_t acc_ph = 0; long long g = 0;           // g: K blocks since the kernel started
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-                for (int kb = 0; kb < nkb; kb++) {
-                    if (!ptx::mbar_wait(&sm->tmem_empty[acc], acc_ph ^ 1, abort_flag)) goto done;
-                    if (p.trace && blockIdx.x == 0 && tr < TRACE_CAP) p.trace[1 * TRACE_CAP + tr] = clock64();
-                    if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
-                    if (p.trace && blockIdx.x == 0 && tr < TRACE_CAP) p.trace[2 * TRACE_CAP + tr++] = clock64();
-                    ptx::tc_fence_after();
-                    const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
-                    const uint32_t b_addr = a_addr + A_BYTES;
-                    const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < nkb; kb++, g++) {
+                    if ((int)(g & 1) == role) {
+                        if (!ptx::mbar_wait_relaxed(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
+                        if (p.trace && blockIdx.x == 0 && g < TRACE_CAP) p.trace[1 * TRACE_CAP + g] = clock64();
+                        if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
+                        if (p.trace && blockIdx.x == 0 && g < TRACE_CAP) p.trace[2 * TRACE_CAP + g] = clock64();
+                        ptx::tc_fence_after();
+                        const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                        const uint32_t b_addr = a_addr + A_BYTES;
+                        const uint32_t d_tmem = tmem_base + role * BN;
+                        long long t_first = 0;
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; k4++) {
-                        uint64_t ad = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
-                        uint64_t bd = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
-                        ptx::mma_f8(d_tmem, ad, bd, idesc, k4 > 0 ? 1u : 0u);
+                        for (int k4 = 0; k4 < 4; k4++) {
+                            uint64_t ad = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
+                            uint64_t bd = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
+                            // An MMA that finds the tensor pipe's queue full stalls its whole scheduler, not
+                            // only this warp: the promotion warps next to it then notice their barrier
+                            // hundreds of cycles late.  The third and fourth MMA are therefore held back (a
+                            // light clock poll, nanosleep is far too coarse) until the one two places ahead
+                            // has about finished.
+                            if (k4 == 0) t_first = clock64();
+                            if (k4 >= 2) {
+                                const long long until = t_first + (k4 - 1) * MMA_ISSUE_GAP_CLK;
+                                while (clock64() < until) {}
+                            }
+                            ptx::mma_f8(d_tmem, ad, bd, idesc, k4 > 0 ? 1u : 0u);
+                        }
+                        ptx::tc_commit(&sm->empty[s]);          // smem stage reusable once the MMAs have read it
+                        ptx::tc_commit(&sm->tmem_full[role]);   // partial sums ready for promotion
+                        acc_ph ^= 1;
                     }
-                    ptx::tc_commit(&sm->empty[s]);          // smem stage reusable once the MMAs have read it
-                    ptx::tc_commit(&sm->tmem_full[acc]);    // partial sums ready for promotion
                     if (++s == STAGES) { s = 0; ph ^= 1; }
-                    if (++acc == 2) { acc = 0; acc_ph ^= 1; }
                 }
             }
         }
@@ -261,7 +290,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     w1_n = w_sc1[kb + 1];
                 }
                 if (!warp_wait(&sm->tmem_full[acc], acc_ph)) goto done;
-                const bool trc = p.trace && blockIdx.x == 0 && threadIdx.x == 0 && tr < TRACE_CAP;
+                const bool trc = p.trace && blockIdx.x == 0 && threadIdx.x == p.trace_warp * 32 && tr < TRACE_CAP;
                 if (trc) p.trace[3 * TRACE_CAP + tr] = clock64();
                 ptx::tc_fence_after();
                 const uint32_t t0 = tmem_base + lane_addr + acc * BN + wg * 128;
@@ -481,6 +510,7 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     CUtensorMap ta, tb;
     GemmParams p{};
     p.trace = g_gemm_trace;
+    p.trace_warp = g_gemm_trace_warp;
     p.offsets = s.offsets; p.E = E; p.D = D; p.I = I; p.status = ws->d_status; p.total_rows = TK;
 
     // GEMM1
@@ -521,6 +551,7 @@ extern "C" {
 
 // Debug aid (not in the public header): timeline stamps of CTA 0 of the next grouped GEMM launches.
 __attribute__((visibility("default"))) void b200_debug_gemm_trace(long long* dev_buf) { g_gemm_trace = dev_buf; }
+__attribute__((visibility("default"))) void b200_debug_gemm_trace_warp(int warp) { g_gemm_trace_warp = warp & 7; }
 
 int b200_moe_fp8_profile(int enable) {
     if (enable && !g_prof_created) {

@@ -451,7 +451,7 @@ gate_logits_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__
         stage();
         __syncthreads();
         if (d0 + GL_TK < d_end) fetch(d0 + GL_TK);
-#pragma unroll 4
+#pragma unroll
         for (int k = 0; k < GL_TK; k++) {
             const float4 a0 = *reinterpret_cast<const float4*>(&As[k][ty * 8]);
             const float4 a1 = *reinterpret_cast<const float4*>(&As[k][ty * 8 + 4]);
