@@ -387,6 +387,17 @@ permute_kernel(const int* __restrict__ ids, int TK, int K, int E, const int* __r
 // 8 * TY rows (TY = 8..16, 16 * TY threads) so that the launcher can pick the height whose tile
 // count fills whole waves of resident CTAs, and the next k-tile is fetched into registers while
 // the current one is multiplied.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 template <int TY>
 __global__ void __launch_bounds__(16 * TY, 512 / (16 * TY))
 gate_logits_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, const float* __restrict__ wg,
@@ -399,11 +410,13 @@ gate_logits_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__
     const int d_begin = c * chunk;
     const int d_end = min(D, d_begin + chunk);
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;   // tx -> 8 experts, ty -> 8 tokens
-    float acc[8][8];
+    // accumulators as pairs of adjacent experts: one fma.rn.f32x2 does two IEEE fused multiply-adds
+    // (same bits as two scalar ones) for one issue slot, and this kernel is bound by issue slots
+    unsigned long long acc2[8][4];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+        for (int j = 0; j < 4; j++) acc2[i][j] = 0ull;
 
     uint4 a_raw = make_uint4(0, 0, 0, 0);
     float a_sc = 0.0f;
@@ -458,11 +471,14 @@ gate_logits_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__
             const float4 b0 = *reinterpret_cast<const float4*>(&Bs[k][tx * 8]);
             const float4 b1 = *reinterpret_cast<const float4*>(&Bs[k][tx * 8 + 4]);
             const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const unsigned long long bb[4] = {pack_f32x2(b0.x, b0.y), pack_f32x2(b0.z, b0.w), pack_f32x2(b1.x, b1.y),
+                                              pack_f32x2(b1.z, b1.w)};
 #pragma unroll
-            for (int i = 0; i < 8; i++)
+            for (int i = 0; i < 8; i++) {
+                const unsigned long long aa = pack_f32x2(a[i], a[i]);
 #pragma unroll
-                for (int j = 0; j < 8; j++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; j++) acc2[i][j] = fma_f32x2(aa, bb[j], acc2[i][j]);
+            }
         }
         __syncthreads();
     }
@@ -473,7 +489,9 @@ gate_logits_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__
 #pragma unroll
         for (int j = 0; j < 8; j++) {
             const int e = e0 + tx * 8 + j;
-            if (e < E) partials[((size_t)c * T + t) * E + e] = acc[i][j];
+            const unsigned long long v = acc2[i][j >> 1];
+            const float f = __uint_as_float((j & 1) ? (unsigned)(v >> 32) : (unsigned)(v & 0xffffffffull));
+            if (e < E) partials[((size_t)c * T + t) * E + e] = f;
         }
     }
 }
