@@ -17,8 +17,8 @@
 //   warps 9,10  MMA issuers, one per 256-column TMEM accumulator stage (K blocks alternate between
 //               them): 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block, started fresh for
 //               every K block.  Everything that waits next to the promotion warps sleeps between
-//               polls: a warp that spins, or that sits in an MMA issue blocked on a full tensor
-//               queue, takes the scheduler away from the two promotion warps that share it.
+//               polls: a warp that spins takes issue slots from the two promotion warps that share
+//               its scheduler.
 //   warps 0-7   promotion + epilogue: tcgen05.ld the K block's partial sums and fold them
 //               into fp32 registers with a_scale[row,kb] * w_scale[nblk,kb] (the scales are
 //               arbitrary fp32 values, so the scaling cannot be left to the tensor core).
@@ -39,9 +39,6 @@ constexpr int GEMM_THREADS = 384;          // warpgroups 0,1: promotion/epilogue
 constexpr int MAX_E = 1024;
 #ifndef ISSUER_SLEEP_NS
 #define ISSUER_SLEEP_NS 64
-#endif
-#ifndef MMA_ISSUE_GAP_CLK
-#define MMA_ISSUE_GAP_CLK 125
 #endif
 
 struct GemmSmem {
@@ -213,21 +210,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
                         const uint32_t b_addr = a_addr + A_BYTES;
                         const uint32_t d_tmem = tmem_base + role * BN;
-                        long long t_first = 0;
 #pragma unroll
                         for (int k4 = 0; k4 < 4; k4++) {
                             uint64_t ad = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
                             uint64_t bd = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
-                            // An MMA that finds the tensor pipe's queue full stalls its whole scheduler, not
-                            // only this warp: the promotion warps next to it then notice their barrier
-                            // hundreds of cycles late.  The third and fourth MMA are therefore held back (a
-                            // light clock poll, nanosleep is far too coarse) until the one two places ahead
-                            // has about finished.
-                            if (k4 == 0) t_first = clock64();
-                            if (k4 >= 2) {
-                                const long long until = t_first + (k4 - 1) * MMA_ISSUE_GAP_CLK;
-                                while (clock64() < until) {}
-                            }
                             ptx::mma_f8(d_tmem, ad, bd, idesc, k4 > 0 ? 1u : 0u);
                         }
                         ptx::tc_commit(&sm->empty[s]);          // smem stage reusable once the MMAs have read it
