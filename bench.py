@@ -35,9 +35,9 @@ if ROOT not in sys.path:
 MOE = dict(T=4096, E=256, K=8, D=7168, I=2048, n_group=8, topk_group=4, routed_scale=2.5)
 DSA = dict(B=64, H=128, Dc=512, Dp=64, S=2048, page=64, seq_min=8192, seq_max=131072)
 ZIPF_S, ZIPF_BETA = 1.1, 0.08
-# "strided": expert e lives on GPU e mod N (a group's 32 experts and a run of hot ones spread over all GPUs);
-# "balanced": greedy placement by the expert loads of a calibration batch; "contiguous": blocks of E/N experts
-EP_PLACEMENT = os.environ.get("B200_EP_PLACEMENT", "balanced")
+# --ep-placement "strided": expert e lives on GPU e mod N (a group's 32 experts and a run of hot ones spread over
+# all GPUs); "balanced": greedy placement by the expert loads of a calibration batch; "contiguous": blocks of E/N
+EP_PLACEMENT = "balanced"
 RTOL, ATOL = 2e-2, 1e-2
 
 
@@ -658,7 +658,11 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized case of the same kernels (32 experts, 512 tokens; 16 queries, short caches): "
                          "inputs still exceed L2 but only ~2 GB live on the device; not a bench value")
+    ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "strided", "contiguous"],
+                    help="expert placement of the expert-parallel layer (N > 1)")
     args = ap.parse_args()
+    global EP_PLACEMENT
+    EP_PLACEMENT = args.ep_placement
     if args.small:
         MOE.update(T=512, E=32, n_group=4, topk_group=2)
         DSA.update(B=16, seq_min=8192, seq_max=16384)

@@ -75,7 +75,17 @@ typedef struct b200_moe_fp8_config {
     int n_group;        /* expert groups (E % n_group == 0); 1 = ungrouped */
     int topk_group;     /* groups kept per token */
     float routed_scale; /* factor applied to the normalised weights */
+    int flags;          /* bit set of enum b200_moe_flags; 0 = defaults */
 } b200_moe_fp8_config;
+
+enum b200_moe_flags {
+    /* Sum a token's K expert contributions in ascending expert order with plain fp32 adds (the order of
+     * the reference's host loop, kernels/moe/naive_moe.cu:424, and of its CPU code, tests/test_moe.cu:74):
+     * GEMM2 writes one weighted row per (token, expert) and a second kernel reduces them, so the output is
+     * bit-reproducible from run to run.  Costs T*K*D*4 bytes of workspace and one more pass over them.
+     * Without the flag GEMM2 scatter-adds into the output (order varies, results agree to fp32 rounding). */
+    B200_MOE_DETERMINISTIC = 1
+};
 
 /* --------------------------------------------------------------------------- */
 /* Library / workspace                                                         */
@@ -154,7 +164,9 @@ B200_API int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* x
 /* Weight pre-tiling for the grouped GEMMs (no reference counterpart).  DRAM delivers random 128-byte
  * pieces at well under half the rate of 1 KB+ contiguous pieces, and a row-major weight tile is made of
  * 128-byte pieces 7 KB apart; the packed form stores each (expert, n tile, K block) tile as one
- * contiguous 32 KB block.  which = 1: w1q [E,2I,D]; which = 2: w2q [E,D,I]; packed has the same size.
+ * contiguous 32 KB block of 256 rows x 128 bytes.  which = 1: w1q [E,2I,D], tile rows for j0 = 128 * n tile:
+ * gate j0..+31, up j0..+31, gate j0+32..+63, up j0+32..+63, ... (gate row j = w1 row j, up row j = w1 row
+ * I + j); which = 2: w2q [E,D,I], tile rows = w2 rows 256 * n tile .. +255; packed has the same size.
  * Scales are unchanged.  The *_packed entry points take packed weights and are otherwise identical to
  * b200_moe_fp8_forward / b200_moe_fp8_experts. */
 B200_API int b200_moe_fp8_pack_weights(int which, const uint8_t* src, uint8_t* packed, int E, int D, int I,
@@ -175,11 +187,12 @@ B200_API int b200_moe_fp8_gemm1_stage(b200_ws* ws, const uint8_t* xq, const floa
                                       b200_stream_t stream);
 
 /* Measurement aid (no reference counterpart): when enabled, CUDA events are recorded on
- * the launch stream around the two grouped GEMM kernels of every FP8 layer call (enabling
- * resets the record); the read returns the mean device time of GEMM1 and GEMM2 in
- * milliseconds over the recorded calls (at most the last 256) and their number. */
-B200_API int b200_moe_fp8_profile(int enable);
-B200_API int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms, int* calls);
+ * the launch stream around the two grouped GEMM kernels of every FP8 layer call that uses this
+ * workspace (enabling resets the record); the read returns the mean device time of GEMM1 and
+ * GEMM2 in milliseconds over the recorded calls (at most the last 256) and their number.
+ * The record belongs to the workspace: host threads with their own workspaces do not share it. */
+B200_API int b200_moe_fp8_profile(b200_ws* ws, int enable);
+B200_API int b200_moe_fp8_profile_read(b200_ws* ws, float* gemm1_ms, float* gemm2_ms, int* calls);
 
 /* --------------------------------------------------------------------------- */
 /* DSA / MLA sparse decode                                                      */
@@ -261,12 +274,6 @@ B200_API int b200_fill_normal_bf16(uint16_t* dst, long long n, unsigned long lon
  * (weights: 128x128 blocks; activations: 1x128) without an fp32 copy in memory. */
 B200_API int b200_fill_normal_fp8_w128(uint8_t* q, float* scales, long long rows, int cols,
                                        unsigned long long seed, float sigma, b200_stream_t stream);
-
-/* Tensor-core self check: D[128,N] = A[128,K] * B[N,K]^T through the same shared-memory
- * descriptors the production kernels use.  mode 0: bf16, both operands K-major;
- * mode 1: bf16, B stored [K,N] (MN-major); mode 2: e4m3 K-major.  a/b are raw bits. */
-B200_API int b200_umma_selftest(int mode, const void* a, const void* b, float* d, int N, int K,
-                                b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -12,8 +12,7 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# B200_LIBRARY points at another build of the same library (A/B runs of two builds on one machine)
-LIB_PATH = os.environ.get("B200_LIBRARY") or os.path.join(_HERE, "lib", "libb200moedsa.so")
+LIB_PATH = os.path.join(_HERE, "lib", "libb200moedsa.so")
 _lib = None
 
 (B200_OK, B200_BAD_SHAPE, B200_UNSUPPORTED, B200_CUDA_ERROR, B200_TIMEOUT, B200_NCCL_ERROR,
@@ -38,7 +37,11 @@ class DsaConfig(C.Structure):  # kernels/dsa/naive_dsa.cuh:9-17
 
 class MoeFp8Config(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("num_tokens", "num_experts", "top_k", "hidden_dim", "intermediate_dim",
-                                       "scoring", "n_group", "topk_group")] + [("routed_scale", C.c_float)]
+                                       "scoring", "n_group", "topk_group")] + [("routed_scale", C.c_float),
+                                                                                  ("flags", C.c_int)]
+
+
+MOE_DETERMINISTIC = 1      # MoeFp8Config.flags: fixed-order (experts ascending) combine, bit-reproducible
 
 
 MoEConfig, DSAConfig = MoeConfig, DsaConfig
@@ -55,8 +58,10 @@ EXPORTED_SYMBOLS = [
     "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
     "b200_dsa_softmax_f32", "b200_dsa_output_proj_f32",
     "b200_ep_plan", "b200_ep_sum_rows",
-    "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128", "b200_umma_selftest",
+    "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128",
 ]
+# exported for the test suite only (declared in csrc/selftest.h, not in the public header)
+TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest"]
 
 
 def lib():
@@ -217,12 +222,12 @@ def ep_sum_rows(back, pos, world, out, stream=None):
 
 
 def moe_fp8_profile(enable):
-    _check(lib().b200_moe_fp8_profile(1 if enable else 0), "moe_fp8_profile")
+    _check(lib().b200_moe_fp8_profile(None, 1 if enable else 0), "moe_fp8_profile")
 
 
 def moe_fp8_profile_read():
     a, b, n = C.c_float(0), C.c_float(0), C.c_int(0)
-    _check(lib().b200_moe_fp8_profile_read(C.byref(a), C.byref(b), C.byref(n)), "moe_fp8_profile_read")
+    _check(lib().b200_moe_fp8_profile_read(None, C.byref(a), C.byref(b), C.byref(n)), "moe_fp8_profile_read")
     return a.value, b.value, n.value
 
 
@@ -334,8 +339,16 @@ def synth_normal_host(seed, start, n, sigma):
 
 
 def umma_selftest(mode, a, b, d, N, K, stream=None):
+    """Test hook: one tensor-core tile through the production shared-memory layouts."""
     _check(lib().b200_umma_selftest(int(mode), _p(a), _p(b), _p(d), int(N), int(K), _stream(stream)),
            "umma_selftest")
+
+
+def wait_selftest(elapsed_ns, stream=None):
+    """Test hook: a one-block kernel waits (bounded, a few milliseconds) on an mbarrier nobody signals,
+    gives up, records B200_TIMEOUT in the default workspace's status word and exits.
+    elapsed_ns: int64 CUDA tensor [2] receiving the time each of the two waiters spent."""
+    _check(lib().b200_wait_selftest(None, _p(elapsed_ns), _stream(stream)), "wait_selftest")
 
 
 from .ep import ExpertParallelMoe, balanced_placement, dispatch_plan, expert_owner  # noqa: E402,F401

@@ -367,18 +367,13 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
     if (!ws) return B200_CUDA_ERROR;
 
     // The CTA-pair kernels take every shape with S % 64 == 0 (128-row tiles when S % 128 == 0, else
-    // 64-row tiles); the single-CTA kernel (32-row tiles) takes the rest.  B200_DSA_SINGLE_CTA=1 forces
-    // the latter, B200_DSA_TILE64=1 the 64-row pair kernel (both for comparison runs).
-    static const bool force_single = getenv("B200_DSA_SINGLE_CTA") != nullptr;
-    static const bool force_tile64 = getenv("B200_DSA_TILE64") != nullptr;
-    const bool use_pair = (S % 64 == 0) && !force_single;
-    const int pair_tile = (S % 128 == 0 && !force_tile64) ? 128 : 64;
+    // 64-row tiles); the single-CTA kernel (32-row tiles) takes the rest.
+    const bool use_pair = (S % 64 == 0);
+    const int pair_tile = (S % 128 == 0) ? 128 : 64;
     // split the selected rows so that the grid covers the machine about once
     const int nt_total = S / (use_pair ? pair_tile : TKV);
     int NS = 1;
     if (2 * Q < ws->sm_count) NS = ws->sm_count / (2 * Q);
-    static const int forced_splits = getenv("B200_DSA_SPLITS") ? atoi(getenv("B200_DSA_SPLITS")) : 0;   // tuning aid
-    if (forced_splits > 0) NS = forced_splits;
     if (NS > nt_total) NS = nt_total;
     if (NS > 64) NS = 64;
     if (NS < 1) NS = 1;

@@ -66,7 +66,6 @@ struct Params {
     int* status;
     int H, S, NS, tiles_per_split;
     float sl2;
-    long long* trace;   // optional [10][64] clock64 stamps of cluster 0 (debug aid)
 };
 
 // ---- cluster-scope helpers --------------------------------------------------------------------
@@ -251,7 +250,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             for (int x = 0; x < 16; x++) vid[x] = vid_n[x];
             load_ids(j + 1, kid_n, kpid_n, vid_n);
             if (!ptx::mbar_wait(&sm->k_empty[st], par, abort_flag)) goto done;
-            if (p.trace && rank == 0 && pt == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64) p.trace[8 * 64 + j] = clock64();
             {
                 const uint32_t kst = ptx::smem_u32(sK) + st * K_STAGE_BYTES;
                 // Kc: row r = 8 gw + x, 16-byte chunk ch = lane (+32): slot ch/8, position (ch%8) ^ (r%8)
@@ -275,7 +273,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             ptx::cp_async_arrive_noinc(&sm->k_full[st]);
             {
                 if (!ptx::mbar_wait(&sm->v_empty[st], par, abort_flag)) goto done;
-                if (p.trace && rank == 0 && pt == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64) p.trace[9 * 64 + j] = clock64();
                 const uint32_t vbase = ptx::smem_u32(sV) + st * V_STAGE_BYTES;
                 // this CTA's 512 contiguous bytes of a V row: columns [256 rank, 256 rank + 256);
                 // 64-column chunk q = lane / 8 (MMA q/2, half q%2)
@@ -317,7 +314,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                 if (!ptx::mbar_wait(&sm->v_full[st], par, abort_flag)) return false;
                 if (!forward_or_wait(&sm->pv_peer[st], par)) return false;
                 if (!leader) return true;
-                if (p.trace && blockIdx.y == 0 && blockIdx.z == 0 && i < 64) p.trace[2 * 64 + i] = clock64();
                 ptx::tc_fence_after();
 #pragma unroll
                 for (int inst = 0; inst < 2; inst++) {
@@ -331,7 +327,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                 }
                 commit_both(&sm->v_empty[st]);
                 commit_both(&sm->p_empty);
-                if (p.trace && blockIdx.y == 0 && blockIdx.z == 0 && i < 64) p.trace[3 * 64 + i] = clock64();
                 return true;
             };
             if (!ptx::mbar_wait(&sm->q_full, 0, abort_flag)) goto done;
@@ -341,7 +336,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                 if (!ptx::mbar_wait(&sm->s_empty[st], par ^ 1, abort_flag)) goto done;   // passes at once on first use
                 if (!ptx::mbar_wait(&sm->k_full[st], par, abort_flag)) goto done;
                 if (!forward_or_wait(&sm->qk_peer[st], par)) goto done;
-                if (leader && p.trace && blockIdx.y == 0 && blockIdx.z == 0 && j < 64) p.trace[0 * 64 + j] = clock64();
                 if (leader) {
                     ptx::tc_fence_after();
 #pragma unroll
@@ -356,7 +350,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                     }
                     commit_both(&sm->k_empty[st]);
                     commit_both(&sm->s_full[st]);
-                    if (p.trace && blockIdx.y == 0 && blockIdx.z == 0 && j < 64) p.trace[1 * 64 + j] = clock64();
                 }
                 if (j > 0 && !issue_pv(j - 1)) goto done;
             }
@@ -374,8 +367,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
         for (int j = 0; j < nt; j++) {
             const int sb = j & 1;
             if (!ptx::mbar_wait(&sm->s_full[sb], (uint32_t)((j >> 1) & 1), abort_flag)) goto done;
-            const bool trc = p.trace && rank == 0 && blockIdx.y == 0 && blockIdx.z == 0 && t == 0 && j < 64;
-            if (trc) p.trace[4 * 64 + j] = clock64();
             ptx::tc_fence_after();
             uint32_t r[32];
             ptx::tmem_ld_32x32(tmem + lane_addr + S_COL + sb * 32, r);
@@ -390,7 +381,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             ptx::mbar_arrive(&sm->mx_bar);
             if (!ptx::mbar_wait(&sm->mx_bar, (uint32_t)(j & 1), abort_flag)) goto done;
             tmax = fmaxf(tmax, sm->xchg[sb][t ^ 64]);
-            if (trc) p.trace[5 * 64 + j] = clock64();
             const bool need = tmax > m + thr;
             const float m_new = need ? tmax : m;
             const float corr = need ? exp2f((m - m_new) * p.sl2) : 1.0f;
@@ -405,7 +395,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
                 pk[i] = *reinterpret_cast<uint32_t*>(&h2);
             }
             if (!ptx::mbar_wait(&sm->p_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
-            if (trc) p.trace[6 * 64 + j] = clock64();
             ptx::tc_fence_after();
             if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
@@ -430,7 +419,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before();
             ptx::mbar_arrive(&sm->p_full);
-            if (trc) p.trace[7 * 64 + j] = clock64();
             l = l * corr + rowsum;
             m = m_new;
         }
@@ -533,8 +521,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
     const int nt_total = p.S / TKV;
     const int t_begin = sp * p.tiles_per_split;
     const int nt = max(0, min(nt_total, t_begin + p.tiles_per_split) - t_begin);
-    const bool tracing = p.trace && rank == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-    if (tracing && threadIdx.x == 0) p.trace[10 * 64 + 4] = (long long)ptx::globaltimer_ns();
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(&sm->q_full, NPROD);
@@ -606,7 +592,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
                 const int id = id_n;
                 if (j + 1 < nt) id_n = ids[(size_t)(j + 1) * TKV + my];
                 if (!ptx::mbar_wait(&sm->k_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
-                if (tracing && pt == 0 && j < 64) p.trace[8 * 64 + j] = clock64();
                 // Kc: row r, 16-byte chunk ch = lane (+32): slot ch/8, position (ch%8) ^ (r%8)
 #pragma unroll 8
                 for (int x = 0; x < RPW; x++) {
@@ -651,7 +636,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
                     id1_n = ids[(size_t)(j + 1) * TKV + my1];
                 }
                 if (!ptx::mbar_wait(&sm->v_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
-                if (tracing && pt == 32 * NKW && j < 64) p.trace[9 * 64 + j] = clock64();
 #pragma unroll 8
                 for (int x = 0; x < VPW; x++) {
                     const size_t rid = (size_t)__shfl_sync(0xffffffffu, (x < 32) ? id0 : id1, x & 31);
@@ -689,7 +673,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
                 if (!ptx::mbar_wait(&sm->v_full, par, abort_flag)) return false;
                 if (!forward_or_wait(&sm->pv_peer, par)) return false;
                 if (!leader) return true;
-                if (tracing && i < 64) p.trace[2 * 64 + i] = clock64();
                 ptx::tc_fence_after();
 #pragma unroll
                 for (int inst = 0; inst < 2; inst++) {
@@ -702,10 +685,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
                 }
                 commit_both(&sm->v_empty);
                 commit_both(&sm->p_empty);
-                if (tracing && i < 64) p.trace[3 * 64 + i] = clock64();
                 return true;
             };
-            if (tracing) { p.trace[10 * 64 + 0] = clock64(); p.trace[10 * 64 + 1] = (long long)ptx::globaltimer_ns(); }
             if (!ptx::mbar_wait(&sm->q_full, 0, abort_flag)) goto done;
             for (int j = 0; j < nt; j++) {
                 const int sb = j & 1;
@@ -713,7 +694,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
                 if (!ptx::mbar_wait(&sm->k_full, (uint32_t)(j & 1), abort_flag)) goto done;
                 if (!forward_or_wait(&sm->qk_peer, (uint32_t)(j & 1))) goto done;
                 if (leader) {
-                    if (tracing && j < 64) p.trace[0 * 64 + j] = clock64();
                     ptx::tc_fence_after();
 #pragma unroll
                     for (int c = 0; c < KBLK; c++) {
@@ -726,13 +706,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
                     }
                     commit_both(&sm->k_empty);
                     commit_both(&sm->s_full[sb]);
-                    if (tracing && j < 64) p.trace[1 * 64 + j] = clock64();
                 }
                 if (j > 0 && !issue_pv(j - 1)) goto done;
             }
             if (!issue_pv(nt - 1)) goto done;
             if (leader) commit_both(&sm->o_done);
-            if (tracing) { p.trace[10 * 64 + 2] = clock64(); p.trace[10 * 64 + 3] = (long long)ptx::globaltimer_ns(); }
         }
     } else {
         // ===================== softmax / correction / epilogue (warps 0-3 of each CTA) =====================
@@ -745,8 +723,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
         for (int j = 0; j < nt; j++) {
             const int sb = j & 1;
             if (!ptx::mbar_wait(&sm->s_full[sb], (uint32_t)((j >> 1) & 1), abort_flag)) goto done;
-            const bool trc = tracing && t == 0 && j < 64;
-            if (trc) p.trace[4 * 64 + j] = clock64();
             ptx::tc_fence_after();
             uint32_t r[64];
             ptx::tmem_ld_32x64(tmem + lane_addr + S_COL + sb * 64, r);
@@ -761,7 +737,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
             ptx::mbar_arrive(&sm->mx_bar);
             if (!ptx::mbar_wait(&sm->mx_bar, (uint32_t)(j & 1), abort_flag)) goto done;
             tmax = fmaxf(tmax, sm->xchg[sb][t ^ 64]);
-            if (trc) p.trace[5 * 64 + j] = clock64();
             const bool need = tmax > m + thr;
             const float m_new = need ? tmax : m;
             const float corr = need ? exp2f((m - m_new) * p.sl2) : 1.0f;
@@ -776,7 +751,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
                 pk[i] = *reinterpret_cast<uint32_t*>(&h2);
             }
             if (!ptx::mbar_wait(&sm->p_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
-            if (trc) p.trace[6 * 64 + j] = clock64();
             ptx::tc_fence_after();
             if (j > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
@@ -801,7 +775,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
             ptx::fence_proxy_async_smem();
             ptx::tc_fence_before();
             ptx::mbar_arrive(&sm->p_full);
-            if (trc) p.trace[7 * 64 + j] = clock64();
             l = l * corr + rowsum;
             m = m_new;
         }
@@ -848,7 +821,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
             }
             __syncwarp();
         }
-        if (tracing && t == 0) p.trace[10 * 64 + 5] = (long long)ptx::globaltimer_ns();
         if (!direct && hh == 0) {
             float* ml = p.part_ml + (((size_t)b * p.NS + sp) * HEADS + head) * 2;
             ml[0] = (nt > 0) ? m * p.sl2 : -1e30f;
@@ -860,7 +832,6 @@ done:
     __syncthreads();
     cluster_sync_all();                  // the pair's MMAs and TMEM reads are over in both CTAs
     if (warp == 4) tmem_dealloc2(tmem, 512);
-    if (tracing && threadIdx.x == 0) p.trace[10 * 64 + 6] = (long long)ptx::globaltimer_ns();
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
 }
 
@@ -868,8 +839,6 @@ done:
 
 }  // namespace pair
 
-long long* g_dsa_trace = nullptr;
-extern "C" __attribute__((visibility("default"))) void b200_debug_dsa_trace(long long* dev_buf) { g_dsa_trace = dev_buf; }
 
 // Host side: called by b200_dsa_forward_bf16 with tile_rows = 128 (S % 128 == 0) or 64 (S % 64 == 0);
 // tiles_per_split counts tiles of that size.
@@ -892,9 +861,7 @@ int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, c
     p.idx = idx; p.out = out; p.part_o = part_o; p.part_ml = part_ml; p.status = status;
     p.H = H; p.S = S; p.NS = NS; p.tiles_per_split = tiles_per_split;
     p.sl2 = 1.4426950408889634f / sqrtf((float)(pair::DC + pair::DP));
-    p.trace = g_dsa_trace;
     if (tile_rows == 128) {
-        static const bool no_pdl = getenv("B200_DSA_NO_PDL") != nullptr;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2, NS, Q);
         cfg.blockDim = dim3(pair::t128::THREADS128);
@@ -904,7 +871,7 @@ int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, c
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = no_pdl ? 0 : 1;
+        cfg.numAttrs = 1;
         B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, pair::t128::dsa_decode_pair128_kernel, p));
     } else
         pair::dsa_decode_pair_kernel<<<dim3(2, NS, Q), pair::THREADS, pair::SMEM_BYTES, stream>>>(p);

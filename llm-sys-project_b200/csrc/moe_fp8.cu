@@ -10,18 +10,26 @@
 //                          requantisation fused in the epilogue: no fp32 GEMM1 output in HBM)
 //   grouped_gemm_fp8<2>    out[token] += w * (act W2^T)                      (router weight and
 //                          scatter-add fused in the epilogue)
+//   grouped_gemm_fp8<3>    rows[r] = w * (act W2^T), then reduce_rows_kernel sums a token's rows
+//                          in ascending expert order (the reference's order, naive_moe.cu:424):
+//                          the bit-reproducible alternative to the scatter-add.
 //
-// GEMM structure (one CTA per SM, tiles 128 x 256 x 128 handed out round-robin, expert-major):
-//   warp 8      TMA producer: A tile (128 rows x 128 B) and B tile (256 rows x 128 B) per
-//               K block into a 4-stage shared-memory ring (128-byte swizzle, K-major).
-//   warps 9,10  MMA issuers, one per 256-column TMEM accumulator stage (K blocks alternate between
-//               them): 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block, started fresh for
-//               every K block.  Everything that waits next to the promotion warps sleeps between
-//               polls: a warp that spins takes issue slots from the two promotion warps that share
-//               its scheduler.
-//   warps 0-7   promotion + epilogue: tcgen05.ld the K block's partial sums and fold them
-//               into fp32 registers with a_scale[row,kb] * w_scale[nblk,kb] (the scales are
-//               arbitrary fp32 values, so the scaling cannot be left to the tensor core).
+// GEMM structure (one CTA per SM, 640 threads, tiles 128 x 256 x 128 handed out round-robin,
+// expert-major):
+//   warp 16      TMA producer: A tile (128 rows x 128 B) and B tile (256 rows x 128 B) per
+//                K block into a 4-stage shared-memory ring (128-byte swizzle, K-major).
+//   warps 17,18  MMA issuers, one per 256-column TMEM accumulator stage (K blocks alternate between
+//                them): 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block, started fresh for
+//                every K block.  Everything that waits next to the promotion warps sleeps between
+//                polls: a warp that spins takes issue slots from the promotion warps that share
+//                its scheduler.
+//   warps 0-15   promotion + epilogue: tcgen05.ld the K block's partial sums and fold them
+//                into fp32 registers with a_scale[row,kb] * w_scale[nblk,kb] (the scales are
+//                arbitrary fp32 values, so the scaling cannot be left to the tensor core).
+//                Warp w owns TMEM lanes 32 (w % 4) .. +31 (the tile rows) and accumulator columns
+//                64 (w / 4) .. +63: 64 running sums per thread, updated by packed fma.rn.f32x2.
+//                Four promotion warps per scheduler (instead of two with 128 sums each) hide the
+//                commit -> tcgen05.ld -> FMA latency chain of one warp behind the others' work.
 // Every mbarrier wait is bounded; on give-up the CTA flags B200_TIMEOUT and winds down.
 #include "common.cuh"
 #include "moe_internal.cuh"
@@ -34,12 +42,17 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;            // 16384
 constexpr int B_BYTES = BN * BK;            // 32768
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int NUM_EPI_WARPS = 8;             // one barrier arrival per warp, one polling lane per warp
-constexpr int GEMM_THREADS = 384;          // warpgroups 0,1: promotion/epilogue; warpgroup 2: TMA + MMA warps
+constexpr int NUM_PROMO_WARPS = 16;          // one barrier arrival per warp, one polling lane per warp
+constexpr int QCOLS = BN / (NUM_PROMO_WARPS / 4);   // 64 accumulator columns per promotion thread
+constexpr int GEMM_THREADS = 32 * (NUM_PROMO_WARPS + 4);   // warpgroups 0-3: promotion/epilogue; 4: TMA + MMA warps
+constexpr int W_TMA = NUM_PROMO_WARPS, W_MMA0 = NUM_PROMO_WARPS + 1;
 constexpr int MAX_E = 1024;
-#ifndef ISSUER_SLEEP_NS
-#define ISSUER_SLEEP_NS 64
+constexpr unsigned ISSUER_SLEEP_NS = 64;
+#ifndef PROMO_REGS_V
+#define PROMO_REGS_V 120
+#define AUX_REGS_V 32
 #endif
+constexpr int PROMO_REGS = PROMO_REGS_V, AUX_REGS = AUX_REGS_V;   // 512 * 120 + 128 * 32 = 65536: the whole register file
 
 struct GemmSmem {
     uint64_t full[STAGES];
@@ -51,29 +64,24 @@ struct GemmSmem {
     int abort_flag;
     int total_tiles;
     int tile_prefix[MAX_E + 1];
-    float amax[2][2][BM];   // [tile parity][warpgroup][row]
-    alignas(16) float stage[8][32][20]; // per promotion warp: 32 rows x 16 columns (+4 pad) for the scatter-add transpose
+    float amax[2][4][BM];   // [tile parity][column quarter][row]
+    alignas(16) float stage[NUM_PROMO_WARPS][32][12];   // per promotion warp: 32 rows x 8 columns (+4 pad), scatter-add transpose
 };
 
 constexpr size_t GEMM_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(GemmSmem);
-
-constexpr int TRACE_CAP = 512;
-long long* g_gemm_trace = nullptr;
-int g_gemm_trace_warp = 0;
+static_assert(GEMM_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 
 struct GemmParams {
     const float* a_scale;      // [rows, nkb]
-    const float* w_scale;      // MODE 1: [E, 2I/128, D/128]   MODE 2: [E, D/128, I/128]
+    const float* w_scale;      // MODE 1: [E, 2I/128, D/128]   MODE 2/3: [E, D/128, I/128]
     const int* offsets;        // [E+1]
     const int* row_tok;        // MODE 2
-    const float* row_w;        // MODE 2
+    const float* row_w;        // MODE 2/3
     uint8_t* act_q;            // MODE 1 out [rows, I]
     float* act_s;              // MODE 1 out [rows, I/128]
-    float* out;                // MODE 2 out [T, D]
+    float* out;                // MODE 2 out [T, D]; MODE 3 out [rows, D]
     int* status;
     int E, D, I;
-    long long* trace;          // optional timeline buffer [6][TRACE_CAP] of clock64 stamps of CTA 0 (debug aid)
-    int trace_warp;            // which promotion warp writes the promotion stamps
     int packed;                // weights pre-tiled: one contiguous 256 x 128-byte block per (expert, n tile, K block)
     long long total_rows;      // capacity of the sorted row buffers
 };
@@ -83,6 +91,16 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                  : "memory");
 }
 
+// acc[0..15] += v[0..15] * s  as eight packed fused multiply-adds
+__device__ __forceinline__ void promote16(unsigned long long* acc2, const uint32_t (&v)[16], unsigned long long s2) {
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+        acc2[i] = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), s2, acc2[i]);
+}
+
+// MODE 1: the tile's 256 accumulator columns are four quarters [gate j0+32q .. +31 | up j0+32q .. +31]
+// (j0 = 128 n_tile), so that the gate and the up value of an activation column meet in one thread.
+// MODE 2/3: plain output columns 256 n_tile .. +255.
 template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -103,25 +121,35 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         for (int s = 0; s < STAGES; s++) { ptx::mbar_init(&sm->full[s], 1); ptx::mbar_init(&sm->empty[s], 1); }
         for (int a = 0; a < 2; a++) {
             ptx::mbar_init(&sm->tmem_full[a], 1);
-            ptx::mbar_init(&sm->tmem_empty[a], NUM_EPI_WARPS);
-            ptx::mbar_init(&sm->amax_bar[a], NUM_EPI_WARPS);
+            ptx::mbar_init(&sm->tmem_empty[a], NUM_PROMO_WARPS);
+            ptx::mbar_init(&sm->amax_bar[a], NUM_PROMO_WARPS);
         }
         sm->abort_flag = 0;
-        int acc = 0;
-        for (int e = 0; e < p.E; e++) {
-            sm->tile_prefix[e] = acc;
-            int cnt = p.offsets[e + 1] - p.offsets[e];
-            acc += ((cnt + BM - 1) / BM) * NT;
-        }
-        sm->tile_prefix[p.E] = acc;
-        sm->total_tiles = acc;
         ptx::fence_mbar_init();
     }
-    if (warp == 9) {
+    if (warp == 0) {
+        // tile_prefix[e] = tiles of experts < e (warp scan over the expert counts)
+        int running = 0;
+        for (int e0 = 0; e0 < p.E; e0 += 32) {
+            const int e = e0 + lane;
+            int t = 0;
+            if (e < p.E) t = ((p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM) * NT;
+            int incl = t;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (e < p.E) sm->tile_prefix[e] = running + incl - t;
+            running += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) { sm->tile_prefix[p.E] = running; sm->total_tiles = running; }
+    }
+    if (warp == W_MMA0) {
         ptx::tmem_alloc(&sm->tmem_base, 512);
         ptx::tmem_relinquish();
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == W_TMA && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
         ptx::prefetch_tensormap(&tmap_b);
     }
@@ -149,15 +177,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         m_tile = local - n_tile * mt;
     };
 
-    // Register budget: the two promotion warpgroups hold a 128-value accumulator row plus a
-    // 64-value staging buffer per thread; the TMA/MMA warpgroup needs almost nothing.
-
-    if (warp >= 8) {
-        ptx::setmaxnreg_dec<40>();
-      if (warp == 8) {
+    if (warp >= NUM_PROMO_WARPS) {
+        ptx::setmaxnreg_dec<AUX_REGS>();
+      if (warp == W_TMA) {
         // ===================== TMA producer =====================
         if (lane == 0) {
-            int s = 0; uint32_t ph = 0; int tr = 0;
+            int s = 0; uint32_t ph = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 int e, m_tile, n_tile, cnt;
                 locate(tile, e, m_tile, n_tile, cnt);
@@ -165,7 +190,6 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const long long wrow0 = (long long)e * w_rows;
                 for (int kb = 0; kb < nkb; kb++) {
                     if (!ptx::mbar_wait_relaxed(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done;
-                    if (p.trace && blockIdx.x == 0 && tr < TRACE_CAP) p.trace[0 * TRACE_CAP + tr++] = clock64();
                     uint8_t* a_dst = tiles + (size_t)s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
                     ptx::mbar_expect_tx(&sm->full[s], STAGE_BYTES);
@@ -174,13 +198,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         // the tile's K block is one contiguous 32 KB piece of the packed weights
                         ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], 0, (((e * NT + n_tile) * nkb) + kb) * BN);
                     } else if (MODE == 1) {
-                        // accumulator columns: [gate j0..+63 | up j0..+63 | gate j0+64..+127 | up j0+64..+127]
+                        // eight boxes of 32 weight rows: quarter q = [gate j0+32q.. | up j0+32q..]
                         const int j0 = n_tile * 128;
-                        ptx::tma_load_2d(b_dst + 0 * 8192, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + j0));
-                        ptx::tma_load_2d(b_dst + 1 * 8192, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + p.I + j0));
-                        ptx::tma_load_2d(b_dst + 2 * 8192, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + j0 + 64));
-                        ptx::tma_load_2d(b_dst + 3 * 8192, &tmap_b, &sm->full[s], kb * BK,
-                                         (int)(wrow0 + p.I + j0 + 64));
+#pragma unroll
+                        for (int bx = 0; bx < 8; bx++)
+                            ptx::tma_load_2d(b_dst + bx * 4096, &tmap_b, &sm->full[s], kb * BK,
+                                             (int)(wrow0 + ((bx & 1) ? p.I : 0) + j0 + 32 * (bx >> 1)));
                     } else {
                         ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + n_tile * 256));
                     }
@@ -188,7 +211,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 }
             }
         }
-      } else if (warp == 9 || warp == 10) {
+      } else if (warp == W_MMA0 || warp == W_MMA0 + 1) {
         // ===================== MMA issuers =====================
         // Two issuers, one per TMEM stage (K blocks alternate between them).  The thread that issues a
         // K block's MMAs stays tied up until they have run (in the issue of the later ones and in the
@@ -196,16 +219,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // hundreds of cycles after the promotion warps had released it.
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::make_idesc(0, 0, 0, 0, BM, BN);
-            const int role = warp - 9;                      // the TMEM stage this issuer owns
+            const int role = warp - W_MMA0;                 // the TMEM stage this issuer owns
             int s = 0; uint32_t ph = 0;
             uint32_t acc_ph = 0; long long g = 0;           // g: K blocks since the kernel started
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 for (int kb = 0; kb < nkb; kb++, g++) {
                     if ((int)(g & 1) == role) {
                         if (!ptx::mbar_wait_relaxed(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
-                        if (p.trace && blockIdx.x == 0 && g < TRACE_CAP) p.trace[1 * TRACE_CAP + g] = clock64();
                         if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
-                        if (p.trace && blockIdx.x == 0 && g < TRACE_CAP) p.trace[2 * TRACE_CAP + g] = clock64();
                         ptx::tc_fence_after();
                         const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
                         const uint32_t b_addr = a_addr + A_BYTES;
@@ -226,10 +247,10 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         }
       }
     } else {
-        // ===================== promotion + epilogue (warps 0-7) =====================
-        ptx::setmaxnreg_inc<232>();
-        // one lane polls the barrier, the warp follows (256 pollers and 256 arrivals per K block on one
-        // shared-memory word cost more than the promotion itself)
+        // ===================== promotion + epilogue (warps 0-15) =====================
+        ptx::setmaxnreg_inc<PROMO_REGS>();
+        // one lane polls the barrier, the warp follows (hundreds of pollers and arrivals per K block on
+        // one shared-memory word cost more than the promotion itself)
         auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
             int ok = 1;
             if (lane == 0) ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
@@ -237,11 +258,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             __syncwarp();
             return ok != 0;
         };
-        const int wg = warp >> 2;                         // column half of the accumulator
+        const int wq = warp >> 2;                         // column quarter of the accumulator
         const int row = (warp & 3) * 32 + lane;           // TMEM lane = tile row
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         int acc = 0; uint32_t acc_ph = 0;
-        int tile_par = 0; uint32_t amax_ph[2] = {0, 0}; int tr = 0;
+        int tile_par = 0; uint32_t amax_ph[2] = {0, 0};
         const int nkb_w = Kdim / 128;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             int e, m_tile, n_tile, cnt;
@@ -258,12 +279,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 w_sc1 = base + (size_t)(p.I / 128 + n_tile) * nkb_w;       // up rows' block
             } else {
                 const float* base = p.w_scale + (size_t)e * (p.D / 128) * nkb_w;
-                w_sc0 = base + (size_t)(n_tile * 2 + wg) * nkb_w;
+                w_sc0 = base + (size_t)(n_tile * 2 + (wq >> 1)) * nkb_w;
                 w_sc1 = w_sc0;
             }
-            float accv[128];
+            unsigned long long acc2[QCOLS / 2];
 #pragma unroll
-            for (int i = 0; i < 128; i++) accv[i] = 0.0f;
+            for (int i = 0; i < QCOLS / 2; i++) acc2[i] = 0ull;
 
             // scales of K block kb+1 are fetched while block kb is being promoted
             float sa_n = row_ok ? a_sc[0] : 0.0f, w0_n = w_sc0[0], w1_n = w_sc1[0];
@@ -276,98 +297,121 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     w1_n = w_sc1[kb + 1];
                 }
                 if (!warp_wait(&sm->tmem_full[acc], acc_ph)) goto done;
-                const bool trc = p.trace && blockIdx.x == 0 && threadIdx.x == p.trace_warp * 32 && tr < TRACE_CAP;
-                if (trc) p.trace[3 * TRACE_CAP + tr] = clock64();
-                ptx::tc_fence_after();
-                const uint32_t t0 = tmem_base + lane_addr + acc * BN + wg * 128;
-                uint32_t ra[32], rb[32];
-                ptx::tmem_ld_32x32(t0, ra);               // MODE 1: gate columns
-                ptx::tmem_ld_32x32(t0 + 32, rb);
-                ptx::tc_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i++) accv[i] += __uint_as_float(ra[i]) * s0;
-#pragma unroll
-                for (int i = 0; i < 32; i++) accv[32 + i] += __uint_as_float(rb[i]) * s0;
-                ptx::tmem_ld_32x32(t0 + 64, ra);          // MODE 1: up columns
-                ptx::tmem_ld_32x32(t0 + 96, rb);
-                ptx::tc_wait_ld();
-                ptx::tc_fence_before();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
-                if (trc) p.trace[4 * TRACE_CAP + tr] = clock64();
-#pragma unroll
-                for (int i = 0; i < 32; i++) accv[64 + i] += __uint_as_float(ra[i]) * s1;
-#pragma unroll
-                for (int i = 0; i < 32; i++) accv[96 + i] += __uint_as_float(rb[i]) * s1;
-                if (trc) p.trace[5 * TRACE_CAP + tr] = clock64();
-                tr++;
+                if (warp_valid) {
+                    // warps whose 32 rows are all padding only hand the stage back
+                    ptx::tc_fence_after();
+                    const unsigned long long s0p = ptx::pack_f32x2(s0, s0), s1p = ptx::pack_f32x2(s1, s1);
+                    const uint32_t t0 = tmem_base + lane_addr + acc * BN + wq * QCOLS;
+                    uint32_t ra[16], rb[16];
+                    ptx::tmem_ld_32x16(t0, ra);               // MODE 1: gate columns
+                    ptx::tmem_ld_32x16(t0 + 16, rb);
+                    ptx::tc_wait_ld();
+                    promote16(acc2, ra, s0p);
+                    ptx::tmem_ld_32x16(t0 + 32, ra);          // MODE 1: up columns
+                    promote16(acc2 + 8, rb, s0p);
+                    ptx::tmem_ld_32x16(t0 + 48, rb);
+                    ptx::tc_wait_ld();
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
+                    promote16(acc2 + 16, ra, s1p);
+                    promote16(acc2 + 24, rb, s1p);
+                } else {
+                    if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
+                }
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
 
             if (MODE == 1) {
-                // SwiGLU on 64 activation columns, 1x128 requantisation shared with the other warpgroup.
+                // SwiGLU on 32 activation columns, 1x128 requantisation shared with the three other quarters.
                 // Fast exp / reciprocal: the result is rounded to e4m3 next, an ulp of fp32 does not matter.
+                float av[32];
                 float amax = 0.0f;
-                if (warp_valid) {
 #pragma unroll
-                    for (int i = 0; i < 64; i++) {
-                        const float g = accv[i], u = accv[64 + i];
-                        const float a = __fdividef(g, 1.0f + __expf(-g)) * u;
-                        accv[i] = a;
-                        amax = fmaxf(amax, fabsf(a));
-                    }
+                for (int i = 0; i < 16; i++) {
+                    float g0, g1, u0, u1;
+                    ptx::unpack_f32x2(acc2[i], g0, g1);
+                    ptx::unpack_f32x2(acc2[16 + i], u0, u1);
+                    av[2 * i] = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+                    av[2 * i + 1] = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                    amax = fmaxf(amax, fmaxf(fabsf(av[2 * i]), fabsf(av[2 * i + 1])));
                 }
-                sm->amax[tile_par][wg][row] = amax;
+                if (!warp_valid) amax = 0.0f;
+                sm->amax[tile_par][wq][row] = amax;
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&sm->amax_bar[tile_par]);
                 if (!warp_wait(&sm->amax_bar[tile_par], amax_ph[tile_par])) goto done;
                 amax_ph[tile_par] ^= 1;
-                amax = fmaxf(amax, sm->amax[tile_par][wg ^ 1][row]);
+                amax = fmaxf(fmaxf(sm->amax[tile_par][0][row], sm->amax[tile_par][1][row]),
+                             fmaxf(sm->amax[tile_par][2][row], sm->amax[tile_par][3][row]));
                 if (row_ok) {
                     const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
                     const float inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 1.0f;
-                    uint32_t packed[16];
+                    uint32_t packed[8];
 #pragma unroll
-                    for (int i = 0; i < 16; i++) {
+                    for (int i = 0; i < 8; i++) {
                         uint32_t wv = 0;
 #pragma unroll
                         for (int b = 0; b < 4; b++) {
-                            uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(accv[i * 4 + b] * inv, __NV_SATFINITE, __NV_E4M3);
+                            uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(av[i * 4 + b] * inv, __NV_SATFINITE, __NV_E4M3);
                             wv |= q << (8 * b);
                         }
                         packed[i] = wv;
                     }
-                    uint4* dst = reinterpret_cast<uint4*>(p.act_q + grow * p.I + n_tile * 128 + wg * 64);
-#pragma unroll
-                    for (int i = 0; i < 4; i++)
-                        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-                    if (wg == 0) p.act_s[grow * (p.I / 128) + n_tile] = scale;
+                    uint4* dst = reinterpret_cast<uint4*>(p.act_q + grow * p.I + n_tile * 128 + wq * 32);
+                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    if (wq == 0) p.act_s[grow * (p.I / 128) + n_tile] = scale;
                 }
                 tile_par ^= 1;
             } else if (warp_valid) {
-                // out[token] += w * acc.  The accumulator row of a lane is transposed through shared memory
-                // 16 columns at a time so that one red instruction covers 8 rows x 64 contiguous bytes
-                // instead of 32 rows x 16 bytes (4 times fewer memory requests).
-                const int tok = row_ok ? p.row_tok[grow] : -1;
                 const float w = row_ok ? p.row_w[grow] : 0.0f;
-                float (*st)[20] = sm->stage[warp];
-                float* const out_col = p.out + n_tile * 256 + wg * 128;
-                const int sub_row = lane >> 2, seg = lane & 3;
+                float (*st)[12] = sm->stage[warp];
+                const int sub_row = lane >> 1, seg = lane & 1;
+                if (MODE == 2) {
+                    // out[token] += w * acc.  The accumulator row of a lane is transposed through shared memory
+                    // 8 columns at a time so that one red instruction covers 16 rows x 32 contiguous bytes
+                    // instead of 32 rows x 16 bytes.
+                    const int tok = row_ok ? p.row_tok[grow] : -1;
+                    float* const out_col = p.out + n_tile * 256 + wq * QCOLS;
 #pragma unroll
-                for (int pass = 0; pass < 8; pass++) {
-                    __syncwarp();
+                    for (int pass = 0; pass < QCOLS / 8; pass++) {
+                        float v[8];
 #pragma unroll
-                    for (int q = 0; q < 4; q++)
-                        *reinterpret_cast<float4*>(&st[lane][q * 4]) =
-                            make_float4(w * accv[pass * 16 + q * 4], w * accv[pass * 16 + q * 4 + 1],
-                                        w * accv[pass * 16 + q * 4 + 2], w * accv[pass * 16 + q * 4 + 3]);
-                    __syncwarp();
+                        for (int i = 0; i < 4; i++) ptx::unpack_f32x2(acc2[pass * 4 + i], v[2 * i], v[2 * i + 1]);
+                        __syncwarp();
+                        *reinterpret_cast<float4*>(&st[lane][0]) = make_float4(w * v[0], w * v[1], w * v[2], w * v[3]);
+                        *reinterpret_cast<float4*>(&st[lane][4]) = make_float4(w * v[4], w * v[5], w * v[6], w * v[7]);
+                        __syncwarp();
 #pragma unroll
-                    for (int k = 0; k < 4; k++) {
-                        const int r = 8 * k + sub_row;
-                        const int tok_r = __shfl_sync(0xffffffffu, tok, r);
-                        const float4 v = *reinterpret_cast<const float4*>(&st[r][seg * 4]);
-                        if (tok_r >= 0) red_add_v4(out_col + (size_t)tok_r * p.D + pass * 16 + seg * 4, v.x, v.y, v.z, v.w);
+                        for (int k = 0; k < 2; k++) {
+                            const int r = 16 * k + sub_row;
+                            const int tok_r = __shfl_sync(0xffffffffu, tok, r);
+                            const float4 x4 = *reinterpret_cast<const float4*>(&st[r][seg * 4]);
+                            if (tok_r >= 0) red_add_v4(out_col + (size_t)tok_r * p.D + pass * 8 + seg * 4, x4.x, x4.y, x4.z, x4.w);
+                        }
+                    }
+                } else {
+                    // rows[r] = w * acc, plain stores (same transposition: 16 rows x 32 bytes per instruction)
+                    const long long grow0 = (long long)p.offsets[e] + m_tile * BM + (warp & 3) * 32;
+                    const int rows_ok = min(32, cnt - (m_tile * BM + (warp & 3) * 32));
+                    float* const out_col = p.out + n_tile * 256 + wq * QCOLS;
+#pragma unroll
+                    for (int pass = 0; pass < QCOLS / 8; pass++) {
+                        float v[8];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) ptx::unpack_f32x2(acc2[pass * 4 + i], v[2 * i], v[2 * i + 1]);
+                        __syncwarp();
+                        *reinterpret_cast<float4*>(&st[lane][0]) = make_float4(w * v[0], w * v[1], w * v[2], w * v[3]);
+                        *reinterpret_cast<float4*>(&st[lane][4]) = make_float4(w * v[4], w * v[5], w * v[6], w * v[7]);
+                        __syncwarp();
+#pragma unroll
+                        for (int k = 0; k < 2; k++) {
+                            const int r = 16 * k + sub_row;
+                            const float4 x4 = *reinterpret_cast<const float4*>(&st[r][seg * 4]);
+                            if (r < rows_ok)
+                                *reinterpret_cast<float4*>(out_col + (size_t)(grow0 + r) * p.D + pass * 8 + seg * 4) = x4;
+                        }
                     }
                 }
             }
@@ -376,8 +420,41 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 done:
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 9) ptx::tmem_dealloc(tmem_base, 512);
+    if (warp == W_MMA0) ptx::tmem_dealloc(tmem_base, 512);
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
+}
+
+// Deterministic combine: out[t,:] = sum over the token's K slots, in ascending expert order (ties cannot
+// occur: an expert appears at most once per token), of rows[row_of_pair[t*K+k],:].  One block per token.
+__global__ void __launch_bounds__(256)
+reduce_rows_kernel(const float* __restrict__ rows, const int* __restrict__ pair_row, const int* __restrict__ ids,
+                   int K, int D, float* __restrict__ out) {
+    const int t = blockIdx.x;
+    __shared__ int order[64];
+    if (threadIdx.x == 0) {
+        // slots sorted by expert id (K <= 64), skipped slots (row < 0) dropped
+        int n = 0;
+        for (int k = 0; k < K; k++)
+            if (pair_row[t * K + k] >= 0) order[n++] = k;
+        for (int i = 1; i < n; i++) {
+            const int kk = order[i];
+            int j = i - 1;
+            while (j >= 0 && ids[t * K + order[j]] > ids[t * K + kk]) { order[j + 1] = order[j]; j--; }
+            order[j + 1] = kk;
+        }
+        for (int i = n; i < K; i++) order[i] = -1;
+    }
+    __syncthreads();
+    for (int c = threadIdx.x * 4; c < D; c += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < K; i++) {
+            const int k = order[i];
+            if (k < 0) break;
+            const float4 v = *reinterpret_cast<const float4*>(rows + (size_t)pair_row[t * K + k] * D + c);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        *reinterpret_cast<float4*>(out + (size_t)t * D + c) = acc;
+    }
 }
 
 // Expert-sorted copy of the FP8 rows.  One block per sorted row, grid-stride (the number of valid
@@ -386,7 +463,7 @@ __global__ void __launch_bounds__(128)
 sort_rows_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, const int* __restrict__ row_pair,
                      const int* __restrict__ offsets, const float* __restrict__ wts, int E, int K, int D,
                      uint8_t* __restrict__ sq, float* __restrict__ ss, int* __restrict__ row_tok,
-                     float* __restrict__ row_w) {
+                     float* __restrict__ row_w, int* __restrict__ pair_row) {
     const int total = offsets[E];
     const int nb = D / 128;
     for (int r = blockIdx.x; r < total; r += gridDim.x) {
@@ -399,17 +476,22 @@ sort_rows_fp8_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ x
         if (threadIdx.x == 0) {
             row_tok[r] = tok;
             row_w[r] = wts[pair];
+            if (pair_row) pair_row[pair] = r;      // deterministic combine: sorted row of (token, slot)
         }
     }
 }
 
 // Optional per-kernel timing: CUDA events recorded on the launch stream around the two grouped
-// GEMMs (used by the benchmark for the roofline line; off by default).
+// GEMMs (used by the benchmark for the roofline line; off by default).  The record belongs to the
+// workspace, so host threads that drive different GPUs (or different workspaces) do not share it.
 constexpr int PROF_SLOTS = 256;
-bool g_prof_on = false;
-cudaEvent_t g_prof_ev[PROF_SLOTS][4];
-bool g_prof_created = false;
-long long g_prof_calls = 0;      // layer calls recorded since profiling was enabled
+}  // namespace
+struct b200_gemm_profile {
+    bool on = false;
+    cudaEvent_t ev[PROF_SLOTS][4];
+    long long calls = 0;      // layer calls recorded since profiling was enabled
+};
+namespace {
 
 __global__ void pack_weights_kernel(int which, const uint8_t* __restrict__ src, uint8_t* __restrict__ packed, int E,
                                     int D, int I, long long chunks) {
@@ -426,8 +508,9 @@ __global__ void pack_weights_kernel(int which, const uint8_t* __restrict__ src, 
     const int e = (int)(t / NT);
     long long row;
     if (which == 1) {
-        const int j0 = nt * 128, q = r >> 6, rr = r & 63;
-        row = (long long)e * 2 * I + ((q & 1) ? I : 0) + j0 + ((q >> 1) ? 64 : 0) + rr;
+        // quarter q of the tile's 256 rows = [gate j0+32q .. +31 | up j0+32q .. +31]
+        const int j0 = nt * 128, q = r >> 6, up = (r >> 5) & 1, rr = r & 31;
+        row = (long long)e * 2 * I + (up ? I : 0) + j0 + 32 * q + rr;
     } else {
         row = (long long)e * D + nt * 256 + r;
     }
@@ -438,6 +521,7 @@ __global__ void pack_weights_kernel(int which, const uint8_t* __restrict__ src, 
 struct Fp8Scratch {
     float* partials; int* ids; float* wts; int* hist; int* counts; int* offsets; int* row_pair;
     uint8_t* sq; float* ss; int* row_tok; float* row_w; uint8_t* act_q; float* act_s;
+    int* pair_row; float* rows;     // deterministic combine only
 };
 
 void carve_fp8(WsCarver& c, const b200_moe_fp8_config* cfg, bool with_route, Fp8Scratch& s) {
@@ -457,6 +541,9 @@ void carve_fp8(WsCarver& c, const b200_moe_fp8_config* cfg, bool with_route, Fp8
     s.row_w = c.take<float>(TK);
     s.act_q = c.take<uint8_t>(TK * I);
     s.act_s = c.take<float>(TK * (I / 128));
+    const bool det = (cfg->flags & B200_MOE_DETERMINISTIC) != 0;
+    s.pair_row = det ? c.take<int>(TK) : nullptr;
+    s.rows = det ? c.take<float>(TK * D) : nullptr;
 }
 
 int check_fp8_cfg(const b200_moe_fp8_config* cfg) {
@@ -465,6 +552,7 @@ int check_fp8_cfg(const b200_moe_fp8_config* cfg) {
     if (cfg->hidden_dim <= 0 || cfg->intermediate_dim <= 0) return B200_BAD_SHAPE;
     if (cfg->hidden_dim % 256 || cfg->intermediate_dim % 128) return B200_BAD_SHAPE;
     if (cfg->num_experts > MAX_E) return B200_UNSUPPORTED;
+    if ((cfg->flags & B200_MOE_DETERMINISTIC) && cfg->top_k > 64) return B200_UNSUPPORTED;
     if ((long long)cfg->num_experts * 2 * cfg->intermediate_dim > 0x7fffffffLL) return B200_UNSUPPORTED;
     if ((long long)cfg->num_experts * cfg->hidden_dim > 0x7fffffffLL) return B200_UNSUPPORTED;
     return B200_OK;
@@ -480,9 +568,11 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     // ids from this library's router are trusted (hist given); ids from outside get the duplicate check
     int st = launch_permute(ids, T, K, E, hist, hist != nullptr, s.counts, s.offsets, s.row_pair, stream);
     if (st) return st;
+    const bool det = (cfg->flags & B200_MOE_DETERMINISTIC) != 0 && do_gemm2;
+    if (det) B200_CUDA_TRY(cudaMemsetAsync(s.pair_row, 0xFF, sizeof(int) * (size_t)TK, stream));
     const unsigned sort_blocks = (unsigned)(TK < (long long)ws->sm_count * 32 ? TK : (long long)ws->sm_count * 32);
     sort_rows_fp8_kernel<<<sort_blocks, 128, 0, stream>>>(xq, xs, s.row_pair, s.offsets, wts, E, K, D, s.sq, s.ss,
-                                                           s.row_tok, s.row_w);
+                                                           s.row_tok, s.row_w, det ? s.pair_row : nullptr);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
 
@@ -492,11 +582,13 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
                                            (int)GEMM_SMEM_BYTES));
         B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)GEMM_SMEM_BYTES));
+        B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)GEMM_SMEM_BYTES));
     }
+    b200_gemm_profile* prof = (ws->gemm_prof && ws->gemm_prof->on) ? ws->gemm_prof : nullptr;
+    const int slot = prof ? (int)(prof->calls % PROF_SLOTS) : 0;
     CUtensorMap ta, tb;
     GemmParams p{};
-    p.trace = g_gemm_trace;
-    p.trace_warp = g_gemm_trace_warp;
     p.offsets = s.offsets; p.E = E; p.D = D; p.I = I; p.status = ws->d_status; p.total_rows = TK;
 
     // GEMM1
@@ -504,12 +596,12 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     if (st) return st;
     p.packed = packed ? 1 : 0;
     if (packed) st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I * (D / 128), 128, 256);
-    else        st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, 64);
+    else        st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, 32);
     if (st) return st;
     p.a_scale = s.ss; p.w_scale = w1s; p.act_q = s.act_q; p.act_s = s.act_s;
-    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][0], stream));
+    if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][0], stream));
     grouped_gemm_fp8_kernel<1><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
-    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][1], stream));
+    if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][1], stream));
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     if (!do_gemm2) return B200_OK;
@@ -520,12 +612,24 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     if (packed) st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D * (I / 128), 128, 256);
     else        st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D, I, 256);
     if (st) return st;
-    if (p.trace) p.trace += 6 * TRACE_CAP;      // second half of the buffer for GEMM2
-    p.a_scale = s.act_s; p.w_scale = w2s; p.row_tok = s.row_tok; p.row_w = s.row_w; p.out = out;
+    p.a_scale = s.act_s; p.w_scale = w2s; p.row_tok = s.row_tok; p.row_w = s.row_w;
+    if (det) {
+        p.out = s.rows;
+        if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][2], stream));
+        grouped_gemm_fp8_kernel<3><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+        b200_count_launch(1);
+        B200_CUDA_TRY(cudaGetLastError());
+        reduce_rows_kernel<<<T, 256, 0, stream>>>(s.rows, s.pair_row, ids, K, D, out);
+        if (prof) { B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][3], stream)); prof->calls++; }
+        b200_count_launch(1);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    }
+    p.out = out;
     B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)T * D, stream));
-    if (g_prof_on) B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][2], stream));
+    if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][2], stream));
     grouped_gemm_fp8_kernel<2><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
-    if (g_prof_on) { B200_CUDA_TRY(cudaEventRecord(g_prof_ev[g_prof_calls % PROF_SLOTS][3], stream)); g_prof_calls++; }
+    if (prof) { B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][3], stream)); prof->calls++; }
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
@@ -535,33 +639,36 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
 
 extern "C" {
 
-// Debug aid (not in the public header): timeline stamps of CTA 0 of the next grouped GEMM launches.
-__attribute__((visibility("default"))) void b200_debug_gemm_trace(long long* dev_buf) { g_gemm_trace = dev_buf; }
-__attribute__((visibility("default"))) void b200_debug_gemm_trace_warp(int warp) { g_gemm_trace_warp = warp & 7; }
-
-int b200_moe_fp8_profile(int enable) {
-    if (enable && !g_prof_created) {
+int b200_moe_fp8_profile(b200_ws* ws, int enable) {
+    if (!ws) ws = b200_default_ws();
+    if (!ws) return B200_CUDA_ERROR;
+    if (!ws->gemm_prof) {
+        if (!enable) return B200_OK;
+        b200_gemm_profile* pr = new b200_gemm_profile();
         for (int i = 0; i < PROF_SLOTS; i++)
-            for (int j = 0; j < 4; j++) B200_CUDA_TRY(cudaEventCreate(&g_prof_ev[i][j]));
-        g_prof_created = true;
+            for (int j = 0; j < 4; j++) B200_CUDA_TRY(cudaEventCreate(&pr->ev[i][j]));
+        ws->gemm_prof = pr;
     }
-    g_prof_on = enable != 0;
-    g_prof_calls = 0;
+    ws->gemm_prof->on = enable != 0;
+    ws->gemm_prof->calls = 0;
     return B200_OK;
 }
 
-int b200_moe_fp8_profile_read(float* gemm1_ms, float* gemm2_ms, int* calls) {
+int b200_moe_fp8_profile_read(b200_ws* ws, float* gemm1_ms, float* gemm2_ms, int* calls) {
     if (!gemm1_ms || !gemm2_ms || !calls) return B200_BAD_ARG;
-    const int n = (int)(g_prof_calls < PROF_SLOTS ? g_prof_calls : PROF_SLOTS);
+    if (!ws) ws = b200_default_ws();
+    if (!ws) return B200_CUDA_ERROR;
+    const b200_gemm_profile* pr = ws->gemm_prof;
+    const int n = pr ? (int)(pr->calls < PROF_SLOTS ? pr->calls : PROF_SLOTS) : 0;
     *calls = n;
     *gemm1_ms = *gemm2_ms = 0.0f;
     if (n == 0) return B200_OK;
     double s1 = 0.0, s2 = 0.0;
     for (int i = 0; i < n; i++) {
         float a = 0.f, b = 0.f;
-        B200_CUDA_TRY(cudaEventSynchronize(g_prof_ev[i][3]));
-        B200_CUDA_TRY(cudaEventElapsedTime(&a, g_prof_ev[i][0], g_prof_ev[i][1]));
-        B200_CUDA_TRY(cudaEventElapsedTime(&b, g_prof_ev[i][2], g_prof_ev[i][3]));
+        B200_CUDA_TRY(cudaEventSynchronize(pr->ev[i][3]));
+        B200_CUDA_TRY(cudaEventElapsedTime(&a, pr->ev[i][0], pr->ev[i][1]));
+        B200_CUDA_TRY(cudaEventElapsedTime(&b, pr->ev[i][2], pr->ev[i][3]));
         s1 += a; s2 += b;
     }
     *gemm1_ms = (float)(s1 / n);
@@ -640,8 +747,8 @@ int b200_moe_fp8_forward_packed(b200_ws* ws, const uint8_t* xq, const float* xs,
     return forward_impl(ws, xq, xs, gate_w, bias, w1p, w1s, w2p, w2s, out, cfg, true, stream);
 }
 
-// Weight pre-tiling.  which = 1: w1 [E,2I,D] -> tiles of 256 accumulator rows (gate j0..+63, up j0..+63,
-// gate j0+64..+127, up j0+64..+127 for j0 = 128 * n_tile); which = 2: w2 [E,D,I] -> tiles of 256 rows.
+// Weight pre-tiling.  which = 1: w1 [E,2I,D] -> tiles of 256 accumulator rows (for q = 0..3: gate
+// j0+32q..+31, then up j0+32q..+31, with j0 = 128 * n_tile); which = 2: w2 [E,D,I] -> tiles of 256 rows.
 // packed[(((e * NT + n_tile) * nkb + kb) * 256 + r) * 128 + b] = src[e][row(n_tile, r)][kb * 128 + b].
 int b200_moe_fp8_pack_weights(int which, const uint8_t* src, uint8_t* packed, int E, int D, int I,
                               b200_stream_t stream) {

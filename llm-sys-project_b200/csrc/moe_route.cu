@@ -387,16 +387,8 @@ permute_kernel(const int* __restrict__ ids, int TK, int K, int E, const int* __r
 // 8 * TY rows (TY = 8..16, 16 * TY threads) so that the launcher can pick the height whose tile
 // count fills whole waves of resident CTAs, and the next k-tile is fetched into registers while
 // the current one is multiplied.
-__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
-    unsigned long long d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
+using ptx::pack_f32x2;
+using ptx::fma_f32x2;
 
 template <int TY>
 __global__ void __launch_bounds__(16 * TY, 512 / (16 * TY))

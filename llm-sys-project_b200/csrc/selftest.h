@@ -1,0 +1,25 @@
+/* Test hooks of the library: exported symbols that only the test suite calls.  They are not part of
+ * the public interface (include/b200_moe_dsa.h) and may change without notice. */
+#pragma once
+#include "../../include/b200_moe_dsa.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Tensor-core self check: D[128,N] = A[128,K] * B[N,K]^T through the same shared-memory
+ * descriptors the production kernels use.  mode 0: bf16, both operands K-major;
+ * mode 1: bf16, B stored [K,N] (MN-major); mode 2: e4m3 K-major; mode 3: bf16 CTA pair. a/b are raw bits. */
+B200_API int b200_umma_selftest(int mode, const void* a, const void* b, float* d, int N, int K,
+                                b200_stream_t stream);
+
+/* Runs the give-up branch of the bounded device-side waits: one block, two waiters (a spinning one
+ * and a sleeping one) on an mbarrier that nobody signals, compiled with a wait limit of 2 ms.
+ * Both return, the block records B200_TIMEOUT in the workspace status word (read it with
+ * b200_ws_device_status) and exits normally; nothing traps and no wait is unbounded.
+ * elapsed_ns [2] (device, may be NULL): nanoseconds each waiter spent before giving up. */
+B200_API int b200_wait_selftest(b200_ws* ws, long long* elapsed_ns, b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

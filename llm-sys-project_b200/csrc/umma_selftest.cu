@@ -9,6 +9,7 @@
 //   mode 3  bf16, A K-major without swizzle (8x16-byte core matrices, chunk-major), B as mode 0
 //                                                          (DSA: P tile written by the softmax warps)
 #include "common.cuh"
+#include "selftest.h"
 
 namespace {
 

@@ -20,14 +20,26 @@ u8p = np.ctypeslib.ndpointer(np.uint8, flags="C_CONTIGUOUS")
 u16p = np.ctypeslib.ndpointer(np.uint16, flags="C_CONTIGUOUS")
 
 
+def reference_dir():
+    """A checkout of the reference project, or None: $B200_REFERENCE_DIR, else a directory named
+    ``reference`` beside the repository, else ``baseline/_ref`` inside it."""
+    root = os.path.dirname(HERE)
+    for p in (os.environ.get("B200_REFERENCE_DIR"), os.path.join(os.path.dirname(root), "reference"),
+              os.path.join(root, "baseline", "_ref")):
+        if p and os.path.exists(os.path.join(p, "tests", "test_moe.cu")):
+            return p
+    return None
+
+
 def build(force=False):
     """Compile liboracle.so (and _ref/ when a reference checkout is present)."""
     so = os.path.join(HERE, "liboracle.so")
     src = os.path.join(HERE, "moe_dsa_oracle.c")
     stale = (not os.path.exists(so)) or os.path.getmtime(so) < os.path.getmtime(src)
-    if force or stale or (os.path.exists("/root/reference/tests/test_moe.cu")
-                          and not os.path.exists(os.path.join(HERE, "_ref", "libref_moe.so"))):
-        subprocess.run(["make", "-C", HERE], check=True, capture_output=True)
+    ref = reference_dir()
+    if force or stale or (ref is not None and not os.path.exists(os.path.join(HERE, "_ref", "libref_moe.so"))):
+        cmd = ["make", "-C", HERE] + ([f"REF={ref}"] if ref else [])
+        subprocess.run(cmd, check=True, capture_output=True)
     return so
 
 

@@ -23,6 +23,10 @@ def test_header_symbols_are_exported(b200):
     missing = [s for s in declared if not hasattr(L, s)]
     assert not missing, missing
     assert sorted(b200.EXPORTED_SYMBOLS) == declared
+    # the test hooks are exported too, but are not part of the public header
+    hooks = open(os.path.join(ROOT, "llm-sys-project_b200", "csrc", "selftest.h")).read()
+    for s in b200.TEST_ONLY_SYMBOLS:
+        assert hasattr(L, s) and s in hooks and s not in declared
 
 
 def test_reference_cxx_symbols_are_exported(b200):
@@ -43,7 +47,8 @@ def test_config_struct_layouts(b200):
     d = b200.DsaConfig(4, 16, 512, 64, 256, 64, 4096)
     assert (d.num_selected_kv, d.page_size, d.total_kv_tokens) == (256, 64, 4096)
     assert b200.MoEConfig is b200.MoeConfig and b200.DSAConfig is b200.DsaConfig
-    assert C.sizeof(b200.MoeFp8Config) == 36
+    assert C.sizeof(b200.MoeFp8Config) == 40
+    assert b200.MoeFp8Config(1, 2, 3, 4, 5, 1, 1, 1, 2.5).flags == 0          # trailing flags default to 0
 
 
 def test_status_strings_and_argument_checks_without_gpu(b200):
@@ -65,8 +70,9 @@ def test_synthetic_generator_host_twin(b200):
 
 
 def test_reference_drivers_linked_when_checkout_present():
+    import oracle
     drv = os.path.join(ROOT, "oracle", "_ref", "drivers")
-    if not os.path.exists("/root/reference/tests/test_moe.cu"):
+    if oracle.reference_dir() is None:
         return
     for exe in ("test_moe", "test_dsa", "bench_moe", "bench_dsa"):
         assert os.access(os.path.join(drv, exe), os.X_OK), f"{exe}: run python llm-sys-project_b200/build.py"
