@@ -310,7 +310,7 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     # both buffers hold a result of the same input (the scatter-add order differs from run to run)
     e2e_same = bool(torch.allclose(out_hs[0][:64], out_hs[1][:64], rtol=1e-4, atol=1e-5))
 
-    threads = oracle.max_threads()
+    threads = oracle.host_threads()
     cpu = moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out, args.cpu_tokens, threads)
     hbm, bf16_tf, which = measured_peaks()
     g1_bytes, active, rows = moe_gemm1_bytes(counts)
@@ -359,7 +359,59 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     return res
 
 
-def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
+def ep_parity_sample(b200, torch, oracle, layer, placement, world, xq, xs, out_dev, ids_dev, n_tokens, threads):
+    """Oracle check of the expert-parallel layer on rank 0: a seeded sample of this rank's tokens through
+    the CPU emulation.  The experts they use live on other GPUs; their weights are regenerated here from the
+    seeds (one owner rank's set at a time into a scratch buffer), so the check needs no communication."""
+    c = MOE
+    El = c["E"] // world
+    rng = np.random.default_rng(5)
+    toks = np.sort(rng.choice(c["T"], n_tokens, replace=False)).astype(np.int32)
+    sel_t = torch.from_numpy(toks).to(xq.device).long()
+    xq_h, xs_h = xq.index_select(0, sel_t).cpu().numpy(), xs.index_select(0, sel_t).cpu().numpy()
+    wg_h, bias_h = layer.gate_w.cpu().numpy(), layer.bias.cpu().numpy()
+    oracle.set_threads(threads)
+    t0 = time.perf_counter()
+    ids, wts = oracle.route_grouped(xq_h, xs_h, wg_h, bias_h, c["K"], c["n_group"], c["topk_group"], c["routed_scale"])
+    cpu_s = time.perf_counter() - t0
+    ids_ok = bool(np.array_equal(ids_dev.index_select(0, sel_t).cpu().numpy(), ids))
+    if isinstance(placement, (tuple, list)):
+        owner, local = placement[0].numpy().astype(np.int64), placement[1].numpy().astype(np.int64)
+    elif placement == "strided":
+        owner, local = np.arange(c["E"]) % world, np.arange(c["E"]) // world
+    else:
+        owner, local = np.arange(c["E"]) // El, np.arange(c["E"]) % El
+    uniq = np.unique(ids)
+    remap = -np.ones(c["E"], np.int32)
+    remap[uniq] = np.arange(len(uniq), dtype=np.int32)
+    w1q_h = np.empty((len(uniq), 2 * c["I"], c["D"]), np.uint8)
+    w1s_h = np.empty((len(uniq), 2 * c["I"] // 128, c["D"] // 128), np.float32)
+    w2q_h = np.empty((len(uniq), c["D"], c["I"]), np.uint8)
+    w2s_h = np.empty((len(uniq), c["D"] // 128, c["I"] // 128), np.float32)
+    s1q, s1s = torch.empty_like(layer.w1q), torch.empty_like(layer.w1s)
+    s2q, s2s = torch.empty_like(layer.w2q), torch.empty_like(layer.w2s)
+    for r in sorted(set(owner[uniq].tolist())):
+        b200.fill_normal_fp8_w128_(s1q, s1s, 1000 + r, 0.02)        # the weights rank r generated for itself
+        b200.fill_normal_fp8_w128_(s2q, s2s, 2000 + r, 0.02)
+        mine = uniq[owner[uniq] == r]
+        sel = torch.from_numpy(local[mine]).to(xq.device)
+        dst = remap[mine]
+        w1q_h[dst], w1s_h[dst] = s1q.index_select(0, sel).cpu().numpy(), s1s.index_select(0, sel).cpu().numpy()
+        w2q_h[dst], w2s_h[dst] = s2q.index_select(0, sel).cpu().numpy(), s2s.index_select(0, sel).cpu().numpy()
+    del s1q, s1s, s2q, s2s
+    t0 = time.perf_counter()
+    ref = oracle.moe_fp8_experts(xq_h, xs_h, w1q_h, w1s_h, w2q_h, w2s_h, remap[ids], wts,
+                                 np.arange(n_tokens, dtype=np.int32))
+    cpu_s += time.perf_counter() - t0
+    got = out_dev.index_select(0, sel_t).float().cpu().numpy()
+    err = np.abs(got - ref)
+    viol = err > ATOL + RTOL * np.abs(ref)
+    return {"cpu_seconds": cpu_s, "checked_tokens": int(n_tokens), "rank": 0, "ids_bit_equal": ids_ok, "ok": bool(ids_ok and not viol.any()),
+            "violations": int(viol.sum()), "max_abs_err": float(err.max()), "ref_absmax": float(np.abs(ref).max()),
+            "tolerance": f"{RTOL} rel + {ATOL} abs", "experts_regenerated": int(len(uniq))}
+
+
+def bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler):
     c = MOE
     layer, xq, xs = build_moe(b200, torch, dev, world, rank)
     placement = EP_PLACEMENT
@@ -469,6 +521,19 @@ def bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler):
                     "hot_gpu_gemm_tflops_lower_bound": flops_hot / (ms * 1e-3) / 1e12,
                     "fp8_peak_tflops_nominal": 4500.0},
     }
+    if rank == 0:
+        # the timed configuration itself (bf16 combine, this placement, Zipf bias) against the CPU emulation
+        out, ids, _ = ep.forward(xq, xs)
+        torch.cuda.synchronize()
+        threads = oracle.host_threads()
+        par = ep_parity_sample(b200, torch, oracle, layer, placement, world, xq, xs, out, ids,
+                               min(args.cpu_tokens, 12), threads)
+        cpu_s = par.pop("cpu_seconds")
+        res["parity"] = par
+        res["cpu_baseline"] = {"value": par["checked_tokens"] / cpu_s, "unit": "tokens/s", "cores": threads,
+                               "kind": "port",
+                               "sample": f"{par['checked_tokens']} seeded tokens of rank 0 (routing + 8 experts each) "
+                                         f"through the fp32 CPU emulation, {cpu_s:.2f} s"}
     return res
 
 
@@ -582,7 +647,7 @@ def bench_dsa(b200, torch, oracle, dev, args, sampler, do_cpu):
         torch.cuda.synchronize()
         as_u16 = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
         gkc = as_u16(layer.kc[idx.reshape(-1)]); gkp = as_u16(layer.kp[idx.reshape(-1)]); gv = as_u16(layer.v[idx.reshape(-1)])
-        threads = oracle.max_threads()
+        threads = oracle.host_threads()
         oracle.set_threads(threads)
         t0 = time.perf_counter()
         ref = oracle.dsa_forward_bf16_gathered(as_u16(qn[:nq]), as_u16(qp[:nq]), gkc, gkp, gv, c["S"])
@@ -605,7 +670,7 @@ def reference_arm(args, world, rank):
     import oracle
     b200 = load_package()
     c = MOE
-    threads = oracle.max_threads()
+    threads = oracle.host_threads()      # the affinity mask, not OMP_NUM_THREADS (launchers set that to 1 per rank)
     oracle.set_threads(threads)
     n_tok, n_exp = args.cpu_tokens, 2
     # bounded sample of the same workload: n_tok tokens, their 8 experts mapped onto a pool of n_exp
@@ -640,7 +705,8 @@ def reference_arm(args, world, rank):
             "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port",
                              "sample": f"{n_tok} tokens per step (routing + 8 experts each), fp32 CPU emulation of "
                                        "the FP8 sequence; the reference's own CPU code is fp32-only and has no "
-                                       "FP8 / grouped-routing path"},
+                                       f"FP8 / grouped-routing path; the tokens' experts are mapped onto a pool of {n_exp} "
+                                       "generated experts (88 MB of weights, partly cache-resident, which favours the CPU)"},
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -690,7 +756,7 @@ def main():
     elif world == 1:
         moe = bench_moe_single(b200, torch, oracle, dev, args, sampler)
     else:
-        moe = bench_moe_ep(b200, torch, dist, dev, args, world, rank, sampler)
+        moe = bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler)
     clocks = sampler.summary()
     dsa = None
     if not args.skip_dsa:

@@ -5,7 +5,12 @@
  * pointers and sizes, works asynchronously on the given CUDA stream and does
  * no host synchronisation.  Scratch memory comes from a workspace handle
  * (NULL selects a lazily created per-device default workspace).  A workspace
- * serves one call at a time; calls on one stream are ordered by the stream.
+ * serves one call at a time: calls that share a workspace (ws = NULL included, and
+ * the C++ functions with the reference's names, which use the default workspace)
+ * must be ordered by one stream or by events; concurrent streams or host threads
+ * need a workspace each (b200_ws_create).  The reference allocates its scratch
+ * inside every call (kernels/moe/naive_moe.cu:408-420), so two streams that were
+ * independent there share scratch here unless they bring their own workspace.
  *
  * The comment above each declaration names the reference interface it stands
  * in for (file:line in arun-reddy-a/llm-sys-project).
@@ -204,7 +209,8 @@ B200_API int b200_dsa_forward_f32(b200_ws* ws, const float* q_nope, const float*
                                   const float* kp, const float* v, const int* idx, float* out,
                                   const b200_dsa_config* cfg, b200_stream_t stream);
 /* Same layer on bf16 inputs with fp32 accumulation on the tensor cores (tcgen05/TMEM);
- * out [Q,H,Dc] fp32.  Requires H == 128 or 64, Dc == 512, Dp == 64, S % 64 == 0. */
+ * out [Q,H,Dc] fp32.  Requires H <= 128, Dc == 512, Dp == 64, S % 32 == 0 (S % 128 == 0 runs the
+ * fastest kernel, S % 64 == 0 the next), 16-byte aligned pointers. */
 B200_API int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe,
                                    const uint16_t* kc, const uint16_t* kp, const uint16_t* v, const int* idx,
                                    float* out, const b200_dsa_config* cfg, b200_stream_t stream);
@@ -214,15 +220,17 @@ B200_API int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const ui
  * latency-critical loops that cannot tolerate a workspace that grows (and synchronises the device
  * when it does).  The split-KV partial results go to a 16 MiB array built into the library (every
  * GPU that loads the library holds it until the process exits) instead of the workspace; the call
- * uses no workspace and calls no allocating routine.  Shapes whose partial results do not fit
- * (queries x splits x 256 KiB + 1 KiB each, beyond 16 MiB) are rejected with B200_UNSUPPORTED and
- * an explanatory b200_last_error_string.  The first call on each device looks up the array's
- * device address (cudaGetSymbolAddress) and sets the kernel's shared-memory limit, so make that
- * first call outside any stream capture.  All calls on a device share the one array: it keeps the
- * previous call's contents (only the status word is cleared, everything read is rewritten first),
- * and two calls that overlap on the GPU (different streams) race on it.  device_status, if not
- * NULL, is a caller-owned device int that is cleared and receives B200_TIMEOUT should a bounded
- * device-side wait run out. */
+ * uses no workspace and calls no allocating routine.  The array holds the partial results of 63
+ * (query, row range) pairs (257 KiB each: 128 x 512 fp32 outputs + 128 (max, sum) pairs), so a query's
+ * rows are split into at most floor(63 / queries) ranges (the workspace-backed call may use more on a
+ * small batch); 64 or more queries run one range each and use no scratch.  Every shape the kernel
+ * supports is therefore accepted up to 65535 queries per call; more are rejected with
+ * B200_UNSUPPORTED and an explanatory b200_last_error_string.  The first call on each device looks up
+ * the array's device address (cudaGetSymbolAddress) and sets the kernel's shared-memory limit, so make
+ * that first call outside any stream capture.  All calls on a device share the one array: it keeps the
+ * previous call's contents (everything read is rewritten first), and two calls that overlap on the GPU
+ * (different streams) race on it.  device_status (required) is a caller-owned device int that the call
+ * clears and that receives B200_TIMEOUT should a bounded device-side wait run out. */
 B200_API int b200_dsa_forward_bf16_static(const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
                                           const uint16_t* kp, const uint16_t* v, const int* idx, float* out,
                                           const b200_dsa_config* cfg, int* device_status, b200_stream_t stream);
@@ -260,6 +268,51 @@ B200_API int b200_ep_plan(const int* expert_ids, const float* expert_w, int T, i
  * overwritten; back holds fp32 rows or, with back_is_bf16 != 0, bf16 rows.  D % 8 == 0. */
 B200_API int b200_ep_sum_rows(const void* back, int back_is_bf16, const int* pos, int world, int T, int D,
                               float* out, b200_stream_t stream);
+
+/* Expert-parallel FP8 layer as one object per GPU (no reference counterpart: the reference is single-GPU;
+ * the loop being sharded is kernels/moe/naive_moe.cu:424-469).  One host thread or process per GPU.  The
+ * data plane is this library's own kernels over peer memory: every rank allocates an exchange buffer,
+ * the ranks swap its 64-byte handles out of band (any transport: a file, MPI, torch.distributed) and map
+ * each other's buffers; a step then runs without host synchronisation and without a collective call:
+ * rows are dispatched with peer stores, owners wait (bounded) on per-source ready words, the grouped
+ * GEMMs read local memory only, partial output rows go back with peer stores.  Ranks must call
+ * b200_ep_forward the same number of times (a step is a collective).  A wait that runs out sets
+ * B200_TIMEOUT in the status word (b200_ep_stats) and the step's output is then undefined; nothing hangs. */
+typedef struct b200_ep b200_ep;
+#define B200_EP_HANDLE_BYTES 64
+enum b200_ep_flags {
+    B200_EP_COMBINE_F32 = 2 /* partial rows travel back as fp32 instead of bf16 (twice the combine bytes) */
+};
+typedef struct b200_ep_config {
+    int rank, world;      /* this rank, number of ranks (<= 64); rank g holds num_experts / world experts */
+    int max_tokens;       /* upper bound of tokens per rank and step */
+    int num_experts;      /* global E */
+    int top_k, hidden_dim, intermediate_dim;
+    int scoring, n_group, topk_group;   /* as b200_moe_fp8_config */
+    float routed_scale;
+    int flags;            /* enum b200_ep_flags */
+    int wait_limit_ms;    /* bound of every device-side wait for a peer; 0 = 2000 */
+} b200_ep_config;
+/* Allocates the buffers on the current device.  owner_map / local_map [num_experts] (host arrays, both or
+ * neither): expert e lives on rank owner_map[e] as its local expert local_map[e]; NULL = consecutive blocks.
+ * handle_out receives B200_EP_HANDLE_BYTES bytes to hand to every other rank. */
+B200_API int b200_ep_create(b200_ep** ep, const b200_ep_config* cfg, const int* owner_map, const int* local_map,
+                            void* handle_out);
+/* handles: world * B200_EP_HANDLE_BYTES bytes, rank-major (this rank's own entry is ignored; may be NULL
+ * when world == 1).  Call once, after every rank has created its object. */
+B200_API int b200_ep_connect(b200_ep* ep, const void* handles);
+/* One layer step for this rank's num_tokens tokens (<= max_tokens): xq [T,D] e4m3 + xs [T,D/128]; the
+ * replicated router (gate_w [E,D], bias [E] or NULL); this rank's experts w1 [E/world,2I,D] + w1s, w2
+ * [E/world,D,I] + w2s in local order (packed != 0: pre-tiled by b200_moe_fp8_pack_weights); out [T,D] fp32,
+ * overwritten.  ids_out / w_out [T,K] (optional) receive the routing (global expert ids). */
+B200_API int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float* xs, const float* gate_w,
+                             const float* bias, const uint8_t* w1, const float* w1s, const uint8_t* w2,
+                             const float* w2s, int packed, float* out, int* ids_out, float* w_out,
+                             b200_stream_t stream);
+/* Synchronises `stream`; status (optional) receives and clears the device status word; send_counts /
+ * recv_counts [world] (optional) the rows this rank sent to / received from each rank in the last step. */
+B200_API int b200_ep_stats(b200_ep* ep, b200_stream_t stream, int* status, int* send_counts, int* recv_counts);
+B200_API int b200_ep_destroy(b200_ep* ep);
 
 /* --------------------------------------------------------------------------- */
 /* Synthetic inputs (stand in for utils/cuda_utils.cuh:56-60 random_fill at      */

@@ -44,6 +44,12 @@ class MoeFp8Config(C.Structure):
 MOE_DETERMINISTIC = 1      # MoeFp8Config.flags: fixed-order (experts ascending) combine, bit-reproducible
 
 
+class EpConfig(C.Structure):
+    _fields_ = ([(n, C.c_int) for n in ("rank", "world", "max_tokens", "num_experts", "top_k", "hidden_dim",
+                                        "intermediate_dim", "scoring", "n_group", "topk_group")]
+                + [("routed_scale", C.c_float), ("flags", C.c_int), ("wait_limit_ms", C.c_int)])
+
+
 MoEConfig, DSAConfig = MoeConfig, DsaConfig
 
 # every symbol include/b200_moe_dsa.h declares
@@ -57,11 +63,12 @@ EXPORTED_SYMBOLS = [
     "b200_moe_fp8_experts_packed", "b200_moe_fp8_gemm1_stage", "b200_moe_fp8_profile", "b200_moe_fp8_profile_read",
     "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
     "b200_dsa_softmax_f32", "b200_dsa_output_proj_f32",
-    "b200_ep_plan", "b200_ep_sum_rows",
+    "b200_ep_plan", "b200_ep_sum_rows", "b200_ep_create", "b200_ep_connect", "b200_ep_forward", "b200_ep_stats",
+    "b200_ep_destroy",
     "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128",
 ]
 # exported for the test suite only (declared in csrc/selftest.h, not in the public header)
-TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest"]
+TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest", "b200_ep_connect_loopback"]
 
 
 def lib():
@@ -249,11 +256,13 @@ def dsa_forward_bf16(q_nope, q_pe, kv_cache_compressed, kv_cache_positional, v_c
 
 
 def dsa_forward_bf16_static(q_nope, q_pe, kv_cache_compressed, kv_cache_positional, v_cache, sparse_indices, output,
-                            cfg, device_status=None, stream=None):
+                            cfg, device_status, stream=None):
     """bf16 decode for callers that may not allocate device memory (a pool that owns all of HBM, a
     plugin that only receives its input/output buffers): the split-KV partial results live in a
-    16 MiB array built into the library instead of the growable workspace.  Raises B200Error
-    (B200_UNSUPPORTED) when they would not fit.  Calls share the array; do not overlap them."""
+    16 MiB array built into the library instead of the growable workspace, and the row split is
+    limited to what that array holds.  device_status: caller-owned int32 CUDA tensor [1], cleared by
+    the call; B200_TIMEOUT lands there if a device-side wait runs out.  Calls share the array; do
+    not overlap them."""
     _check(lib().b200_dsa_forward_bf16_static(_p(q_nope), _p(q_pe), _p(kv_cache_compressed),
                                               _p(kv_cache_positional), _p(v_cache), _p(sparse_indices), _p(output),
                                               C.byref(cfg), _p(device_status), _stream(stream)),
@@ -351,5 +360,6 @@ def wait_selftest(elapsed_ns, stream=None):
     _check(lib().b200_wait_selftest(None, _p(elapsed_ns), _stream(stream)), "wait_selftest")
 
 
-from .ep import ExpertParallelMoe, balanced_placement, dispatch_plan, expert_owner  # noqa: E402,F401
+from .ep import (ExpertParallelMoe, PeerExpertParallelMoe, balanced_placement, dispatch_plan,  # noqa: E402,F401
+                 expert_owner)
 from .hostapi import MoeFp8Layer, DsaDecodeLayer, HostPipeline  # noqa: E402,F401

@@ -28,6 +28,7 @@
 #include "common.cuh"
 
 void b200_count_launch(int n);
+void b200_set_last_error_text(const char* text);
 
 namespace {
 
@@ -441,6 +442,7 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
 // exits, whether or not this entry point is ever called.
 // ---------------------------------------------------------------------------------------------
 #define B200_DSA_STATIC_SCRATCH_BYTES (16u << 20)
+#define B200_DSA_STATIC_MAX_QUERIES 65535          // one grid row per query
 static __device__ __align__(256) unsigned char g_dsa_static_scratch[B200_DSA_STATIC_SCRATCH_BYTES];
 
 namespace {
@@ -465,20 +467,24 @@ int static_scratch_setup(int dev) {
 }
 }  // namespace
 
-void b200_set_last_error_text(const char* text);
-
 extern "C" int b200_dsa_forward_bf16_static(const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
                                             const uint16_t* kp, const uint16_t* v, const int* idx, float* out,
                                             const b200_dsa_config* cfg, int* device_status,
                                             b200_stream_t stream) {
     if (!cfg) return B200_BAD_ARG;
-    if (!q_nope || !q_pe || !kc || !kp || !v || !idx || !out) return B200_BAD_ARG;
+    if (!q_nope || !q_pe || !kc || !kp || !v || !idx || !out || !device_status) return B200_BAD_ARG;
     const int Q = cfg->num_queries, H = cfg->num_heads, S = cfg->num_selected_kv;
     if (Q <= 0 || H <= 0 || S <= 0) return B200_BAD_SHAPE;
     if (cfg->head_dim_compressed != DC || cfg->head_dim_positional != DP) return B200_UNSUPPORTED;
     if (H > HEADS) return B200_UNSUPPORTED;
     if (S % TKV) return B200_BAD_SHAPE;
-    if (Q > 65535) return B200_UNSUPPORTED;
+    if (Q > B200_DSA_STATIC_MAX_QUERIES) {
+        char msg[160];
+        snprintf(msg, sizeof(msg), "b200_dsa_forward_bf16_static: %d queries in one call, the limit is %d; split the batch",
+                 Q, B200_DSA_STATIC_MAX_QUERIES);
+        b200_set_last_error_text(msg);
+        return B200_UNSUPPORTED;
+    }
     const uintptr_t align = reinterpret_cast<uintptr_t>(q_nope) | reinterpret_cast<uintptr_t>(q_pe) |
                             reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(kp) |
                             reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out);
@@ -490,12 +496,18 @@ extern "C" int b200_dsa_forward_bf16_static(const uint16_t* q_nope, const uint16
     if (st) return st;
     unsigned char* scratch = g_static_scratch_addr[dev];
 
-    // same work split as the workspace-backed call
+    // Work split: as many row ranges per query as fill the machine about once, but never more than
+    // the built-in array holds partial results for (one (query, range) slot = 128 x 512 fp32 outputs +
+    // 128 (max, sum) pairs = 257 KiB).  With one range per query no scratch is needed at all, so every
+    // shape the kernel supports is accepted; a large batch simply runs with fewer, longer ranges.
     const int nt_total = S / TKV;
     int NS = 1;
     if (2 * Q < g_static_sm_count[dev]) NS = g_static_sm_count[dev] / (2 * Q);
     if (NS > nt_total) NS = nt_total;
     if (NS > 64) NS = 64;
+    const size_t slot_bytes = (size_t)HEADS * DC * sizeof(float) + (size_t)HEADS * 2 * sizeof(float);
+    const size_t max_slots = (B200_DSA_STATIC_SCRATCH_BYTES - 512) / slot_bytes;      // 63
+    if ((size_t)Q * NS > max_slots) NS = (int)(max_slots / (size_t)Q);
     if (NS < 1) NS = 1;
     const int tps = ceil_div(nt_total, NS);
     NS = ceil_div(nt_total, tps);
@@ -504,16 +516,16 @@ extern "C" int b200_dsa_forward_bf16_static(const uint16_t* q_nope, const uint16
     const size_t ml_bytes = ((size_t)Q * NS * HEADS * 2 * sizeof(float) + 255) & ~size_t(255);
     const size_t o_bytes = (size_t)Q * NS * HEADS * DC * sizeof(float);
     const size_t need = (NS > 1) ? 256 + ml_bytes + o_bytes : 256;
-    if (need > B200_DSA_STATIC_SCRATCH_BYTES) {
+    if (need > B200_DSA_STATIC_SCRATCH_BYTES) {      // cannot happen after the clamp above; kept as a guard
         char msg[200];
         snprintf(msg, sizeof(msg),
                  "b200_dsa_forward_bf16_static: %d queries x %d splits need %zu bytes of scratch, the built-in "
-                 "array holds %u; use b200_dsa_forward_bf16 or fewer queries per call",
+                 "array holds %u",
                  Q, NS, need, (unsigned)B200_DSA_STATIC_SCRATCH_BYTES);
         b200_set_last_error_text(msg);
         return B200_UNSUPPORTED;
     }
-    int* status_word = device_status ? device_status : reinterpret_cast<int*>(scratch);
+    int* status_word = device_status;
     // the status word must start at zero; the partial results are fully rewritten by the decode
     // kernel before the merge kernel reads them, so stale contents of earlier calls do not matter
     B200_CUDA_TRY(cudaMemsetAsync(status_word, 0, sizeof(int), stream));

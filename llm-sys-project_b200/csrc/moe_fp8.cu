@@ -35,6 +35,8 @@
 #include "moe_internal.cuh"
 #include "tma_host.cuh"
 
+void b200_set_last_error_text(const char* text);
+
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 128;
@@ -48,11 +50,17 @@ constexpr int GEMM_THREADS = 32 * (NUM_PROMO_WARPS + 4);   // warpgroups 0-3: pr
 constexpr int W_TMA = NUM_PROMO_WARPS, W_MMA0 = NUM_PROMO_WARPS + 1;
 constexpr int MAX_E = 1024;
 constexpr unsigned ISSUER_SLEEP_NS = 64;
-#ifndef PROMO_REGS_V
-#define PROMO_REGS_V 120
-#define AUX_REGS_V 32
+// Register budgets after setmaxnreg.  The registers a warpgroup gives up are the only ones the others can
+// take (the pool is what the CTA was launched with: 640 threads x LAUNCH_REGS), and setmaxnreg.inc waits
+// without bound until its request is met, so the two sides must balance:
+// 512 * (PROMO_REGS - LAUNCH_REGS) <= 128 * (LAUNCH_REGS - AUX_REGS).  The launcher checks the compiled
+// register count against LAUNCH_REGS before the first launch.
+#ifndef PROMO_X8
+#define PROMO_X8 1      // promotion loads of 8 columns (two in flight); 0: 16 columns (more registers, spills)
 #endif
-constexpr int PROMO_REGS = PROMO_REGS_V, AUX_REGS = AUX_REGS_V;   // 512 * 120 + 128 * 32 = 65536: the whole register file
+constexpr int LAUNCH_REGS = 96, PROMO_REGS = 112, AUX_REGS = 32;
+static_assert(NUM_PROMO_WARPS * (PROMO_REGS - LAUNCH_REGS) <= 4 * (LAUNCH_REGS - AUX_REGS), "setmaxnreg balance");
+static_assert(GEMM_THREADS * LAUNCH_REGS <= 65536, "register file");
 
 struct GemmSmem {
     uint64_t full[STAGES];
@@ -95,6 +103,12 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 __device__ __forceinline__ void promote16(unsigned long long* acc2, const uint32_t (&v)[16], unsigned long long s2) {
 #pragma unroll
     for (int i = 0; i < 8; i++)
+        acc2[i] = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), s2, acc2[i]);
+}
+
+__device__ __forceinline__ void promote8(unsigned long long* acc2, const uint32_t (&v)[8], unsigned long long s2) {
+#pragma unroll
+    for (int i = 0; i < 4; i++)
         acc2[i] = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), s2, acc2[i]);
 }
 
@@ -287,14 +301,14 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             for (int i = 0; i < QCOLS / 2; i++) acc2[i] = 0ull;
 
             // scales of K block kb+1 are fetched while block kb is being promoted
-            float sa_n = row_ok ? a_sc[0] : 0.0f, w0_n = w_sc0[0], w1_n = w_sc1[0];
+            float sa_n = row_ok ? a_sc[0] : 0.0f, w0_n = w_sc0[0], w1_n = (MODE == 1) ? w_sc1[0] : 0.0f;
             for (int kb = 0; kb < nkb; kb++) {
                 const float s0 = sa_n * w0_n;
-                const float s1 = sa_n * w1_n;
+                const float s1 = (MODE == 1) ? sa_n * w1_n : s0;
                 if (kb + 1 < nkb) {
                     sa_n = row_ok ? a_sc[kb + 1] : 0.0f;
                     w0_n = w_sc0[kb + 1];
-                    w1_n = w_sc1[kb + 1];
+                    if (MODE == 1) w1_n = w_sc1[kb + 1];
                 }
                 if (!warp_wait(&sm->tmem_full[acc], acc_ph)) goto done;
                 if (warp_valid) {
@@ -302,6 +316,25 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     ptx::tc_fence_after();
                     const unsigned long long s0p = ptx::pack_f32x2(s0, s0), s1p = ptx::pack_f32x2(s1, s1);
                     const uint32_t t0 = tmem_base + lane_addr + acc * BN + wq * QCOLS;
+#if PROMO_X8
+                    uint32_t ra[8], rb[8];
+                    ptx::tmem_ld_32x8(t0, ra);
+                    ptx::tmem_ld_32x8(t0 + 8, rb);
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        ptx::tc_wait_ld();
+                        if (c == 3) {
+                            ptx::tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
+                        }
+                        const unsigned long long sp = (c < 2) ? s0p : s1p;
+                        promote8(acc2 + 8 * c, ra, sp);
+                        if (c < 3) ptx::tmem_ld_32x8(t0 + 16 * (c + 1), ra);
+                        promote8(acc2 + 8 * c + 4, rb, sp);
+                        if (c < 3) ptx::tmem_ld_32x8(t0 + 16 * (c + 1) + 8, rb);
+                    }
+#else
                     uint32_t ra[16], rb[16];
                     ptx::tmem_ld_32x16(t0, ra);               // MODE 1: gate columns
                     ptx::tmem_ld_32x16(t0 + 16, rb);
@@ -316,6 +349,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
                     promote16(acc2 + 16, ra, s1p);
                     promote16(acc2 + 24, rb, s1p);
+#endif
                 } else {
                     if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
                 }
@@ -561,7 +595,8 @@ int check_fp8_cfg(const b200_moe_fp8_config* cfg) {
 // permute + sort + GEMM1 (+ GEMM2) on given routing
 int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float* xs, const int* ids,
                 const float* wts, const int* hist, const uint8_t* w1q, const float* w1s, const uint8_t* w2q, const float* w2s,
-                float* out, const b200_moe_fp8_config* cfg, bool do_gemm2, bool packed, cudaStream_t stream) {
+                float* out, const b200_moe_fp8_config* cfg, bool do_gemm2, bool packed, cudaStream_t stream,
+                bool zero_out = true) {
     const int T = cfg->num_tokens, E = cfg->num_experts, K = cfg->top_k, D = cfg->hidden_dim,
               I = cfg->intermediate_dim;
     const long long TK = (long long)T * K;
@@ -584,6 +619,26 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
                                            (int)GEMM_SMEM_BYTES));
         B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)GEMM_SMEM_BYTES));
+    }
+    {
+        // setmaxnreg.inc waits without bound for registers that only setmaxnreg.dec of the same CTA frees:
+        // never launch a build whose compiled register count breaks the balance the budgets assume
+        static int regs_ok = -1;
+        if (regs_ok < 0) {
+            cudaFuncAttributes a1{}, a2{}, a3{};
+            B200_CUDA_TRY(cudaFuncGetAttributes(&a1, grouped_gemm_fp8_kernel<1>));
+            B200_CUDA_TRY(cudaFuncGetAttributes(&a2, grouped_gemm_fp8_kernel<2>));
+            B200_CUDA_TRY(cudaFuncGetAttributes(&a3, grouped_gemm_fp8_kernel<3>));
+            auto ok = [](int n) {
+                return n * GEMM_THREADS <= 65536 && n <= PROMO_REGS &&
+                       NUM_PROMO_WARPS * (PROMO_REGS - n) <= 4 * (n - AUX_REGS);
+            };
+            regs_ok = (ok(a1.numRegs) && ok(a2.numRegs) && ok(a3.numRegs)) ? 1 : 0;
+        }
+        if (!regs_ok) {
+            b200_set_last_error_text("grouped GEMM: the compiled register count does not balance the setmaxnreg budgets");
+            return B200_UNSUPPORTED;
+        }
     }
     b200_gemm_profile* prof = (ws->gemm_prof && ws->gemm_prof->on) ? ws->gemm_prof : nullptr;
     const int slot = prof ? (int)(prof->calls % PROF_SLOTS) : 0;
@@ -626,7 +681,7 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
         return B200_OK;
     }
     p.out = out;
-    B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)T * D, stream));
+    if (zero_out) B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)T * D, stream));
     if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][2], stream));
     grouped_gemm_fp8_kernel<2><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
     if (prof) { B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][3], stream)); prof->calls++; }
@@ -679,7 +734,7 @@ int b200_moe_fp8_profile_read(b200_ws* ws, float* gemm1_ms, float* gemm2_ms, int
 static int experts_impl(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
                         const float* expert_w, const uint8_t* w1q, const float* w1s, const uint8_t* w2q,
                         const float* w2s, float* out, const b200_moe_fp8_config* cfg, bool packed,
-                        b200_stream_t stream) {
+                        b200_stream_t stream, bool zero_out = true) {
     int st = check_fp8_cfg(cfg);
     if (st) return st;
     if (!xq || !xs || !expert_ids || !expert_w || !w1q || !w1s || !w2q || !w2s || !out) return B200_BAD_ARG;
@@ -692,8 +747,24 @@ static int experts_impl(b200_ws* ws, const uint8_t* xq, const float* xs, const i
     if (st) return st;
     WsCarver cv(ws->base);
     carve_fp8(cv, cfg, false, s);
-    return run_experts(ws, s, xq, xs, expert_ids, expert_w, nullptr, w1q, w1s, w2q, w2s, out, cfg, true, packed, stream);
+    return run_experts(ws, s, xq, xs, expert_ids, expert_w, nullptr, w1q, w1s, w2q, w2s, out, cfg, true, packed, stream,
+                       zero_out);
 }
+
+}  // extern "C"
+
+// Expert-parallel owner side (moe_ep.cu): `out` already holds zeros in every row that can receive a
+// contribution (the push kernel of the previous step cleared what it read), so the scatter-add GEMM2
+// runs without the zero-fill pass over the whole row capacity.
+int b200_moe_fp8_experts_accumulate(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                                    const float* expert_w, const uint8_t* w1, const float* w1s, const uint8_t* w2,
+                                    const float* w2s, float* out, const b200_moe_fp8_config* cfg, bool packed,
+                                    cudaStream_t stream) {
+    if (cfg && (cfg->flags & B200_MOE_DETERMINISTIC)) return B200_UNSUPPORTED;
+    return experts_impl(ws, xq, xs, expert_ids, expert_w, w1, w1s, w2, w2s, out, cfg, packed, stream, false);
+}
+
+extern "C" {
 
 int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
                          const float* expert_w, const uint8_t* w1q, const float* w1s, const uint8_t* w2q,

@@ -18,3 +18,10 @@ int launch_route_select(const float* partials, int n_chunks, const float* bias, 
 int launch_permute(const int* ids, int T, int K, int E, const int* counts_in, bool trusted, int* counts,
                    int* offsets, int* row_pair, cudaStream_t stream);
 int check_route_cfg(int T, int E, int K, int D, int scoring, int n_group, int topk_group);
+
+// b200_moe_fp8_experts without the zero-fill of `out` (the caller keeps the rows that receive
+// contributions at zero); used by the expert-parallel owner side.
+int b200_moe_fp8_experts_accumulate(b200_ws* ws, const uint8_t* xq, const float* xs, const int* expert_ids,
+                                    const float* expert_w, const uint8_t* w1, const float* w1s, const uint8_t* w2,
+                                    const float* w2s, float* out, const b200_moe_fp8_config* cfg, bool packed,
+                                    cudaStream_t stream);

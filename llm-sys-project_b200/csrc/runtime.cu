@@ -79,6 +79,10 @@ int b200_ws_device_status(b200_ws* ws, b200_stream_t stream, int* status) {
 }  // extern "C"
 
 int b200_ws_ensure(b200_ws* ws, size_t bytes) {
+    // growth (free + allocate) is serialised; the calls that then use the buffer still have to be
+    // ordered by the caller (one in-flight call per workspace)
+    static std::mutex grow_mu;
+    std::lock_guard<std::mutex> lock(grow_mu);
     if (bytes <= ws->capacity) return B200_OK;
     // Grow-only.  Earlier launches may still read the old buffer: drain first.
     B200_CUDA_TRY(cudaDeviceSynchronize());

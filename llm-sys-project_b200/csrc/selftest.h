@@ -20,6 +20,11 @@ B200_API int b200_umma_selftest(int mode, const void* a, const void* b, float* d
  * elapsed_ns [2] (device, may be NULL): nanoseconds each waiter spent before giving up. */
 B200_API int b200_wait_selftest(b200_ws* ws, long long* elapsed_ns, b200_stream_t stream);
 
+/* Maps every peer of an expert-parallel object onto the object's own exchange buffer, so that a single
+ * GPU can run the step of "rank 0 of 2": the words of the absent rank never arrive, the bounded waits run
+ * out, and the step reports B200_TIMEOUT (results are meaningless; every access stays inside the buffers). */
+B200_API int b200_ep_connect_loopback(b200_ep* ep);
+
 #ifdef __cplusplus
 }
 #endif

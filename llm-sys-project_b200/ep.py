@@ -204,3 +204,89 @@ class ExpertParallelMoe:
             out.index_add_(0, send_tok, back.to(torch.float32))
         self._mark("sum", xq)
         return out, ids, wts
+
+
+class PeerExpertParallelMoe:
+    """The expert-parallel layer of the C ABI (``b200_ep_*``): same exchange scheme as ExpertParallelMoe,
+    but the data plane is the library's own kernels over peer memory (rows are stored straight into the
+    owner's receive buffers, partial rows straight back) and a step has no host synchronisation and no
+    collective call.  ``group`` is only used once, to hand every rank the 64-byte handles of the other
+    ranks' exchange buffers.  The layer's weights are this rank's experts in local order.
+
+    placement: "contiguous" or a pair (owner [E], local [E]) as for ExpertParallelMoe."""
+
+    def __init__(self, group, layer, num_experts, max_tokens, placement="contiguous", combine_dtype=torch.bfloat16,
+                 wait_limit_ms=0, loopback=False):
+        import ctypes as C
+        from . import EpConfig, _check, lib
+        self._C, self._check, self._lib = C, _check, lib()
+        self.group = group
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.rank = dist.get_rank(group) if group is not None else 0
+        if loopback:                  # test aid: pretend to be rank 0 of two, with the peer mapped onto this rank
+            self.world, self.rank = 2, 0
+        self.layer = layer
+        self.E, self.K, self.D, self.I = num_experts, layer.K, layer.D, layer.I
+        self.max_tokens = max_tokens
+        flags = 0 if combine_dtype == torch.bfloat16 else 2
+        cfg = EpConfig(self.rank, self.world, max_tokens, num_experts, layer.K, layer.D, layer.I, layer.scoring,
+                       layer.n_group, layer.topk_group, layer.routed_scale, flags, int(wait_limit_ms))
+        om = lm = None
+        if isinstance(placement, (tuple, list)):
+            own = placement[0].to(torch.int32).contiguous().cpu().numpy()
+            loc = placement[1].to(torch.int32).contiguous().cpu().numpy()
+            om, lm = own.ctypes.data_as(C.c_void_p), loc.ctypes.data_as(C.c_void_p)
+            self._keep = (own, loc)
+        elif placement != "contiguous":
+            raise ValueError("placement must be 'contiguous' or (owner, local) tensors")
+        self._h = C.c_void_p()
+        handle = (C.c_char * 64)()
+        _check(self._lib.b200_ep_create(C.byref(self._h), C.byref(cfg), om, lm, handle), "b200_ep_create")
+        if loopback:
+            _check(self._lib.b200_ep_connect_loopback(self._h), "b200_ep_connect_loopback")
+        elif self.world > 1:
+            mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).clone()
+            gathered = [None] * self.world
+            dist.all_gather_object(gathered, mine.tolist(), group=group)
+            allh = bytes(b for h in gathered for b in h)
+            _check(self._lib.b200_ep_connect(self._h, allh), "b200_ep_connect")
+        else:
+            _check(self._lib.b200_ep_connect(self._h, None), "b200_ep_connect")
+
+    def forward(self, xq, xs, out=None, want_routing=True):
+        C = self._C
+        T = xq.shape[0]
+        if out is None:
+            out = torch.empty((T, self.D), dtype=torch.float32, device=xq.device)
+        ids = wts = None
+        if want_routing:
+            ids = torch.empty((T, self.K), dtype=torch.int32, device=xq.device)
+            wts = torch.empty((T, self.K), dtype=torch.float32, device=xq.device)
+        L = self.layer
+        packed = L.w1p is not None
+        w1, w2 = (L.w1p, L.w2p) if packed else (L.w1q, L.w2q)
+        p = lambda t: C.c_void_p(0 if t is None else t.data_ptr())
+        self._check(self._lib.b200_ep_forward(self._h, int(T), p(xq), p(xs), p(L.gate_w), p(L.bias), p(w1), p(L.w1s),
+                                              p(w2), p(L.w2s), 1 if packed else 0, p(out), p(ids), p(wts),
+                                              C.c_void_p(torch.cuda.current_stream().cuda_stream)), "b200_ep_forward")
+        return out, ids, wts
+
+    def stats(self):
+        """(status, send_counts, recv_counts) of the last step; synchronises the current stream."""
+        C = self._C
+        st = C.c_int(0)
+        sc, rc = (C.c_int * self.world)(), (C.c_int * self.world)()
+        self._check(self._lib.b200_ep_stats(self._h, C.c_void_p(torch.cuda.current_stream().cuda_stream), C.byref(st),
+                                            sc, rc), "b200_ep_stats")
+        return st.value, list(sc), list(rc)
+
+    def close(self):
+        if self._h:
+            self._lib.b200_ep_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -108,6 +108,15 @@ def max_threads():
     return int(lib().orc_max_threads())
 
 
+def host_threads():
+    """Host cores this process may run on (its affinity mask).  Unlike max_threads() this does not
+    follow OMP_NUM_THREADS, which process launchers set to 1 for every rank."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def set_threads(n):
     lib().orc_set_threads(int(n))
 

@@ -165,6 +165,39 @@ def test_bf16_tensor_core_decode(b200, cuda, Q, H, S, N):
     assert err < 1e-2, err
 
 
+@pytest.mark.parametrize("Q,S,N,entry", [(2, 256, 1024, "ws"), (2, 192, 1024, "ws"), (3, 96, 512, "ws"),
+                                         (1, 2048, 4096, "ws"), (5, 1024, 2048, "ws"), (1, 1024, 4096, "static"),
+                                         (2, 96, 512, "static")])
+def test_bf16_decode_running_max_rescale(b200, cuda, Q, S, N, entry):
+    """The online softmax rescales the accumulated output only when a tile's maximum exceeds the running
+    maximum by more than 2^8 (about 133 raw score units).  Ordinary data never does that after the first
+    tile, so this case makes the scores grow along each query's row list: the K rows get a gain of 1, 8,
+    64 by thirds of the cache and every index list is ascending.  Covers the 128-row, 64-row and 32-row
+    kernels, split row ranges with their merge (Q = 1, S = 2048) and the built-in-scratch entry point."""
+    rng = np.random.default_rng(S + Q)
+    qn, qp, kc, kp, v, idx = _bf16_case(b200, rng, Q, 128, S, N)
+    gain = np.repeat(np.array([1.0, 8.0, 64.0], np.float32), [N // 3, N // 3, N - 2 * (N // 3)])[:, None]
+    kc = oracle.bf16_bits(oracle.bf16_to_f32(kc) * gain)
+    kp = oracle.bf16_bits(oracle.bf16_to_f32(kp) * gain)
+    idx = np.sort(idx, axis=1).astype(np.int32)
+    ref = oracle.dsa_forward_bf16(qn, qp, kc, kp, v, idx)
+    cfg = b200.DsaConfig(Q, 128, 512, 64, S, 64, N)
+    out = torch.full((Q, 128, 512), float("nan"), dtype=torch.float32, device=cuda)
+    as16 = lambda a: _dev(a.view(np.int16), cuda).view(torch.bfloat16)
+    args = (as16(qn), as16(qp), as16(kc), as16(kp), as16(v), _dev(idx, cuda), out, cfg)
+    if entry == "static":
+        status = torch.zeros(1, dtype=torch.int32, device=cuda)
+        b200.dsa_forward_bf16_static(*args, status)
+    else:
+        b200.dsa_forward_bf16(*args)
+    torch.cuda.synchronize()
+    assert b200.device_status() == 0
+    got = out.cpu().numpy()
+    assert np.isfinite(got).all()
+    err = np.abs(got - ref).max()
+    assert err < 1e-2, err
+
+
 def test_bf16_rejects_unsupported_shapes(b200, cuda):
     t = torch.zeros(64, dtype=torch.bfloat16, device=cuda)
     i = torch.zeros(64, dtype=torch.int32, device=cuda)

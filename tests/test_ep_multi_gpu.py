@@ -32,7 +32,7 @@ def _tokens(rank):
     return oracle.quant_act(rng.normal(0, 1, (T, D)).astype(np.float32))
 
 
-def _worker(rank, world, port, placement_name, ret):
+def _worker(rank, world, port, placement_name, combine_bf16, ret):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle
@@ -58,7 +58,8 @@ def _worker(rank, world, port, placement_name, ret):
         to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
         layer = b200.MoeFp8Layer(to(wg), to(bias), to(w1q[mine]), to(w1s[mine]), to(w2q[mine]), to(w2s[mine]), K,
                                  b200.SCORE_SIGMOID_GROUPED, 4, 2, 2.5)
-        ep = b200.ExpertParallelMoe(dist.group.WORLD, E, K, layer.route, layer.local_experts, placement=placement)
+        ep = b200.ExpertParallelMoe(dist.group.WORLD, E, K, layer.route, layer.local_experts, placement=placement,
+                                    combine_dtype=torch.bfloat16 if combine_bf16 else torch.float32)
         xq, xs = _tokens(rank)
         out, ids, wts = ep.forward(to(xq), to(xs))
         torch.cuda.synchronize()
@@ -73,15 +74,16 @@ def _worker(rank, world, port, placement_name, ret):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("combine_bf16", [False, True])
 @pytest.mark.parametrize("placement", ["contiguous", "strided", "balanced"])
-def test_two_gpu_ep_matches_oracle(placement):
+def test_two_gpu_ep_matches_oracle(placement, combine_bf16):
     if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     world = 2
     mgr = mp.Manager()
     ret = mgr.dict()
-    port = 29700 + os.getpid() % 200 + {"contiguous": 0, "strided": 3, "balanced": 6}[placement]
-    mp.spawn(_worker, args=(world, port, placement, ret), nprocs=world, join=True)
+    port = 29700 + os.getpid() % 200 + {"contiguous": 0, "strided": 3, "balanced": 6}[placement] + int(combine_bf16)
+    mp.spawn(_worker, args=(world, port, placement, combine_bf16, ret), nprocs=world, join=True)
     pairs = 0
     for rank in range(world):
         status, ids_ok, out_ok, recv = ret[rank]

@@ -2,7 +2,7 @@
 top-2048 over a multi-GB paged cache) checked on the GPU through properties that do not depend on the size:
 a token's output does not depend on the rest of its batch, the output scales with the routed scaling
 factor, a query's output does not depend on the order of its selected rows or on the other queries; plus the
-CPU oracle on sampled tokens for the token counts the workload is swept over (1, 16, 128, 1024)."""
+CPU oracle on sampled tokens for the token counts the workload is swept over (1, 16, 128, 1024, 4096)."""
 import os
 import sys
 
@@ -30,7 +30,7 @@ def moe_full(b200, cuda):
     torch.cuda.empty_cache()
 
 
-@pytest.mark.parametrize("T", [1, 16, 128, 1024])
+@pytest.mark.parametrize("T", [1, 16, 128, 1024, 4096])
 def test_moe_full_shape_token_sweep_against_oracle(b200, cuda, moe_full, T):
     """Config-3 shape at the swept token counts: ids bit-exact, outputs within the FP8 tolerance on up
     to 16 sampled tokens (all of them for T <= 16)."""
@@ -43,7 +43,7 @@ def test_moe_full_shape_token_sweep_against_oracle(b200, cuda, moe_full, T):
     try:
         c["T"] = T
         res = bench.moe_cpu_sample(b200, torch, oracle, layer, xq[:T].contiguous(), xs[:T].contiguous(), out,
-                                   min(T, 16), oracle.max_threads())
+                                   min(T, 16), oracle.host_threads())
     finally:
         c["T"] = old_T
     ids_dev, _ = layer.route(xq[:T].contiguous(), xs[:T].contiguous())
