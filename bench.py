@@ -427,14 +427,30 @@ def bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler):
         dist.all_reduce(cal)
         placement = b200.balanced_placement(cal.cpu(), world)
         del xc, cq, cs
-    ep = b200.ExpertParallelMoe(dist.group.WORLD, c["E"], c["K"], layer.route, layer.local_experts,
-                                combine_dtype=torch.bfloat16, placement=placement)
+    peer = args.ep_impl == "peer"
+    if peer:
+        # the C-ABI object: rows travel by peer stores into mapped exchange buffers, no collective in a step
+        pl = placement
+        if placement == "strided":
+            pl = (torch.arange(c["E"], dtype=torch.int32) % world, torch.arange(c["E"], dtype=torch.int32) // world)
+        ep = b200.PeerExpertParallelMoe(dist.group.WORLD, layer, c["E"], c["T"], placement=pl,
+                                        combine_dtype=torch.bfloat16)
+        ws_handle = ep.workspace()
+    else:
+        # the same exchange with torch.distributed (NCCL) all-to-alls around the kernels: the baseline
+        ep = b200.ExpertParallelMoe(dist.group.WORLD, c["E"], c["K"], layer.route, layer.local_experts,
+                                    combine_dtype=torch.bfloat16, placement=placement)
+        ws_handle = None
     for _ in range(max(args.warmup, 3)):
         out, ids, _ = ep.forward(xq, xs)
     torch.cuda.synchronize()
+    if peer:
+        st_w, _, recv_counts = ep.stats()
+        assert st_w == 0, "device-side wait timed out"
+        recv_tokens = int(sum(recv_counts))
+    else:
+        recv_tokens = ep.last_stats["recv_rows"]
     assert b200.device_status() == 0, "device-side wait timed out"
-    recv_rows = ep.recv_pairs()              # (token, expert) pairs computed on this GPU
-    recv_tokens = ep.last_stats["recv_rows"]
     counts = torch.bincount(ids.reshape(-1).long(), minlength=c["E"])
     dist.all_reduce(counts)
     counts = counts.cpu().numpy()
@@ -454,13 +470,16 @@ def bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler):
     t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    ep.profile = True
-    b200.moe_fp8_profile(True)
+    phases = {}
+    b200.moe_fp8_profile(True, ws_handle)
+    if not peer:
+        ep.profile = True
     ep.forward(xq, xs)
-    phases = ep.phase_ms()
-    g1_ms, g2_ms, _ = b200.moe_fp8_profile_read()
-    b200.moe_fp8_profile(False)
-    ep.profile = False
+    if not peer:
+        phases = ep.phase_ms()
+        ep.profile = False
+    g1_ms, g2_ms, _ = b200.moe_fp8_profile_read(ws_handle)
+    b200.moe_fp8_profile(False, ws_handle)
     El = c["E"] // world
     if EP_PLACEMENT == "balanced":
         local_counts = counts[placement[0].numpy() == rank]
@@ -494,15 +513,15 @@ def bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler):
     te = torch.tensor([(time.perf_counter() - t0) / args.steps], device=dev, dtype=torch.float64)
     dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = float(te.item())
-    rr = torch.tensor([recv_rows], device=dev, dtype=torch.float32)
-    rmax = rr.clone(); dist.all_reduce(rmax, op=dist.ReduceOp.MAX)
-    rsum = rr.clone(); dist.all_reduce(rsum)
     if EP_PLACEMENT == "balanced":
         own = placement[0].numpy()
         per_gpu = np.array([counts[own == g].sum() for g in range(world)])
     else:
         per_gpu = counts.reshape(-1, world).sum(0) if EP_PLACEMENT == "strided" else counts.reshape(world, -1).sum(1)
-    flops_hot = 6.0 * float(rmax.item()) * c["D"] * c["I"]
+    rmax_v, rsum_v = float(per_gpu.max()), float(per_gpu.sum())     # (token, expert) pairs computed per GPU
+    flops_hot = 6.0 * rmax_v * c["D"] * c["I"]
+    flops_rank0 = 6.0 * float(per_gpu[0]) * c["D"] * c["I"]
+    fp8_peak = fp8_peak_tflops()
     res = {
         "value": world * c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),
         "e2e": {"value": world * c["T"] / e2e_s, "unit": "tokens/s",
@@ -514,7 +533,9 @@ def bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler):
                      "frac": (g1_bytes / (g1_ms * 1e-3) / 1e9 / hbm) if g1_ms > 0 else None,
                      "traffic": int(g1_bytes * TRAFFIC_RATIO["gemm1"]), "peak_source": which, "kernel_ms": g1_ms,
                      "algorithmic_bytes": int(g1_bytes), "launches_timed": 1},
-        "kernels": {"phase_ms_rank0": phases, "gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "rows_per_gpu_max": float(rmax.item()), "rows_per_gpu_mean": float(rsum.item()) / world,
+        "kernels": {"phase_ms_rank0": phases, "gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "rows_per_gpu_max": rmax_v, "rows_per_gpu_mean": rsum_v / world,
+                    "ep_impl": args.ep_impl,
+                    "rank0_gemm_tflops": flops_rank0 / ((g1_ms + g2_ms) * 1e-3) / 1e12 if g1_ms > 0 else None,
                     "dispatched_tokens_this_gpu": int(recv_tokens),
                     "max_tokens_per_expert": int(counts.max()), "mean_tokens_per_expert": float(counts.mean()),
                     "rows_by_gpu": [int(v) for v in per_gpu],
@@ -724,6 +745,9 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized case of the same kernels (32 experts, 512 tokens; 16 queries, short caches): "
                          "inputs still exceed L2 but only ~2 GB live on the device; not a bench value")
+    ap.add_argument("--ep-impl", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel data plane (N > 1): 'peer' = the library's own kernels over peer memory "
+                         "(b200_ep_*), 'nccl' = torch.distributed all-to-alls around the kernels (the baseline)")
     ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "strided", "contiguous"],
                     help="expert placement of the expert-parallel layer (N > 1)")
     args = ap.parse_args()

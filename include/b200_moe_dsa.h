@@ -170,7 +170,7 @@ B200_API int b200_moe_fp8_experts(b200_ws* ws, const uint8_t* xq, const float* x
  * pieces at well under half the rate of 1 KB+ contiguous pieces, and a row-major weight tile is made of
  * 128-byte pieces 7 KB apart; the packed form stores each (expert, n tile, K block) tile as one
  * contiguous 32 KB block of 256 rows x 128 bytes.  which = 1: w1q [E,2I,D], tile rows for j0 = 128 * n tile:
- * gate j0..+31, up j0..+31, gate j0+32..+63, up j0+32..+63, ... (gate row j = w1 row j, up row j = w1 row
+ * gate j0..+63, up j0..+63, gate j0+64..+127, up j0+64..+127 (gate row j = w1 row j, up row j = w1 row
  * I + j); which = 2: w2q [E,D,I], tile rows = w2 rows 256 * n tile .. +255; packed has the same size.
  * Scales are unchanged.  The *_packed entry points take packed weights and are otherwise identical to
  * b200_moe_fp8_forward / b200_moe_fp8_experts. */
@@ -312,6 +312,9 @@ B200_API int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, con
 /* Synchronises `stream`; status (optional) receives and clears the device status word; send_counts /
  * recv_counts [world] (optional) the rows this rank sent to / received from each rank in the last step. */
 B200_API int b200_ep_stats(b200_ep* ep, b200_stream_t stream, int* status, int* send_counts, int* recv_counts);
+/* The object's own workspace (scratch of its grouped GEMMs, status word): for b200_moe_fp8_profile and
+ * b200_ws_device_status.  Owned by the object. */
+B200_API b200_ws* b200_ep_workspace(b200_ep* ep);
 B200_API int b200_ep_destroy(b200_ep* ep);
 
 /* --------------------------------------------------------------------------- */

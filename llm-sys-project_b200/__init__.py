@@ -64,11 +64,11 @@ EXPORTED_SYMBOLS = [
     "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
     "b200_dsa_softmax_f32", "b200_dsa_output_proj_f32",
     "b200_ep_plan", "b200_ep_sum_rows", "b200_ep_create", "b200_ep_connect", "b200_ep_forward", "b200_ep_stats",
-    "b200_ep_destroy",
+    "b200_ep_workspace", "b200_ep_destroy",
     "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128",
 ]
 # exported for the test suite only (declared in csrc/selftest.h, not in the public header)
-TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest", "b200_ep_connect_loopback"]
+TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest", "b200_ep_connect_loopback", "b200_fp8_mma_rate"]
 
 
 def lib():
@@ -85,6 +85,8 @@ def lib():
         L.b200_launch_count.restype = C.c_longlong
         L.b200_launch_count.argtypes = [C.c_int]
         L.b200_ws_capacity.restype = C.c_size_t
+        L.b200_ep_workspace.restype = C.c_void_p
+        L.b200_ep_workspace.argtypes = [C.c_void_p]
         _lib = L
     return _lib
 
@@ -228,13 +230,14 @@ def ep_sum_rows(back, pos, world, out, stream=None):
                                   _p(out), _stream(stream)), "ep_sum_rows")
 
 
-def moe_fp8_profile(enable):
-    _check(lib().b200_moe_fp8_profile(None, 1 if enable else 0), "moe_fp8_profile")
+def moe_fp8_profile(enable, ws=None):
+    """ws: a workspace handle (e.g. PeerExpertParallelMoe.workspace()); None = the default workspace."""
+    _check(lib().b200_moe_fp8_profile(C.c_void_p(ws), 1 if enable else 0), "moe_fp8_profile")
 
 
-def moe_fp8_profile_read():
+def moe_fp8_profile_read(ws=None):
     a, b, n = C.c_float(0), C.c_float(0), C.c_int(0)
-    _check(lib().b200_moe_fp8_profile_read(None, C.byref(a), C.byref(b), C.byref(n)), "moe_fp8_profile_read")
+    _check(lib().b200_moe_fp8_profile_read(C.c_void_p(ws), C.byref(a), C.byref(b), C.byref(n)), "moe_fp8_profile_read")
     return a.value, b.value, n.value
 
 
@@ -351,6 +354,15 @@ def umma_selftest(mode, a, b, d, N, K, stream=None):
     """Test hook: one tensor-core tile through the production shared-memory layouts."""
     _check(lib().b200_umma_selftest(int(mode), _p(a), _p(b), _p(d), int(N), int(K), _stream(stream)),
            "umma_selftest")
+
+
+def fp8_mma_rate(pair=False, iters=20000, stream=None):
+    """Measurement hook: dense FP8 tensor rate (TFLOP/s, milliseconds) of the MMA shape the grouped GEMMs issue,
+    operands resident in shared memory (pair: cta_group::2, 256 x 256 x 32 per CTA pair)."""
+    tf, ms = C.c_float(0), C.c_float(0)
+    _check(lib().b200_fp8_mma_rate(1 if pair else 0, int(iters), C.byref(tf), C.byref(ms), _stream(stream)),
+           "fp8_mma_rate")
+    return tf.value, ms.value
 
 
 def wait_selftest(elapsed_ns, stream=None):

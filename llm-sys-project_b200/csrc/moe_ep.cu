@@ -629,6 +629,8 @@ int b200_ep_stats(b200_ep* ep, b200_stream_t stream, int* status, int* send_coun
     return B200_OK;
 }
 
+b200_ws* b200_ep_workspace(b200_ep* ep) { return ep ? ep->ws : nullptr; }
+
 int b200_ep_destroy(b200_ep* ep) {
     if (!ep) return B200_OK;
     cudaDeviceSynchronize();

@@ -44,21 +44,32 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;            // 16384
 constexpr int B_BYTES = BN * BK;            // 32768
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int NUM_PROMO_WARPS = 16;          // one barrier arrival per warp, one polling lane per warp
-constexpr int QCOLS = BN / (NUM_PROMO_WARPS / 4);   // 64 accumulator columns per promotion thread
-constexpr int GEMM_THREADS = 32 * (NUM_PROMO_WARPS + 4);   // warpgroups 0-3: promotion/epilogue; 4: TMA + MMA warps
+#ifndef B200_GEMM_PROMO_WARPS
+#define B200_GEMM_PROMO_WARPS 8
+#endif
+constexpr int NUM_PROMO_WARPS = B200_GEMM_PROMO_WARPS;   // 8 or 16; one barrier arrival and one polling lane per warp
+constexpr int NQ = NUM_PROMO_WARPS / 4;      // column groups of the accumulator (TMEM lanes fix the row split at 4)
+constexpr int QCOLS = BN / NQ;               // accumulator columns per promotion thread
+constexpr int GEMM_THREADS = 32 * (NUM_PROMO_WARPS + 4);   // promotion/epilogue warpgroups, then the TMA + MMA warpgroup
 constexpr int W_TMA = NUM_PROMO_WARPS, W_MMA0 = NUM_PROMO_WARPS + 1;
 constexpr int MAX_E = 1024;
 constexpr unsigned ISSUER_SLEEP_NS = 64;
 // Register budgets after setmaxnreg.  The registers a warpgroup gives up are the only ones the others can
-// take (the pool is what the CTA was launched with: 640 threads x LAUNCH_REGS), and setmaxnreg.inc waits
+// take (the pool is what the CTA was launched with: GEMM_THREADS x LAUNCH_REGS), and setmaxnreg.inc waits
 // without bound until its request is met, so the two sides must balance:
-// 512 * (PROMO_REGS - LAUNCH_REGS) <= 128 * (LAUNCH_REGS - AUX_REGS).  The launcher checks the compiled
-// register count against LAUNCH_REGS before the first launch.
-#ifndef PROMO_X8
-#define PROMO_X8 1      // promotion loads of 8 columns (two in flight); 0: 16 columns (more registers, spills)
+// promotion threads x (PROMO_REGS - LAUNCH_REGS) <= 128 x (LAUNCH_REGS - AUX_REGS).  The launcher checks
+// the compiled register count against this before the first launch.
+constexpr int LAUNCH_REGS = (NUM_PROMO_WARPS == 8) ? 168 : 96;
+constexpr int PROMO_REGS = (NUM_PROMO_WARPS == 8) ? 232 : 112;
+constexpr int AUX_REGS = (NUM_PROMO_WARPS == 8) ? 40 : 32;
+// columns per promotion load (two loads in flight)
+#ifndef B200_GEMM_PROMO_CH
+#define B200_GEMM_PROMO_CH ((B200_GEMM_PROMO_WARPS == 8) ? 32 : 8)
 #endif
-constexpr int LAUNCH_REGS = 96, PROMO_REGS = 112, AUX_REGS = 32;
+constexpr int CH = B200_GEMM_PROMO_CH;
+constexpr int SW = (NUM_PROMO_WARPS == 8) ? 16 : 8;     // columns per pass of the output transpose
+static_assert(NUM_PROMO_WARPS == 8 || NUM_PROMO_WARPS == 16, "promotion warps");
+static_assert(QCOLS % (2 * CH) == 0, "promotion chunks");
 static_assert(NUM_PROMO_WARPS * (PROMO_REGS - LAUNCH_REGS) <= 4 * (LAUNCH_REGS - AUX_REGS), "setmaxnreg balance");
 static_assert(GEMM_THREADS * LAUNCH_REGS <= 65536, "register file");
 
@@ -72,8 +83,8 @@ struct GemmSmem {
     int abort_flag;
     int total_tiles;
     int tile_prefix[MAX_E + 1];
-    float amax[2][4][BM];   // [tile parity][column quarter][row]
-    alignas(16) float stage[NUM_PROMO_WARPS][32][12];   // per promotion warp: 32 rows x 8 columns (+4 pad), scatter-add transpose
+    float amax[2][NQ][BM];   // [tile parity][column group][row]
+    alignas(16) float stage[NUM_PROMO_WARPS][32][SW + 4];   // per promotion warp: 32 rows x SW columns (+4 pad), output transpose
 };
 
 constexpr size_t GEMM_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(GemmSmem);
@@ -92,28 +103,51 @@ struct GemmParams {
     int E, D, I;
     int packed;                // weights pre-tiled: one contiguous 256 x 128-byte block per (expert, n tile, K block)
     long long total_rows;      // capacity of the sorted row buffers
+#ifdef B200_GEMM_TRACE
+    long long* trace;          // [8][TRACE_CAP] clock64 stamps of CTA 0's pipeline events (timeline builds only)
+    int trace_warp;
+#endif
 };
+
+#ifdef B200_GEMM_TRACE
+constexpr int TRACE_CAP = 512;
+long long* g_gemm_trace = nullptr;
+int g_gemm_trace_warp = 0;
+#define TRACE_STAMP(slot, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < TRACE_CAP) p.trace[(slot) * TRACE_CAP + (idx)] = clock64(); } while (0)
+#else
+#define TRACE_STAMP(slot, idx) do { } while (0)
+#endif
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                  : "memory");
 }
 
-// acc[0..15] += v[0..15] * s  as eight packed fused multiply-adds
-__device__ __forceinline__ void promote16(unsigned long long* acc2, const uint32_t (&v)[16], unsigned long long s2) {
+// acc[0..N-1] += v[0..N-1] * s  as N/2 packed fused multiply-adds
+template <int N>
+__device__ __forceinline__ void promote(unsigned long long* acc2, const uint32_t (&v)[N], unsigned long long s2) {
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < N / 2; i++) {
+#ifdef B200_GEMM_SCALAR_FMA
+        float a0, a1, s, s_;
+        ptx::unpack_f32x2(acc2[i], a0, a1);
+        ptx::unpack_f32x2(s2, s, s_);
+        acc2[i] = ptx::pack_f32x2(fmaf(__uint_as_float(v[2 * i]), s, a0), fmaf(__uint_as_float(v[2 * i + 1]), s, a1));
+#else
         acc2[i] = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), s2, acc2[i]);
+#endif
+    }
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
+    if constexpr (N == 8) ptx::tmem_ld_32x8(taddr, r);
+    else if constexpr (N == 16) ptx::tmem_ld_32x16(taddr, r);
+    else ptx::tmem_ld_32x32(taddr, r);
 }
 
-__device__ __forceinline__ void promote8(unsigned long long* acc2, const uint32_t (&v)[8], unsigned long long s2) {
-#pragma unroll
-    for (int i = 0; i < 4; i++)
-        acc2[i] = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), s2, acc2[i]);
-}
-
-// MODE 1: the tile's 256 accumulator columns are four quarters [gate j0+32q .. +31 | up j0+32q .. +31]
-// (j0 = 128 n_tile), so that the gate and the up value of an activation column meet in one thread.
+// MODE 1: the tile's 256 accumulator columns are NQ groups [gate j0+g*QCOLS/2 .. | up j0+g*QCOLS/2 ..]
+// (j0 = 128 n_tile, QCOLS/2 columns each), so that the gate and the up value of an activation column
+// meet in one thread.
 // MODE 2/3: plain output columns 256 n_tile .. +255.
 template <int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -196,7 +230,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
       if (warp == W_TMA) {
         // ===================== TMA producer =====================
         if (lane == 0) {
-            int s = 0; uint32_t ph = 0;
+            int s = 0; uint32_t ph = 0; int gk = 0; (void)gk;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 int e, m_tile, n_tile, cnt;
                 locate(tile, e, m_tile, n_tile, cnt);
@@ -204,6 +238,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const long long wrow0 = (long long)e * w_rows;
                 for (int kb = 0; kb < nkb; kb++) {
                     if (!ptx::mbar_wait_relaxed(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done;
+                    TRACE_STAMP(6, gk); gk++;
                     uint8_t* a_dst = tiles + (size_t)s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
                     ptx::mbar_expect_tx(&sm->full[s], STAGE_BYTES);
@@ -212,12 +247,12 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         // the tile's K block is one contiguous 32 KB piece of the packed weights
                         ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], 0, (((e * NT + n_tile) * nkb) + kb) * BN);
                     } else if (MODE == 1) {
-                        // eight boxes of 32 weight rows: quarter q = [gate j0+32q.. | up j0+32q..]
+                        // 2 NQ boxes of QCOLS/2 weight rows: group g = [gate j0 + g QCOLS/2 .. | up j0 + g QCOLS/2 ..]
                         const int j0 = n_tile * 128;
 #pragma unroll
-                        for (int bx = 0; bx < 8; bx++)
-                            ptx::tma_load_2d(b_dst + bx * 4096, &tmap_b, &sm->full[s], kb * BK,
-                                             (int)(wrow0 + ((bx & 1) ? p.I : 0) + j0 + 32 * (bx >> 1)));
+                        for (int bx = 0; bx < 2 * NQ; bx++)
+                            ptx::tma_load_2d(b_dst + bx * (QCOLS / 2) * 128, &tmap_b, &sm->full[s], kb * BK,
+                                             (int)(wrow0 + ((bx & 1) ? p.I : 0) + j0 + (QCOLS / 2) * (bx >> 1)));
                     } else {
                         ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + n_tile * 256));
                     }
@@ -240,7 +275,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 for (int kb = 0; kb < nkb; kb++, g++) {
                     if ((int)(g & 1) == role) {
                         if (!ptx::mbar_wait_relaxed(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
+                        TRACE_STAMP(0, g);
                         if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
+                        TRACE_STAMP(1, g);
                         ptx::tc_fence_after();
                         const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
                         const uint32_t b_addr = a_addr + A_BYTES;
@@ -253,6 +290,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         }
                         ptx::tc_commit(&sm->empty[s]);          // smem stage reusable once the MMAs have read it
                         ptx::tc_commit(&sm->tmem_full[role]);   // partial sums ready for promotion
+                        TRACE_STAMP(2, g);
                         acc_ph ^= 1;
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -272,11 +310,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             __syncwarp();
             return ok != 0;
         };
-        const int wq = warp >> 2;                         // column quarter of the accumulator
+        const int wq = warp >> 2;                         // column group of the accumulator
         const int row = (warp & 3) * 32 + lane;           // TMEM lane = tile row
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
         int acc = 0; uint32_t acc_ph = 0;
         int tile_par = 0; uint32_t amax_ph[2] = {0, 0};
+        int gp = 0; (void)gp;
+#ifdef B200_GEMM_TRACE
+        const bool trw = (threadIdx.x == p.trace_warp * 32);
+#endif
         const int nkb_w = Kdim / 128;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             int e, m_tile, n_tile, cnt;
@@ -293,7 +335,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 w_sc1 = base + (size_t)(p.I / 128 + n_tile) * nkb_w;       // up rows' block
             } else {
                 const float* base = p.w_scale + (size_t)e * (p.D / 128) * nkb_w;
-                w_sc0 = base + (size_t)(n_tile * 2 + (wq >> 1)) * nkb_w;
+                w_sc0 = base + (size_t)(n_tile * 2 + (wq * QCOLS) / 128) * nkb_w;
                 w_sc1 = w_sc0;
             }
             unsigned long long acc2[QCOLS / 2];
@@ -311,64 +353,63 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     if (MODE == 1) w1_n = w_sc1[kb + 1];
                 }
                 if (!warp_wait(&sm->tmem_full[acc], acc_ph)) goto done;
+#ifdef B200_GEMM_TRACE
+                if (trw) TRACE_STAMP(3, gp);
+#endif
                 if (warp_valid) {
                     // warps whose 32 rows are all padding only hand the stage back
                     ptx::tc_fence_after();
                     const unsigned long long s0p = ptx::pack_f32x2(s0, s0), s1p = ptx::pack_f32x2(s1, s1);
                     const uint32_t t0 = tmem_base + lane_addr + acc * BN + wq * QCOLS;
-#if PROMO_X8
-                    uint32_t ra[8], rb[8];
-                    ptx::tmem_ld_32x8(t0, ra);
-                    ptx::tmem_ld_32x8(t0 + 8, rb);
+                    // QCOLS columns in chunks of CH, two loads in flight; columns [0, QCOLS/2) take s0 (MODE 1:
+                    // gate), the rest s1 (MODE 1: up)
+                    constexpr int NPAIR = QCOLS / (2 * CH);
+                    uint32_t ra[CH], rb[CH];
+                    tmem_ld_cols<CH>(t0, ra);
+                    tmem_ld_cols<CH>(t0 + CH, rb);
 #pragma unroll
-                    for (int c = 0; c < 4; c++) {
+                    for (int c = 0; c < NPAIR; c++) {
                         ptx::tc_wait_ld();
-                        if (c == 3) {
+                        if (c == NPAIR - 1) {
                             ptx::tc_fence_before();
                             __syncwarp();
                             if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
-                        }
-                        const unsigned long long sp = (c < 2) ? s0p : s1p;
-                        promote8(acc2 + 8 * c, ra, sp);
-                        if (c < 3) ptx::tmem_ld_32x8(t0 + 16 * (c + 1), ra);
-                        promote8(acc2 + 8 * c + 4, rb, sp);
-                        if (c < 3) ptx::tmem_ld_32x8(t0 + 16 * (c + 1) + 8, rb);
-                    }
-#else
-                    uint32_t ra[16], rb[16];
-                    ptx::tmem_ld_32x16(t0, ra);               // MODE 1: gate columns
-                    ptx::tmem_ld_32x16(t0 + 16, rb);
-                    ptx::tc_wait_ld();
-                    promote16(acc2, ra, s0p);
-                    ptx::tmem_ld_32x16(t0 + 32, ra);          // MODE 1: up columns
-                    promote16(acc2 + 8, rb, s0p);
-                    ptx::tmem_ld_32x16(t0 + 48, rb);
-                    ptx::tc_wait_ld();
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
-                    promote16(acc2 + 16, ra, s1p);
-                    promote16(acc2 + 24, rb, s1p);
+#ifdef B200_GEMM_TRACE
+                            if (trw) TRACE_STAMP(4, gp);
 #endif
+                        }
+                        promote<CH>(acc2 + c * CH, ra, (2 * c * CH < QCOLS / 2) ? s0p : s1p);
+                        if (c < NPAIR - 1) tmem_ld_cols<CH>(t0 + 2 * (c + 1) * CH, ra);
+                        promote<CH>(acc2 + c * CH + CH / 2, rb, ((2 * c + 1) * CH < QCOLS / 2) ? s0p : s1p);
+                        if (c < NPAIR - 1) tmem_ld_cols<CH>(t0 + 2 * (c + 1) * CH + CH, rb);
+                    }
                 } else {
                     if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
                 }
+#ifdef B200_GEMM_TRACE
+                if (trw) TRACE_STAMP(5, gp);
+                gp++;
+#endif
                 if (++acc == 2) { acc = 0; acc_ph ^= 1; }
             }
+#ifdef B200_GEMM_TRACE
+            if (trw) TRACE_STAMP(7, gp / nkb - 1);     // end of the main loop of each tile; epilogue follows
+#endif
 
             if (MODE == 1) {
                 // SwiGLU on 32 activation columns, 1x128 requantisation shared with the three other quarters.
                 // Fast exp / reciprocal: the result is rounded to e4m3 next, an ulp of fp32 does not matter.
-                float av[32];
+                constexpr int AC = QCOLS / 2;          // activation columns of this thread
                 float amax = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 16; i++) {
+                for (int i = 0; i < AC / 2; i++) {
                     float g0, g1, u0, u1;
                     ptx::unpack_f32x2(acc2[i], g0, g1);
-                    ptx::unpack_f32x2(acc2[16 + i], u0, u1);
-                    av[2 * i] = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
-                    av[2 * i + 1] = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
-                    amax = fmaxf(amax, fmaxf(fabsf(av[2 * i]), fabsf(av[2 * i + 1])));
+                    ptx::unpack_f32x2(acc2[AC / 2 + i], u0, u1);
+                    const float a0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+                    const float a1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                    acc2[i] = ptx::pack_f32x2(a0, a1);
+                    amax = fmaxf(amax, fmaxf(fabsf(a0), fabsf(a1)));
                 }
                 if (!warp_valid) amax = 0.0f;
                 sm->amax[tile_par][wq][row] = amax;
@@ -376,75 +417,63 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 if (lane == 0) ptx::mbar_arrive(&sm->amax_bar[tile_par]);
                 if (!warp_wait(&sm->amax_bar[tile_par], amax_ph[tile_par])) goto done;
                 amax_ph[tile_par] ^= 1;
-                amax = fmaxf(fmaxf(sm->amax[tile_par][0][row], sm->amax[tile_par][1][row]),
-                             fmaxf(sm->amax[tile_par][2][row], sm->amax[tile_par][3][row]));
+#pragma unroll
+                for (int g = 0; g < NQ; g++) amax = fmaxf(amax, sm->amax[tile_par][g][row]);
                 if (row_ok) {
                     const float scale = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
                     const float inv = amax > 0.0f ? __fdiv_rn(448.0f, amax) : 1.0f;
-                    uint32_t packed[8];
+                    uint32_t packed[AC / 4];
 #pragma unroll
-                    for (int i = 0; i < 8; i++) {
-                        uint32_t wv = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; b++) {
-                            uint32_t q = (uint32_t)__nv_cvt_float_to_fp8(av[i * 4 + b] * inv, __NV_SATFINITE, __NV_E4M3);
-                            wv |= q << (8 * b);
-                        }
-                        packed[i] = wv;
+                    for (int i = 0; i < AC / 4; i++) {
+                        float a0, a1, a2, a3;
+                        ptx::unpack_f32x2(acc2[2 * i], a0, a1);
+                        ptx::unpack_f32x2(acc2[2 * i + 1], a2, a3);
+                        packed[i] = (uint32_t)__nv_cvt_float_to_fp8(a0 * inv, __NV_SATFINITE, __NV_E4M3) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(a1 * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(a2 * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(a3 * inv, __NV_SATFINITE, __NV_E4M3) << 24);
                     }
-                    uint4* dst = reinterpret_cast<uint4*>(p.act_q + grow * p.I + n_tile * 128 + wq * 32);
-                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    uint4* dst = reinterpret_cast<uint4*>(p.act_q + grow * p.I + n_tile * 128 + wq * AC);
+#pragma unroll
+                    for (int i = 0; i < AC / 16; i++)
+                        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
                     if (wq == 0) p.act_s[grow * (p.I / 128) + n_tile] = scale;
                 }
                 tile_par ^= 1;
             } else if (warp_valid) {
+                // The accumulator row of a lane is transposed through shared memory SW columns at a time so that
+                // one store / red instruction covers 32 / SEGS rows x 16 SEGS contiguous bytes instead of 32 rows
+                // x 16 bytes (fewer, larger memory requests).
                 const float w = row_ok ? p.row_w[grow] : 0.0f;
-                float (*st)[12] = sm->stage[warp];
-                const int sub_row = lane >> 1, seg = lane & 1;
-                if (MODE == 2) {
-                    // out[token] += w * acc.  The accumulator row of a lane is transposed through shared memory
-                    // 8 columns at a time so that one red instruction covers 16 rows x 32 contiguous bytes
-                    // instead of 32 rows x 16 bytes.
-                    const int tok = row_ok ? p.row_tok[grow] : -1;
-                    float* const out_col = p.out + n_tile * 256 + wq * QCOLS;
+                float (*st)[SW + 4] = sm->stage[warp];
+                constexpr int SEGS = SW / 4;
+                const int sub_row = lane / SEGS, seg = lane % SEGS;
+                const int tok = (MODE == 2 && row_ok) ? p.row_tok[grow] : -1;
+                // MODE 2: out[token] += w * acc.  MODE 3: rows[sorted row] = w * acc (plain stores).
+                const long long grow0 = (long long)p.offsets[e] + m_tile * BM + (warp & 3) * 32;
+                const int rows_ok = min(32, cnt - (m_tile * BM + (warp & 3) * 32));
+                float* const out_col = p.out + n_tile * 256 + wq * QCOLS;
 #pragma unroll
-                    for (int pass = 0; pass < QCOLS / 8; pass++) {
-                        float v[8];
+                for (int pass = 0; pass < QCOLS / SW; pass++) {
+                    __syncwarp();
 #pragma unroll
-                        for (int i = 0; i < 4; i++) ptx::unpack_f32x2(acc2[pass * 4 + i], v[2 * i], v[2 * i + 1]);
-                        __syncwarp();
-                        *reinterpret_cast<float4*>(&st[lane][0]) = make_float4(w * v[0], w * v[1], w * v[2], w * v[3]);
-                        *reinterpret_cast<float4*>(&st[lane][4]) = make_float4(w * v[4], w * v[5], w * v[6], w * v[7]);
-                        __syncwarp();
-#pragma unroll
-                        for (int k = 0; k < 2; k++) {
-                            const int r = 16 * k + sub_row;
-                            const int tok_r = __shfl_sync(0xffffffffu, tok, r);
-                            const float4 x4 = *reinterpret_cast<const float4*>(&st[r][seg * 4]);
-                            if (tok_r >= 0) red_add_v4(out_col + (size_t)tok_r * p.D + pass * 8 + seg * 4, x4.x, x4.y, x4.z, x4.w);
-                        }
+                    for (int q = 0; q < SEGS; q++) {
+                        float v0, v1, v2, v3;
+                        ptx::unpack_f32x2(acc2[pass * (SW / 2) + 2 * q], v0, v1);
+                        ptx::unpack_f32x2(acc2[pass * (SW / 2) + 2 * q + 1], v2, v3);
+                        *reinterpret_cast<float4*>(&st[lane][q * 4]) = make_float4(w * v0, w * v1, w * v2, w * v3);
                     }
-                } else {
-                    // rows[r] = w * acc, plain stores (same transposition: 16 rows x 32 bytes per instruction)
-                    const long long grow0 = (long long)p.offsets[e] + m_tile * BM + (warp & 3) * 32;
-                    const int rows_ok = min(32, cnt - (m_tile * BM + (warp & 3) * 32));
-                    float* const out_col = p.out + n_tile * 256 + wq * QCOLS;
+                    __syncwarp();
 #pragma unroll
-                    for (int pass = 0; pass < QCOLS / 8; pass++) {
-                        float v[8];
-#pragma unroll
-                        for (int i = 0; i < 4; i++) ptx::unpack_f32x2(acc2[pass * 4 + i], v[2 * i], v[2 * i + 1]);
-                        __syncwarp();
-                        *reinterpret_cast<float4*>(&st[lane][0]) = make_float4(w * v[0], w * v[1], w * v[2], w * v[3]);
-                        *reinterpret_cast<float4*>(&st[lane][4]) = make_float4(w * v[4], w * v[5], w * v[6], w * v[7]);
-                        __syncwarp();
-#pragma unroll
-                        for (int k = 0; k < 2; k++) {
-                            const int r = 16 * k + sub_row;
-                            const float4 x4 = *reinterpret_cast<const float4*>(&st[r][seg * 4]);
-                            if (r < rows_ok)
-                                *reinterpret_cast<float4*>(out_col + (size_t)(grow0 + r) * p.D + pass * 8 + seg * 4) = x4;
+                    for (int k = 0; k < SEGS; k++) {
+                        const int r = (32 / SEGS) * k + sub_row;
+                        const float4 x4 = *reinterpret_cast<const float4*>(&st[r][seg * 4]);
+                        if (MODE == 2) {
+                            const int tok_r = __shfl_sync(0xffffffffu, tok, r);
+                            if (tok_r >= 0)
+                                red_add_v4(out_col + (size_t)tok_r * p.D + pass * SW + seg * 4, x4.x, x4.y, x4.z, x4.w);
+                        } else if (r < rows_ok) {
+                            *reinterpret_cast<float4*>(out_col + (size_t)(grow0 + r) * p.D + pass * SW + seg * 4) = x4;
                         }
                     }
                 }
@@ -542,9 +571,9 @@ __global__ void pack_weights_kernel(int which, const uint8_t* __restrict__ src, 
     const int e = (int)(t / NT);
     long long row;
     if (which == 1) {
-        // quarter q of the tile's 256 rows = [gate j0+32q .. +31 | up j0+32q .. +31]
-        const int j0 = nt * 128, q = r >> 6, up = (r >> 5) & 1, rr = r & 31;
-        row = (long long)e * 2 * I + (up ? I : 0) + j0 + 32 * q + rr;
+        // group g of the tile's 256 rows = [gate j0 + g QCOLS/2 .. | up j0 + g QCOLS/2 ..], QCOLS/2 rows each
+        const int j0 = nt * 128, g = r / QCOLS, up = (r / (QCOLS / 2)) & 1, rr = r % (QCOLS / 2);
+        row = (long long)e * 2 * I + (up ? I : 0) + j0 + (QCOLS / 2) * g + rr;
     } else {
         row = (long long)e * D + nt * 256 + r;
     }
@@ -645,13 +674,16 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     CUtensorMap ta, tb;
     GemmParams p{};
     p.offsets = s.offsets; p.E = E; p.D = D; p.I = I; p.status = ws->d_status; p.total_rows = TK;
+#ifdef B200_GEMM_TRACE
+    p.trace = g_gemm_trace; p.trace_warp = g_gemm_trace_warp;
+#endif
 
     // GEMM1
     st = b200_make_tmap_u8_sw128(&ta, s.sq, (unsigned long long)TK, D, 128);
     if (st) return st;
     p.packed = packed ? 1 : 0;
     if (packed) st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I * (D / 128), 128, 256);
-    else        st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, 32);
+    else        st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, QCOLS / 2);
     if (st) return st;
     p.a_scale = s.ss; p.w_scale = w1s; p.act_q = s.act_q; p.act_s = s.act_s;
     if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][0], stream));
@@ -668,6 +700,9 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     else        st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D, I, 256);
     if (st) return st;
     p.a_scale = s.act_s; p.w_scale = w2s; p.row_tok = s.row_tok; p.row_w = s.row_w;
+#ifdef B200_GEMM_TRACE
+    if (p.trace) p.trace += 8 * TRACE_CAP;      // second half of the buffer for GEMM2
+#endif
     if (det) {
         p.out = s.rows;
         if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][2], stream));
@@ -693,6 +728,15 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
 }  // namespace
 
 extern "C" {
+
+#ifdef B200_GEMM_TRACE
+// Timeline builds only (-DB200_GEMM_TRACE; never part of the default library): CTA 0 of the next grouped
+// GEMM launches fills dev_buf [2][8][512] with clock64 stamps of its pipeline events.
+__attribute__((visibility("default"))) void b200_debug_gemm_trace(long long* dev_buf, int warp) {
+    g_gemm_trace = dev_buf;
+    g_gemm_trace_warp = warp;
+}
+#endif
 
 int b200_moe_fp8_profile(b200_ws* ws, int enable) {
     if (!ws) ws = b200_default_ws();
@@ -818,8 +862,8 @@ int b200_moe_fp8_forward_packed(b200_ws* ws, const uint8_t* xq, const float* xs,
     return forward_impl(ws, xq, xs, gate_w, bias, w1p, w1s, w2p, w2s, out, cfg, true, stream);
 }
 
-// Weight pre-tiling.  which = 1: w1 [E,2I,D] -> tiles of 256 accumulator rows (for q = 0..3: gate
-// j0+32q..+31, then up j0+32q..+31, with j0 = 128 * n_tile); which = 2: w2 [E,D,I] -> tiles of 256 rows.
+// Weight pre-tiling.  which = 1: w1 [E,2I,D] -> tiles of 256 accumulator rows (gate j0..+63, up j0..+63,
+// gate j0+64..+127, up j0+64..+127 for j0 = 128 * n_tile); which = 2: w2 [E,D,I] -> tiles of 256 rows.
 // packed[(((e * NT + n_tile) * nkb + kb) * 256 + r) * 128 + b] = src[e][row(n_tile, r)][kb * 128 + b].
 int b200_moe_fp8_pack_weights(int which, const uint8_t* src, uint8_t* packed, int E, int D, int I,
                               b200_stream_t stream) {

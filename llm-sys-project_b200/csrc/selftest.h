@@ -20,6 +20,12 @@ B200_API int b200_umma_selftest(int mode, const void* a, const void* b, float* d
  * elapsed_ns [2] (device, may be NULL): nanoseconds each waiter spent before giving up. */
 B200_API int b200_wait_selftest(b200_ws* ws, long long* elapsed_ns, b200_stream_t stream);
 
+/* Measurement hook: dense FP8 (e4m3, fp32 accumulate) tensor rate of this GPU with the MMA shape the
+ * grouped GEMMs issue, operands resident in shared memory, one issuing thread per CTA, all SMs busy.
+ * pair = 0: cta_group::1, 128 x 256 x 32; pair = 1: cta_group::2, 256 x 256 x 32 per CTA pair.
+ * Synchronises the stream (timed with CUDA events inside the call); iters K blocks of four MMAs per CTA. */
+B200_API int b200_fp8_mma_rate(int pair, int iters, float* tflops, float* ms, b200_stream_t stream);
+
 /* Maps every peer of an expert-parallel object onto the object's own exchange buffer, so that a single
  * GPU can run the step of "rank 0 of 2": the words of the absent rank never arrive, the bounded waits run
  * out, and the step reports B200_TIMEOUT (results are meaningless; every access stays inside the buffers). */

@@ -142,3 +142,132 @@ extern "C" int b200_umma_selftest(int mode, const void* a, const void* b, float*
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
+
+// -------------------------------------------------------------------------------------------------
+// Tensor-pipe rate of the FP8 MMA the grouped GEMMs use (kind::f8f6f4, e4m3, fp32 accumulate), measured
+// with nothing else going on: every CTA (one per SM) keeps one operand stage in shared memory and one
+// thread issues `iters` K blocks of four K = 32 MMAs, alternating between two TMEM accumulator stages.
+//   pair = 0   cta_group::1, M = 128, N = 256 (A 16 KB + B 32 KB per K block read from shared memory)
+//   pair = 1   cta_group::2, M = 256, N = 256: each CTA of a pair supplies its 128 rows of A and half
+//              of B (16 KB + 16 KB per K block per SM)
+// The operands are whatever the shared memory holds (the rate does not depend on the values).
+// -------------------------------------------------------------------------------------------------
+namespace {
+
+__device__ __forceinline__ void mma2_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+template <int PAIR>
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int iters, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    SelfSmem* sm = reinterpret_cast<SelfSmem*>(base + 49152);
+    const int tid = threadIdx.x, warp = tid >> 5;
+    uint32_t rank = 0;
+    if (PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    for (int i = tid; i < 49152 / 16; i += 128) reinterpret_cast<uint4*>(base)[i] = make_uint4(0x38383838u, 0x38383838u, 0x38383838u, 0x38383838u);
+    if (tid == 0) {
+        ptx::mbar_init(&sm->done, 1);
+        sm->abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 0) {
+        if (PAIR) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(&sm->tmem_base)), "r"(512) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            ptx::tmem_alloc(&sm->tmem_base, 512);
+            ptx::tmem_relinquish();
+        }
+    }
+    ptx::fence_proxy_async_smem();
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (PAIR) asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    ptx::tc_fence_after();
+    const uint32_t tmem = sm->tmem_base;
+    if (tid == 0 && rank == 0) {
+        const uint32_t a_addr = ptx::smem_u32(base), b_addr = a_addr + 16384;
+        constexpr uint32_t idesc = ptx::make_idesc(0, 0, 0, 0, PAIR ? 256 : 128, 256);
+        for (int it = 0; it < iters; it++) {
+            const uint32_t d = tmem + (it & 1) * 256;
+#pragma unroll
+            for (int k4 = 0; k4 < 4; k4++) {
+                const uint64_t ad = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
+                const uint64_t bd = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
+                if (PAIR) mma2_f8(d, ad, bd, idesc, k4 > 0);
+                else      ptx::mma_f8(d, ad, bd, idesc, k4 > 0);
+            }
+        }
+        if (PAIR) {
+            // one arrival in each CTA of the pair once every MMA has retired
+            asm volatile(
+                "{\n\t.reg .b32 r0, r1;\n\t"
+                "mapa.shared::cluster.u32 r0, %0, 0;\n\t"
+                "mapa.shared::cluster.u32 r1, %0, 1;\n\t"
+                "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [r0];\n\t"
+                "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [r1];\n\t}"
+                ::"r"(ptx::smem_u32(&sm->done)) : "memory");
+        } else {
+            ptx::tc_commit(&sm->done);
+        }
+    }
+    ptx::mbar_wait(&sm->done, 0, &sm->abort_flag);
+    ptx::tc_fence_after();
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (PAIR) asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp == 0) {
+        if (PAIR) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+        else      ptx::tmem_dealloc(tmem, 512);
+    }
+    if (tid == 0 && sm->abort_flag) atomicExch(status, B200_TIMEOUT);
+}
+
+}  // namespace
+
+extern "C" int b200_fp8_mma_rate(int pair, int iters, float* tflops, float* ms_out, b200_stream_t stream) {
+    if (!tflops || iters <= 0 || iters > (1 << 22)) return B200_BAD_ARG;
+    b200_ws* ws = b200_default_ws();
+    if (!ws) return B200_CUDA_ERROR;
+    const size_t smem = 1024 + 49152 + sizeof(SelfSmem) + 64;
+    cudaEvent_t e0, e1;
+    B200_CUDA_TRY(cudaEventCreate(&e0));
+    B200_CUDA_TRY(cudaEventCreate(&e1));
+    const int grid = pair ? (ws->sm_count / 2) * 2 : ws->sm_count;
+    float ms = 0.f;
+    for (int rep = 0; rep < 2; rep++) {        // the first launch warms up
+        B200_CUDA_TRY(cudaEventRecord(e0, stream));
+        if (pair) {
+            B200_CUDA_TRY(cudaFuncSetAttribute(mma_rate_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(grid); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr; cfg.numAttrs = 1;
+            B200_CUDA_TRY(cudaLaunchKernelEx(&cfg, mma_rate_kernel<1>, iters, ws->d_status));
+        } else {
+            B200_CUDA_TRY(cudaFuncSetAttribute(mma_rate_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            mma_rate_kernel<0><<<grid, 128, smem, stream>>>(iters, ws->d_status);
+        }
+        b200_count_launch(1);
+        B200_CUDA_TRY(cudaGetLastError());
+        B200_CUDA_TRY(cudaEventRecord(e1, stream));
+        B200_CUDA_TRY(cudaEventSynchronize(e1));
+        B200_CUDA_TRY(cudaEventElapsedTime(&ms, e0, e1));
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    // per CTA and K block: 4 MMAs of 128 (rows of this CTA) x 256 x 32
+    const double flops = (double)grid * iters * 4.0 * 2.0 * 128 * 256 * 32;
+    *tflops = (float)(flops / (ms * 1e-3) / 1e12);
+    if (ms_out) *ms_out = ms;
+    return B200_OK;
+}

@@ -280,6 +280,10 @@ class PeerExpertParallelMoe:
                                             sc, rc), "b200_ep_stats")
         return st.value, list(sc), list(rc)
 
+    def workspace(self):
+        """Handle of the object's workspace (for moe_fp8_profile / moe_fp8_profile_read)."""
+        return self._lib.b200_ep_workspace(self._h)
+
     def close(self):
         if self._h:
             self._lib.b200_ep_destroy(self._h)

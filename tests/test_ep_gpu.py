@@ -107,3 +107,78 @@ def test_ep_sum_rows_kernel(b200, cuda, dtype):
             if pos[r, t] >= 0:
                 want[t] += b32[pos[r, t]]
     assert np.array_equal(out.cpu().numpy(), want)
+
+
+def _small_layer(b200, cuda, rng, T, E, K, D, I, ng, tg):
+    x = rng.normal(0, 1, (T, D)).astype(np.float32)
+    wg = rng.normal(0, D ** -0.5, (E, D)).astype(np.float32)
+    bias = rng.normal(0, 0.01, E).astype(np.float32)
+    xq, xs = oracle.quant_act(x)
+    w1q, w1s = oracle.quant_weight(rng.normal(0, 0.05, (E, 2 * I, D)).astype(np.float32))
+    w2q, w2s = oracle.quant_weight(rng.normal(0, 0.05, (E, D, I)).astype(np.float32))
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
+    layer = b200.MoeFp8Layer(to(wg), to(bias), to(w1q), to(w1s), to(w2q), to(w2s), K, b200.SCORE_SIGMOID_GROUPED, ng, tg,
+                             2.5)
+    return layer, (xq, xs, wg, bias, w1q, w1s, w2q, w2s), to
+
+
+@pytest.mark.parametrize("combine_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("packed", [False, True])
+def test_peer_ep_world1_matches_plain_layer_and_oracle(b200, cuda, combine_dtype, packed):
+    """The C-ABI expert-parallel object with one rank: dispatch into its own receive region, grouped GEMMs
+    on the region, push and combine; several steps in a row with different token counts (the flag words
+    carry the step number, buffers are reused)."""
+    rng = np.random.default_rng(17)
+    T, E, K, D, I = 96, 16, 4, 512, 256
+    layer, (xq, xs, wg, bias, w1q, w1s, w2q, w2s), to = _small_layer(b200, cuda, rng, T, E, K, D, I, 4, 2)
+    if packed:
+        layer.pack()
+    ep = b200.PeerExpertParallelMoe(None, layer, E, max_tokens=T, combine_dtype=combine_dtype)
+    try:
+        for Ts in (T, 40, T):
+            dxq, dxs = to(xq[:Ts]), to(xs[:Ts])
+            plain = layer.forward(dxq, dxs).cpu().numpy()
+            out, ids, wts = ep.forward(dxq, dxs)
+            status, sent, recv = ep.stats()
+            assert status == 0 and sent == [Ts] and recv == [Ts]
+            oi, ow = oracle.route_grouped(xq[:Ts], xs[:Ts], wg, bias, K, 4, 2, 2.5)
+            assert np.array_equal(ids.cpu().numpy(), oi)
+            assert np.abs(wts.cpu().numpy() - ow).max() <= 5e-7
+            got = out.cpu().numpy()
+            tol = 1e-4 if combine_dtype == torch.float32 else 2.0 ** -8
+            assert np.allclose(got, plain, rtol=tol, atol=1e-5)
+            ref = oracle.moe_fp8_experts(xq[:Ts], xs[:Ts], w1q, w1s, w2q, w2s, oi, ow, np.arange(Ts, dtype=np.int32))
+            assert not (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)).any()
+    finally:
+        ep.close()
+    assert b200.device_status() == 0
+
+
+def test_peer_ep_absent_rank_times_out_without_hanging(b200, cuda):
+    """Rank 0 of a two-rank layer whose peer never shows up (its exchange buffer is mapped onto this
+    rank's own, so every access stays in bounds): the words of rank 1 never arrive, the bounded waits of
+    the owner side and of the combine run out after wait_limit_ms, the step returns and reports
+    B200_TIMEOUT; the next ordinary call works."""
+    import time
+    rng = np.random.default_rng(23)
+    T, E, K, D, I = 64, 16, 4, 512, 256
+    layer, (xq, xs, *_), to = _small_layer(b200, cuda, rng, T, E, K, D, I, 4, 2)
+    half = b200.MoeFp8Layer(layer.gate_w, layer.bias, layer.w1q[: E // 2].contiguous(), layer.w1s[: E // 2].contiguous(),
+                            layer.w2q[: E // 2].contiguous(), layer.w2s[: E // 2].contiguous(), K,
+                            b200.SCORE_SIGMOID_GROUPED, 4, 2, 2.5)
+    ep = b200.PeerExpertParallelMoe(None, half, E, max_tokens=T, wait_limit_ms=20, loopback=True)
+    try:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ep.forward(to(xq), to(xs))
+        status, sent, recv = ep.stats()
+        wall = time.perf_counter() - t0
+        assert status == b200.B200_TIMEOUT
+        assert recv[1] == 0 and sum(sent) >= T            # nothing came from the absent rank
+        assert wall < 5.0, wall
+        assert ep.stats()[0] == 0                          # the read cleared the word
+    finally:
+        ep.close()
+    out = layer.forward(to(xq), to(xs))                    # the context is intact
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all() and b200.device_status() == 0

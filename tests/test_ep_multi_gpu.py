@@ -32,7 +32,7 @@ def _tokens(rank):
     return oracle.quant_act(rng.normal(0, 1, (T, D)).astype(np.float32))
 
 
-def _worker(rank, world, port, placement_name, combine_bf16, ret):
+def _worker(rank, world, port, placement_name, combine_bf16, ret, impl="nccl"):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle
@@ -58,17 +58,43 @@ def _worker(rank, world, port, placement_name, combine_bf16, ret):
         to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
         layer = b200.MoeFp8Layer(to(wg), to(bias), to(w1q[mine]), to(w1s[mine]), to(w2q[mine]), to(w2s[mine]), K,
                                  b200.SCORE_SIGMOID_GROUPED, 4, 2, 2.5)
-        ep = b200.ExpertParallelMoe(dist.group.WORLD, E, K, layer.route, layer.local_experts, placement=placement,
-                                    combine_dtype=torch.bfloat16 if combine_bf16 else torch.float32)
+        cdt = torch.bfloat16 if combine_bf16 else torch.float32
         xq, xs = _tokens(rank)
-        out, ids, wts = ep.forward(to(xq), to(xs))
-        torch.cuda.synchronize()
-        status = b200.device_status()
+        if impl == "peer":
+            # the C-ABI object: peer-store data plane, no collective inside a step; three steps in a row
+            if placement == "strided":
+                placement = (torch.arange(E, dtype=torch.int32) % world, torch.arange(E, dtype=torch.int32) // world)
+            ep = b200.PeerExpertParallelMoe(dist.group.WORLD, layer, E, max_tokens=T, placement=placement,
+                                            combine_dtype=cdt, wait_limit_ms=5000)
+            for _ in range(3):
+                out, ids, wts = ep.forward(to(xq), to(xs))
+            status, sent, recv = ep.stats()
+            status |= b200.device_status()
+        else:
+            ep = b200.ExpertParallelMoe(dist.group.WORLD, E, K, layer.route, layer.local_experts, placement=placement,
+                                        combine_dtype=cdt)
+            out, ids, wts = ep.forward(to(xq), to(xs))
+            torch.cuda.synchronize()
+            status = b200.device_status()
         oi, ow = oracle.route_grouped(xq, xs, wg, bias, K, 4, 2, 2.5)
         ref = oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, oi, ow, np.arange(T, dtype=np.int32))
         got = out.cpu().numpy()
-        ret[rank] = (status, bool(np.array_equal(ids.cpu().numpy(), oi)),
-                     bool(not (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)).any()), ep.recv_pairs())
+        if impl == "peer":
+            # pairs computed on this rank = (token, expert) pairs of ALL ranks whose expert lives here
+            mine_set = set(int(e) for e in mine)
+            pairs = 0
+            for r in range(world):
+                tq, ts = _tokens(r)
+                ri, _ = oracle.route_grouped(tq, ts, wg, bias, K, 4, 2, 2.5)
+                pairs += int(np.isin(ri, list(mine_set)).sum())
+            recv_rows_ok = sum(recv) > 0
+            ret[rank] = (status, bool(np.array_equal(ids.cpu().numpy(), oi)),
+                         bool(recv_rows_ok and not (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)).any()), pairs)
+            dist.barrier()
+            ep.close()
+        else:
+            ret[rank] = (status, bool(np.array_equal(ids.cpu().numpy(), oi)),
+                         bool(not (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)).any()), ep.recv_pairs())
         dist.barrier()
     finally:
         dist.destroy_process_group()
@@ -84,6 +110,27 @@ def test_two_gpu_ep_matches_oracle(placement, combine_bf16):
     ret = mgr.dict()
     port = 29700 + os.getpid() % 200 + {"contiguous": 0, "strided": 3, "balanced": 6}[placement] + int(combine_bf16)
     mp.spawn(_worker, args=(world, port, placement, combine_bf16, ret), nprocs=world, join=True)
+    pairs = 0
+    for rank in range(world):
+        status, ids_ok, out_ok, recv = ret[rank]
+        assert status == 0
+        assert ids_ok and out_ok
+        pairs += recv
+    assert pairs == world * T * K
+
+
+@pytest.mark.parametrize("combine_bf16", [False, True])
+@pytest.mark.parametrize("placement", ["contiguous", "strided", "balanced"])
+def test_two_gpu_peer_ep_matches_oracle(placement, combine_bf16):
+    """Same check for the C-ABI expert-parallel object (rows and partial rows travel by peer stores into
+    mapped exchange buffers; flag words instead of collectives)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    port = 29950 + os.getpid() % 40 + {"contiguous": 0, "strided": 3, "balanced": 6}[placement] + int(combine_bf16)
+    mp.spawn(_worker, args=(world, port, placement, combine_bf16, ret, "peer"), nprocs=world, join=True)
     pairs = 0
     for rank in range(world):
         status, ids_ok, out_ok, recv = ret[rank]

@@ -178,9 +178,8 @@ def test_packed_weights_layout_and_equivalence(b200, cuda):
     p1 = w1p.cpu().numpy().reshape(E, I // 128, D // 128, 256, 128)
     e, nt, kb = 2, 1, 3
     j0 = nt * 128
-    # four quarters, each = 32 gate rows followed by the 32 up rows of the same activation columns
-    rows = np.concatenate([np.concatenate([np.arange(j0 + 32 * q, j0 + 32 * q + 32),
-                                           I + np.arange(j0 + 32 * q, j0 + 32 * q + 32)]) for q in range(4)])
+    rows = np.concatenate([np.arange(j0, j0 + 64), I + np.arange(j0, j0 + 64), np.arange(j0 + 64, j0 + 128),
+                           I + np.arange(j0 + 64, j0 + 128)])
     assert np.array_equal(p1[e, nt, kb], w1q[e][rows][:, kb * 128:(kb + 1) * 128])
     p2 = w2p.cpu().numpy().reshape(E, D // 256, I // 128, 256, 128)
     assert np.array_equal(p2[3, 1, 1], w2q[3][256:512, 128:256])
