@@ -89,7 +89,12 @@ enum b200_moe_flags {
      * GEMM2 writes one weighted row per (token, expert) and a second kernel reduces them, so the output is
      * bit-reproducible from run to run.  Costs T*K*D*4 bytes of workspace and one more pass over them.
      * Without the flag GEMM2 scatter-adds into the output (order varies, results agree to fp32 rounding). */
-    B200_MOE_DETERMINISTIC = 1
+    B200_MOE_DETERMINISTIC = 1,
+    /* Tile shape of the grouped GEMMs.  By default a call with at least 96 (token, expert) rows per expert on
+     * average runs 256-row tiles on CTA pairs (tcgen05 cta_group::2; half of a weight tile per SM) and a
+     * smaller one 128-row tiles on single CTAs; these flags force one or the other (results are the same). */
+    B200_MOE_SINGLE_CTA_TILES = 4,
+    B200_MOE_CTA_PAIR_TILES = 8
 };
 
 /* --------------------------------------------------------------------------- */
@@ -281,7 +286,9 @@ B200_API int b200_ep_sum_rows(const void* back, int back_is_bf16, const int* pos
 typedef struct b200_ep b200_ep;
 #define B200_EP_HANDLE_BYTES 64
 enum b200_ep_flags {
-    B200_EP_COMBINE_F32 = 2 /* partial rows travel back as fp32 instead of bf16 (twice the combine bytes) */
+    /* partial rows travel back as fp32 (twice the combine bytes).  Default: fp16 values relative to the row's
+     * largest magnitude plus that magnitude, i.e. 11 significant bits against the row maximum */
+    B200_EP_COMBINE_F32 = 2
 };
 typedef struct b200_ep_config {
     int rank, world;      /* this rank, number of ranks (<= 64); rank g holds num_experts / world experts */

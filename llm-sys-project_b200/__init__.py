@@ -42,6 +42,7 @@ class MoeFp8Config(C.Structure):
 
 
 MOE_DETERMINISTIC = 1      # MoeFp8Config.flags: fixed-order (experts ascending) combine, bit-reproducible
+MOE_SINGLE_CTA_TILES, MOE_CTA_PAIR_TILES = 4, 8      # force the grouped GEMMs' tile shape (default: by size)
 
 
 class EpConfig(C.Structure):

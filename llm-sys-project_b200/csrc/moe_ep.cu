@@ -8,6 +8,7 @@
 //   ep_sum_rows_kernel  out[t] = sum over ranks (in rank order) of the partial row that came back for
 //                       (t, rank); no atomics, no zero-fill pass.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 
@@ -173,8 +174,9 @@ int b200_ep_sum_rows(const void* back, int back_is_bf16, const int* pos, int wor
 //     grouped GEMMs                  b200_moe_fp8_experts on the regions (local memory only: the tensor
 //                                    maps never cover a peer's memory), per-token partial sums by the
 //                                    GEMM2 scatter-add
-//     ep_push_kernel                 partial rows -> bf16 -> the source rank's `back` region (peer stores),
-//                                    clears what it read; the last block publishes the back words
+//     ep_push_kernel                 partial rows -> fp16 relative to the row maximum (or fp32) -> the source
+//                                    rank's `back` region (peer stores), clears what it read; the last block
+//                                    publishes the back words
 //     ep_combine_kernel              source side: bounded wait for every owner's word, then the per-token
 //                                    sum in rank order
 // A region is reused by the next step only after its reader has finished: a rank dispatches step n+1
@@ -217,7 +219,7 @@ struct b200_ep {
 namespace {
 
 struct XLayout {
-    size_t disp_word, back_word, recv_q, recv_s, recv_id, recv_w, back, total;
+    size_t disp_word, back_word, recv_q, recv_s, recv_id, recv_w, back, back_scale, total;
 };
 __host__ __device__ inline XLayout x_layout(int W, int Tm, int K, int D, int back_elem_bytes) {
     XLayout L;
@@ -230,6 +232,7 @@ __host__ __device__ inline XLayout x_layout(int W, int Tm, int K, int D, int bac
     L.recv_id = take((size_t)W * Tm * K * 4);
     L.recv_w = take((size_t)W * Tm * K * 4);
     L.back = take((size_t)W * Tm * D * back_elem_bytes);
+    L.back_scale = take((size_t)W * Tm * 4);
     L.total = off;
     return L;
 }
@@ -338,12 +341,15 @@ ep_recv_ready_kernel(const EpDev e, int* __restrict__ recv_counts) {
     for (int i = cnt * e.K + threadIdx.x; i < e.Tm * e.K; i += blockDim.x) ids[i] = -1;
 }
 
-// Owner side: partial output rows (fp32 sums over this rank's experts) -> bf16 (or fp32) rows in the
-// source rank's `back` region; the fp32 rows are cleared for the next step's scatter-add.
-template <bool BF16>
+// Owner side: partial output rows (fp32 sums over this rank's experts) -> the source rank's `back` region;
+// the fp32 rows are cleared for the next step's scatter-add.  HALF: a row travels as fp16 values divided by
+// the row's largest magnitude, plus that magnitude (one fp32 per row): 11 significant bits relative to the
+// row maximum.  (bf16 rows, 8 bits, broke the 1e-2 absolute bound where a token's partial rows cancel.)
+template <bool HALF>
 __global__ void __launch_bounds__(256)
 ep_push_kernel(const EpDev e, float* __restrict__ y, const int* __restrict__ recv_counts, unsigned int* done) {
     __shared__ int s_start[65];
+    __shared__ float s_red[8];
     __shared__ bool s_last;
     if (threadIdx.x == 0) {
         int acc = 0;
@@ -352,6 +358,7 @@ ep_push_kernel(const EpDev e, float* __restrict__ y, const int* __restrict__ rec
     }
     __syncthreads();
     const int total = s_start[e.W];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     for (int i = blockIdx.x; i < total; i += gridDim.x) {
         int s = 0;
         while (i >= s_start[s + 1]) s++;
@@ -359,21 +366,36 @@ ep_push_kernel(const EpDev e, float* __restrict__ y, const int* __restrict__ rec
         float4* src = reinterpret_cast<float4*>(y + ((size_t)s * e.Tm + row) * e.D);
         char* dst = e.peer[s] + e.L.back;
         const size_t slot = (size_t)e.rank * e.Tm + row;
-        for (int c = threadIdx.x; c < e.D / 8; c += blockDim.x) {
-            const float4 a = src[2 * c], b = src[2 * c + 1];
-            src[2 * c] = make_float4(0.f, 0.f, 0.f, 0.f);
-            src[2 * c + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (BF16) {
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x, a.y), h1 = __floats2bfloat162_rn(a.z, a.w);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(b.x, b.y), h3 = __floats2bfloat162_rn(b.z, b.w);
+        if (HALF) {
+            float amax = 0.0f;
+            for (int c = threadIdx.x; c < e.D / 4; c += blockDim.x) {
+                const float4 a = src[c];
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+            }
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            __syncthreads();                      // s_red of the previous row has been read
+            if (lane == 0) s_red[warp] = amax;
+            __syncthreads();
+            amax = s_red[0];
+            for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_red[w]);
+            const float inv = amax > 0.0f ? 1.0f / amax : 0.0f;
+            if (threadIdx.x == 0) reinterpret_cast<float*>(e.peer[s] + e.L.back_scale)[slot] = amax;
+            for (int c = threadIdx.x; c < e.D / 8; c += blockDim.x) {
+                const float4 a = src[2 * c], b = src[2 * c + 1];      // second read: from L1 / L2
+                src[2 * c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                src[2 * c + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                __half2 h0 = __floats2half2_rn(a.x * inv, a.y * inv), h1 = __floats2half2_rn(a.z * inv, a.w * inv);
+                __half2 h2 = __floats2half2_rn(b.x * inv, b.y * inv), h3 = __floats2half2_rn(b.z * inv, b.w * inv);
                 uint4 v;
                 v.x = *reinterpret_cast<uint32_t*>(&h0); v.y = *reinterpret_cast<uint32_t*>(&h1);
                 v.z = *reinterpret_cast<uint32_t*>(&h2); v.w = *reinterpret_cast<uint32_t*>(&h3);
                 reinterpret_cast<uint4*>(dst + slot * e.D * 2)[c] = v;
-            } else {
-                float4* d4 = reinterpret_cast<float4*>(dst + slot * e.D * 4);
-                d4[2 * c] = a;
-                d4[2 * c + 1] = b;
+            }
+        } else {
+            for (int c = threadIdx.x; c < e.D / 4; c += blockDim.x) {
+                const float4 a = src[c];
+                src[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                reinterpret_cast<float4*>(dst + slot * e.D * 4)[c] = a;
             }
         }
     }
@@ -392,11 +414,12 @@ ep_push_kernel(const EpDev e, float* __restrict__ y, const int* __restrict__ rec
 
 // Source side, one block per token: wait for every owner's word (the first warp polls, one lane per
 // owner), then out[t] = sum over owners in rank order of the partial row that came back for (t, owner).
-template <bool BF16>
+template <bool HALF>
 __global__ void __launch_bounds__(256)
 ep_combine_kernel(const EpDev e, const int* __restrict__ pos, const int* __restrict__ send_counts, int T,
                   float* __restrict__ out) {
     __shared__ int s_row[64];
+    __shared__ float s_scale[64];
     const int t = blockIdx.x;
     if (threadIdx.x < 64) {
         const int r = threadIdx.x;
@@ -410,6 +433,8 @@ ep_combine_kernel(const EpDev e, const int* __restrict__ pos, const int* __restr
             if (p >= 0) row = min(max(p - start, 0), e.Tm - 1);
         }
         s_row[r] = row;
+        s_scale[r] = (HALF && row >= 0) ? reinterpret_cast<const float*>(e.self + e.L.back_scale)[(size_t)r * e.Tm + row]
+                                        : 1.0f;
     }
     __syncthreads();
     const char* back = e.self + e.L.back;
@@ -419,14 +444,15 @@ ep_combine_kernel(const EpDev e, const int* __restrict__ pos, const int* __restr
             const int row = s_row[r];
             if (row < 0) continue;
             const size_t slot = (size_t)r * e.Tm + row;
-            if (BF16) {
+            if (HALF) {
                 const uint4 v = *reinterpret_cast<const uint4*>(back + (slot * e.D + c) * 2);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+                const __half2* h = reinterpret_cast<const __half2*>(&v);
+                const float sc = s_scale[r];
 #pragma unroll
                 for (int i = 0; i < 4; i++) {
-                    const float2 f = __bfloat1622float2(h[i]);
-                    acc[2 * i] += f.x;
-                    acc[2 * i + 1] += f.y;
+                    const float2 f = __half22float2(h[i]);
+                    acc[2 * i] = fmaf(f.x, sc, acc[2 * i]);
+                    acc[2 * i + 1] = fmaf(f.y, sc, acc[2 * i + 1]);
                 }
             } else {
                 const float4* src = reinterpret_cast<const float4*>(back + (slot * e.D + c) * 4);
@@ -567,7 +593,7 @@ int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float*
     ep->step++;
     if (ep->step == 0) ep->step = 1;        // 0 is what the words hold before the first step
     const EpDev e = ep_dev(ep);
-    const bool bf16 = !(c.flags & B200_EP_COMBINE_F32);
+    const bool half = !(c.flags & B200_EP_COMBINE_F32);
 
     // route (replicated router) and plan
     const int nch = moe_gate_chunks(D, true);
@@ -604,13 +630,13 @@ int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float*
                                          reinterpret_cast<const float*>(ep->xbuf + e.L.recv_w), w1, w1s, w2, w2s, ep->y,
                                          &lc, packed != 0, stream);
     if (st) return st;
-    if (bf16) ep_push_kernel<true><<<grid, 256, 0, stream>>>(e, ep->y, ep->recv_counts, ep->done + 1);
+    if (half) ep_push_kernel<true><<<grid, 256, 0, stream>>>(e, ep->y, ep->recv_counts, ep->done + 1);
     else      ep_push_kernel<false><<<grid, 256, 0, stream>>>(e, ep->y, ep->recv_counts, ep->done + 1);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
 
     // source side
-    if (bf16) ep_combine_kernel<true><<<T, 256, 0, stream>>>(e, ep->pos, ep->send_counts, T, out);
+    if (half) ep_combine_kernel<true><<<T, 256, 0, stream>>>(e, ep->pos, ep->send_counts, T, out);
     else      ep_combine_kernel<false><<<T, 256, 0, stream>>>(e, ep->pos, ep->send_counts, T, out);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());

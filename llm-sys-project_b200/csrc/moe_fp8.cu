@@ -123,6 +123,98 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                  : "memory");
 }
 
+// ---- CTA-pair (cta_group::2) helpers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window)
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(ptx::smem_u32(p)), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
+                 "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(ptx::smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait with cluster-scope acquire (the barrier is signalled from the peer CTA)
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  unsigned sleep_ns) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    uint64_t t0 = 0;
+    uint32_t it = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if (sleep_ns) __nanosleep(sleep_ns);
+        if (((++it) & 255u) == 0) {
+            if (*abort_flag) return false;
+            const uint64_t now = ptx::globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > B200_WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
+        }
+    }
+    return true;
+}
+// TMA tile load of one CTA of a pair: data lands in this CTA, completion bytes go to a barrier that may
+// live in the pair's other CTA (no multicast: every CTA fetches its own tile)
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(ptx::smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(smem_dst)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// one arrival on the mbarrier at this offset in both CTAs of the pair once all MMAs issued so far have
+// retired (two commits, each addressed through the cluster window to one CTA; no multicast qualifier)
+__device__ __forceinline__ void commit_both(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .b32 r0, r1;\n\t"
+        "mapa.shared::cluster.u32 r0, %0, 0;\n\t"
+        "mapa.shared::cluster.u32 r1, %0, 1;\n\t"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [r0];\n\t"
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [r1];\n\t}"
+        ::"r"(ptx::smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void mma2_f8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // acc[0..N-1] += v[0..N-1] * s  as N/2 packed fused multiply-adds
 template <int N>
 __device__ __forceinline__ void promote(unsigned long long* acc2, const uint32_t (&v)[N], unsigned long long s2) {
@@ -149,10 +241,20 @@ __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
 // (j0 = 128 n_tile, QCOLS/2 columns each), so that the gate and the up value of an activation column
 // meet in one thread.
 // MODE 2/3: plain output columns 256 n_tile .. +255.
-template <int MODE>
+//
+// PAIR: two CTAs of a cluster (two SMs) work on one tile of 256 rows with tcgen05.mma.cta_group::2: CTA r holds
+// rows 128 r .. +127 (its own A tile and accumulator) and HALF of the tile's weight rows (accumulator columns
+// 128 r .. +127), so per K block each SM writes and reads 32 KB of shared memory instead of 48 KB, and a
+// weight tile crosses L2 -> shared memory once per 256 rows.  Shared-memory bandwidth (TMA fill + MMA operand
+// reads: 96 KB per K block for a single-CTA 128 x 256 tile, 768 cycles at 128 B/clk against 546 cycles of
+// tensor time) is what bounds the single-CTA kernel.  The leader CTA (rank 0) issues the MMAs; both CTAs'
+// loads complete on the leader's `full` barrier, both CTAs' promotion warps release the accumulator stage on
+// the leader's `tmem_empty` barrier, and tcgen05.commit signals `empty` / `tmem_full` in both CTAs.
+template <int MODE, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                         const GemmParams p) {
+    constexpr int TM = PAIR ? 2 * BM : BM;        // rows of a tile
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     GemmSmem* sm = reinterpret_cast<GemmSmem*>(tiles + (size_t)STAGES * STAGE_BYTES);
@@ -165,11 +267,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     const int w_rows = (MODE == 1) ? 2 * p.I : p.D;         // weight rows per expert
 
     // ---- prologue ---------------------------------------------------------
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;     // 0 = leader
+    const int pair_count = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;     // tile walkers
+    const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) { ptx::mbar_init(&sm->full[s], 1); ptx::mbar_init(&sm->empty[s], 1); }
+        // PAIR: the leader's `full` takes one arrive.expect_tx from each CTA's producer, its `tmem_empty` one
+        // arrival from every promotion warp of both CTAs
+        for (int s = 0; s < STAGES; s++) { ptx::mbar_init(&sm->full[s], PAIR ? 2 : 1); ptx::mbar_init(&sm->empty[s], 1); }
         for (int a = 0; a < 2; a++) {
             ptx::mbar_init(&sm->tmem_full[a], 1);
-            ptx::mbar_init(&sm->tmem_empty[a], NUM_PROMO_WARPS);
+            ptx::mbar_init(&sm->tmem_empty[a], PAIR ? 2 * NUM_PROMO_WARPS : NUM_PROMO_WARPS);
             ptx::mbar_init(&sm->amax_bar[a], NUM_PROMO_WARPS);
         }
         sm->abort_flag = 0;
@@ -181,7 +288,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         for (int e0 = 0; e0 < p.E; e0 += 32) {
             const int e = e0 + lane;
             int t = 0;
-            if (e < p.E) t = ((p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM) * NT;
+            if (e < p.E) t = ((p.offsets[e + 1] - p.offsets[e] + TM - 1) / TM) * NT;
             int incl = t;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
@@ -194,8 +301,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         if (lane == 0) { sm->tile_prefix[p.E] = running; sm->total_tiles = running; }
     }
     if (warp == W_MMA0) {
-        ptx::tmem_alloc(&sm->tmem_base, 512);
-        ptx::tmem_relinquish();
+        if (PAIR) { tmem_alloc2(&sm->tmem_base, 512); tmem_relinquish2(); }
+        else      { ptx::tmem_alloc(&sm->tmem_base, 512); ptx::tmem_relinquish(); }
     }
     if (warp == W_TMA && lane == 0) {
         ptx::prefetch_tensormap(&tmap_a);
@@ -203,6 +310,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();             // the peer's barriers are initialised before anyone signals them
     ptx::tc_fence_after();
     const uint32_t tmem_base = sm->tmem_base;
     const int total_tiles = sm->total_tiles;
@@ -219,7 +327,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // expert whose prefix is <= tile, which is the one that owns tiles.
         e = lo;
         cnt = p.offsets[e + 1] - p.offsets[e];
-        int mt = (cnt + BM - 1) / BM;
+        int mt = (cnt + TM - 1) / TM;
         int local = tile - sm->tile_prefix[e];
         n_tile = local / mt;
         m_tile = local - n_tile * mt;
@@ -231,30 +339,48 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // ===================== TMA producer =====================
         if (lane == 0) {
             int s = 0; uint32_t ph = 0; int gk = 0; (void)gk;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            for (int tile = walker; tile < total_tiles; tile += pair_count) {
                 int e, m_tile, n_tile, cnt;
                 locate(tile, e, m_tile, n_tile, cnt);
-                const int row0 = p.offsets[e] + m_tile * BM;
+                const int row0 = p.offsets[e] + m_tile * TM + (int)crank * BM;
                 const long long wrow0 = (long long)e * w_rows;
                 for (int kb = 0; kb < nkb; kb++) {
-                    if (!ptx::mbar_wait_relaxed(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done;
+                    if (PAIR) { if (!mbar_wait_cluster(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done; }
+                    else      { if (!ptx::mbar_wait_relaxed(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done; }
                     TRACE_STAMP(6, gk); gk++;
                     uint8_t* a_dst = tiles + (size_t)s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
-                    ptx::mbar_expect_tx(&sm->full[s], STAGE_BYTES);
-                    ptx::tma_load_2d(a_dst, &tmap_a, &sm->full[s], kb * BK, row0);
-                    if (p.packed) {
-                        // the tile's K block is one contiguous 32 KB piece of the packed weights
-                        ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], 0, (((e * NT + n_tile) * nkb) + kb) * BN);
-                    } else if (MODE == 1) {
-                        // 2 NQ boxes of QCOLS/2 weight rows: group g = [gate j0 + g QCOLS/2 .. | up j0 + g QCOLS/2 ..]
-                        const int j0 = n_tile * 128;
-#pragma unroll
-                        for (int bx = 0; bx < 2 * NQ; bx++)
-                            ptx::tma_load_2d(b_dst + bx * (QCOLS / 2) * 128, &tmap_b, &sm->full[s], kb * BK,
-                                             (int)(wrow0 + ((bx & 1) ? p.I : 0) + j0 + (QCOLS / 2) * (bx >> 1)));
+                    if (PAIR) {
+                        // this CTA's 128 rows of A and its half of the weight tile (accumulator columns
+                        // 128 crank .. +127); the bytes are counted on the leader's barrier
+                        const uint32_t fbar = map_to_cta(&sm->full[s], 0);
+                        mbar_expect_tx_cluster(fbar, A_BYTES + B_BYTES / 2);
+                        tma_load_2d_pair(a_dst, &tmap_a, fbar, kb * BK, row0);
+                        if (p.packed) {
+                            tma_load_2d_pair(b_dst, &tmap_b, fbar, 0, (((e * NT + n_tile) * nkb) + kb) * BN + (int)crank * 128);
+                        } else if (MODE == 1) {
+                            const int j0 = n_tile * 128 + 64 * (int)crank;
+                            tma_load_2d_pair(b_dst, &tmap_b, fbar, kb * BK, (int)(wrow0 + j0));
+                            tma_load_2d_pair(b_dst + 8192, &tmap_b, fbar, kb * BK, (int)(wrow0 + p.I + j0));
+                        } else {
+                            tma_load_2d_pair(b_dst, &tmap_b, fbar, kb * BK, (int)(wrow0 + n_tile * 256 + 128 * (int)crank));
+                        }
                     } else {
-                        ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + n_tile * 256));
+                        ptx::mbar_expect_tx(&sm->full[s], STAGE_BYTES);
+                        ptx::tma_load_2d(a_dst, &tmap_a, &sm->full[s], kb * BK, row0);
+                        if (p.packed) {
+                            // the tile's K block is one contiguous 32 KB piece of the packed weights
+                            ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], 0, (((e * NT + n_tile) * nkb) + kb) * BN);
+                        } else if (MODE == 1) {
+                            // 2 NQ boxes of QCOLS/2 weight rows: group g = [gate j0 + g QCOLS/2 .. | up j0 + g QCOLS/2 ..]
+                            const int j0 = n_tile * 128;
+#pragma unroll
+                            for (int bx = 0; bx < 2 * NQ; bx++)
+                                ptx::tma_load_2d(b_dst + bx * (QCOLS / 2) * 128, &tmap_b, &sm->full[s], kb * BK,
+                                                 (int)(wrow0 + ((bx & 1) ? p.I : 0) + j0 + (QCOLS / 2) * (bx >> 1)));
+                        } else {
+                            ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + n_tile * 256));
+                        }
                     }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
@@ -266,17 +392,23 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // K block's MMAs stays tied up until they have run (in the issue of the later ones and in the
         // commits); with a single issuer it came back to look at the other stage's "free" barrier
         // hundreds of cycles after the promotion warps had released it.
-        if (lane == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc(0, 0, 0, 0, BM, BN);
+        if (lane == 0 && crank == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc(0, 0, 0, 0, TM, BN);
             const int role = warp - W_MMA0;                 // the TMEM stage this issuer owns
             int s = 0; uint32_t ph = 0;
             uint32_t acc_ph = 0; long long g = 0;           // g: K blocks since the kernel started
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            for (int tile = walker; tile < total_tiles; tile += pair_count) {
                 for (int kb = 0; kb < nkb; kb++, g++) {
                     if ((int)(g & 1) == role) {
-                        if (!ptx::mbar_wait_relaxed(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
-                        TRACE_STAMP(0, g);
-                        if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
+                        if (PAIR) {
+                            if (!mbar_wait_cluster(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
+                            TRACE_STAMP(0, g);
+                            if (!mbar_wait_cluster(&sm->full[s], ph, abort_flag, 0)) goto done;
+                        } else {
+                            if (!ptx::mbar_wait_relaxed(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
+                            TRACE_STAMP(0, g);
+                            if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
+                        }
                         TRACE_STAMP(1, g);
                         ptx::tc_fence_after();
                         const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
@@ -286,10 +418,16 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         for (int k4 = 0; k4 < 4; k4++) {
                             uint64_t ad = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
                             uint64_t bd = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
-                            ptx::mma_f8(d_tmem, ad, bd, idesc, k4 > 0 ? 1u : 0u);
+                            if (PAIR) mma2_f8(d_tmem, ad, bd, idesc, k4 > 0 ? 1u : 0u);
+                            else      ptx::mma_f8(d_tmem, ad, bd, idesc, k4 > 0 ? 1u : 0u);
                         }
-                        ptx::tc_commit(&sm->empty[s]);          // smem stage reusable once the MMAs have read it
-                        ptx::tc_commit(&sm->tmem_full[role]);   // partial sums ready for promotion
+                        if (PAIR) {
+                            commit_both(&sm->empty[s]);
+                            commit_both(&sm->tmem_full[role]);
+                        } else {
+                            ptx::tc_commit(&sm->empty[s]);          // smem stage reusable once the MMAs have read it
+                            ptx::tc_commit(&sm->tmem_full[role]);   // partial sums ready for promotion
+                        }
                         TRACE_STAMP(2, g);
                         acc_ph ^= 1;
                     }
@@ -305,7 +443,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // one shared-memory word cost more than the promotion itself)
         auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
             int ok = 1;
-            if (lane == 0) ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+            if (lane == 0) ok = (PAIR ? mbar_wait_cluster(bar, parity, abort_flag, 0) : ptx::mbar_wait(bar, parity, abort_flag)) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             __syncwarp();
             return ok != 0;
@@ -320,12 +458,20 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const bool trw = (threadIdx.x == p.trace_warp * 32);
 #endif
         const int nkb_w = Kdim / 128;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        // the stage's "free" barrier lives in the leader CTA
+        const uint32_t tmem_empty_addr[2] = {PAIR ? map_to_cta(&sm->tmem_empty[0], 0) : 0u,
+                                             PAIR ? map_to_cta(&sm->tmem_empty[1], 0) : 0u};
+        auto release_stage = [&](int a) {
+            if (PAIR) mbar_arrive_cluster(tmem_empty_addr[a]);
+            else      ptx::mbar_arrive(&sm->tmem_empty[a]);
+        };
+        for (int tile = walker; tile < total_tiles; tile += pair_count) {
             int e, m_tile, n_tile, cnt;
             locate(tile, e, m_tile, n_tile, cnt);
-            const long long grow = (long long)p.offsets[e] + m_tile * BM + row;   // sorted row
-            const bool row_ok = (m_tile * BM + row) < cnt;
-            const bool warp_valid = (m_tile * BM + (warp & 3) * 32) < cnt;    // any valid row in this warp's 32
+            const int trow0 = m_tile * TM + (int)crank * BM;                       // first row of this CTA inside the expert
+            const long long grow = (long long)p.offsets[e] + trow0 + row;         // sorted row
+            const bool row_ok = (trow0 + row) < cnt;
+            const bool warp_valid = (trow0 + (warp & 3) * 32) < cnt;              // any valid row in this warp's 32
             const float* a_sc = p.a_scale + (grow < p.total_rows ? grow : 0) * nkb;
             const float* w_sc0;
             const float* w_sc1;
@@ -373,7 +519,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         if (c == NPAIR - 1) {
                             ptx::tc_fence_before();
                             __syncwarp();
-                            if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);   // the stage is in registers now
+                            if (lane == 0) release_stage(acc);   // the stage is in registers now
 #ifdef B200_GEMM_TRACE
                             if (trw) TRACE_STAMP(4, gp);
 #endif
@@ -384,7 +530,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                         if (c < NPAIR - 1) tmem_ld_cols<CH>(t0 + 2 * (c + 1) * CH + CH, rb);
                     }
                 } else {
-                    if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[acc]);
+                    ptx::tc_fence_before();
+                    if (lane == 0) release_stage(acc);
                 }
 #ifdef B200_GEMM_TRACE
                 if (trw) TRACE_STAMP(5, gp);
@@ -450,8 +597,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const int sub_row = lane / SEGS, seg = lane % SEGS;
                 const int tok = (MODE == 2 && row_ok) ? p.row_tok[grow] : -1;
                 // MODE 2: out[token] += w * acc.  MODE 3: rows[sorted row] = w * acc (plain stores).
-                const long long grow0 = (long long)p.offsets[e] + m_tile * BM + (warp & 3) * 32;
-                const int rows_ok = min(32, cnt - (m_tile * BM + (warp & 3) * 32));
+                const long long grow0 = (long long)p.offsets[e] + trow0 + (warp & 3) * 32;
+                const int rows_ok = min(32, cnt - (trow0 + (warp & 3) * 32));
                 float* const out_col = p.out + n_tile * 256 + wq * QCOLS;
 #pragma unroll
                 for (int pass = 0; pass < QCOLS / SW; pass++) {
@@ -483,7 +630,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 done:
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == W_MMA0) ptx::tmem_dealloc(tmem_base, 512);
+    if (PAIR) cluster_sync_all();            // the pair's MMAs, remote arrivals and TMEM reads are over in both CTAs
+    if (warp == W_MMA0) {
+        if (PAIR) tmem_dealloc2(tmem_base, 512);
+        else      ptx::tmem_dealloc(tmem_base, 512);
+    }
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
 }
 
@@ -581,6 +732,8 @@ __global__ void pack_weights_kernel(int which, const uint8_t* __restrict__ src, 
     *reinterpret_cast<uint4*>(packed + i * 16) = v;
 }
 
+bool g_regs_ok = true;
+
 struct Fp8Scratch {
     float* partials; int* ids; float* wts; int* hist; int* counts; int* offsets; int* row_pair;
     uint8_t* sq; float* ss; int* row_tok; float* row_w; uint8_t* act_q; float* act_s;
@@ -642,35 +795,56 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
 
     static bool attr_done[64] = {false};
     if (b200_first_call_on_device(attr_done)) {
-        B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)GEMM_SMEM_BYTES));
-        B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)GEMM_SMEM_BYTES));
-        B200_CUDA_TRY(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)GEMM_SMEM_BYTES));
-    }
-    {
+        const void* kernels[6] = {(const void*)grouped_gemm_fp8_kernel<1, false>, (const void*)grouped_gemm_fp8_kernel<2, false>,
+                                  (const void*)grouped_gemm_fp8_kernel<3, false>, (const void*)grouped_gemm_fp8_kernel<1, true>,
+                                  (const void*)grouped_gemm_fp8_kernel<2, true>, (const void*)grouped_gemm_fp8_kernel<3, true>};
+        for (int i = 0; i < 6; i++)
+            B200_CUDA_TRY(cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
         // setmaxnreg.inc waits without bound for registers that only setmaxnreg.dec of the same CTA frees:
         // never launch a build whose compiled register count breaks the balance the budgets assume
-        static int regs_ok = -1;
-        if (regs_ok < 0) {
-            cudaFuncAttributes a1{}, a2{}, a3{};
-            B200_CUDA_TRY(cudaFuncGetAttributes(&a1, grouped_gemm_fp8_kernel<1>));
-            B200_CUDA_TRY(cudaFuncGetAttributes(&a2, grouped_gemm_fp8_kernel<2>));
-            B200_CUDA_TRY(cudaFuncGetAttributes(&a3, grouped_gemm_fp8_kernel<3>));
-            auto ok = [](int n) {
-                return n * GEMM_THREADS <= 65536 && n <= PROMO_REGS &&
-                       NUM_PROMO_WARPS * (PROMO_REGS - n) <= 4 * (n - AUX_REGS);
-            };
-            regs_ok = (ok(a1.numRegs) && ok(a2.numRegs) && ok(a3.numRegs)) ? 1 : 0;
+        for (int i = 0; i < 6; i++) {
+            cudaFuncAttributes a{};
+            B200_CUDA_TRY(cudaFuncGetAttributes(&a, kernels[i]));
+            const int n = a.numRegs;
+            if (!(n * GEMM_THREADS <= 65536 && n <= PROMO_REGS && NUM_PROMO_WARPS * (PROMO_REGS - n) <= 4 * (n - AUX_REGS)))
+                g_regs_ok = false;
         }
-        if (!regs_ok) {
-            b200_set_last_error_text("grouped GEMM: the compiled register count does not balance the setmaxnreg budgets");
-            return B200_UNSUPPORTED;
-        }
+    }
+    if (!g_regs_ok) {
+        b200_set_last_error_text("grouped GEMM: the compiled register count does not balance the setmaxnreg budgets");
+        return B200_UNSUPPORTED;
     }
     b200_gemm_profile* prof = (ws->gemm_prof && ws->gemm_prof->on) ? ws->gemm_prof : nullptr;
     const int slot = prof ? (int)(prof->calls % PROF_SLOTS) : 0;
+    // CTA pairs (256-row tiles, half of the weight tile per SM) pay off once experts have enough rows; tiny
+    // batches keep one CTA per tile so that more weight streams run side by side
+    bool pair = (TK / E) >= 96;
+    if (cfg->flags & B200_MOE_SINGLE_CTA_TILES) pair = false;
+    if (cfg->flags & B200_MOE_CTA_PAIR_TILES) pair = true;
+    if (ws->sm_count < 2) pair = false;
+    const unsigned grid = pair ? (unsigned)(ws->sm_count / 2) * 2 : (unsigned)ws->sm_count;
+    auto launch = [&](int mode, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p) -> int {
+        cudaLaunchConfig_t lc = {};
+        lc.gridDim = dim3(grid); lc.blockDim = dim3(GEMM_THREADS); lc.dynamicSmemBytes = GEMM_SMEM_BYTES; lc.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        lc.attrs = attr; lc.numAttrs = pair ? 1 : 0;
+        cudaError_t err;
+        if (pair) {
+            if (mode == 1)      err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<1, true>, ta, tb, p);
+            else if (mode == 2) err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<2, true>, ta, tb, p);
+            else                err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<3, true>, ta, tb, p);
+        } else {
+            if (mode == 1)      err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<1, false>, ta, tb, p);
+            else if (mode == 2) err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<2, false>, ta, tb, p);
+            else                err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<3, false>, ta, tb, p);
+        }
+        b200_count_launch(1);
+        B200_CUDA_TRY(err);
+        B200_CUDA_TRY(cudaGetLastError());
+        return B200_OK;
+    };
     CUtensorMap ta, tb;
     GemmParams p{};
     p.offsets = s.offsets; p.E = E; p.D = D; p.I = I; p.status = ws->d_status; p.total_rows = TK;
@@ -678,26 +852,25 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     p.trace = g_gemm_trace; p.trace_warp = g_gemm_trace_warp;
 #endif
 
-    // GEMM1
+    // GEMM1 (a CTA of a pair fetches half of a weight tile: boxes of 128 rows instead of 256)
     st = b200_make_tmap_u8_sw128(&ta, s.sq, (unsigned long long)TK, D, 128);
     if (st) return st;
     p.packed = packed ? 1 : 0;
-    if (packed) st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I * (D / 128), 128, 256);
+    if (packed) st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I * (D / 128), 128, pair ? 128 : 256);
     else        st = b200_make_tmap_u8_sw128(&tb, w1q, (unsigned long long)E * 2 * I, D, QCOLS / 2);
     if (st) return st;
     p.a_scale = s.ss; p.w_scale = w1s; p.act_q = s.act_q; p.act_s = s.act_s;
     if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][0], stream));
-    grouped_gemm_fp8_kernel<1><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+    st = launch(1, ta, tb, p);
+    if (st) return st;
     if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][1], stream));
-    b200_count_launch(1);
-    B200_CUDA_TRY(cudaGetLastError());
     if (!do_gemm2) return B200_OK;
 
     // GEMM2
     st = b200_make_tmap_u8_sw128(&ta, s.act_q, (unsigned long long)TK, I, 128);
     if (st) return st;
-    if (packed) st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D * (I / 128), 128, 256);
-    else        st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D, I, 256);
+    if (packed) st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D * (I / 128), 128, pair ? 128 : 256);
+    else        st = b200_make_tmap_u8_sw128(&tb, w2q, (unsigned long long)E * D, I, pair ? 128 : 256);
     if (st) return st;
     p.a_scale = s.act_s; p.w_scale = w2s; p.row_tok = s.row_tok; p.row_w = s.row_w;
 #ifdef B200_GEMM_TRACE
@@ -706,9 +879,8 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     if (det) {
         p.out = s.rows;
         if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][2], stream));
-        grouped_gemm_fp8_kernel<3><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
-        b200_count_launch(1);
-        B200_CUDA_TRY(cudaGetLastError());
+        st = launch(3, ta, tb, p);
+        if (st) return st;
         reduce_rows_kernel<<<T, 256, 0, stream>>>(s.rows, s.pair_row, ids, K, D, out);
         if (prof) { B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][3], stream)); prof->calls++; }
         b200_count_launch(1);
@@ -718,10 +890,9 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     p.out = out;
     if (zero_out) B200_CUDA_TRY(cudaMemsetAsync(out, 0, sizeof(float) * (size_t)T * D, stream));
     if (prof) B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][2], stream));
-    grouped_gemm_fp8_kernel<2><<<ws->sm_count, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(ta, tb, p);
+    st = launch(2, ta, tb, p);
+    if (st) return st;
     if (prof) { B200_CUDA_TRY(cudaEventRecord(prof->ev[slot][3], stream)); prof->calls++; }
-    b200_count_launch(1);
-    B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 

@@ -213,9 +213,11 @@ class PeerExpertParallelMoe:
     collective call.  ``group`` is only used once, to hand every rank the 64-byte handles of the other
     ranks' exchange buffers.  The layer's weights are this rank's experts in local order.
 
-    placement: "contiguous" or a pair (owner [E], local [E]) as for ExpertParallelMoe."""
+    placement: "contiguous" or a pair (owner [E], local [E]) as for ExpertParallelMoe.
+    combine_dtype: torch.float16 = partial rows travel as fp16 values relative to the row's largest magnitude
+    (plus that magnitude); torch.float32 = as they are."""
 
-    def __init__(self, group, layer, num_experts, max_tokens, placement="contiguous", combine_dtype=torch.bfloat16,
+    def __init__(self, group, layer, num_experts, max_tokens, placement="contiguous", combine_dtype=torch.float16,
                  wait_limit_ms=0, loopback=False):
         import ctypes as C
         from . import EpConfig, _check, lib
@@ -228,7 +230,9 @@ class PeerExpertParallelMoe:
         self.layer = layer
         self.E, self.K, self.D, self.I = num_experts, layer.K, layer.D, layer.I
         self.max_tokens = max_tokens
-        flags = 0 if combine_dtype == torch.bfloat16 else 2
+        if combine_dtype not in (torch.float16, torch.float32):
+            raise ValueError("combine_dtype: torch.float16 (row-scaled, the default) or torch.float32")
+        flags = 0 if combine_dtype == torch.float16 else 2
         cfg = EpConfig(self.rank, self.world, max_tokens, num_experts, layer.K, layer.D, layer.I, layer.scoring,
                        layer.n_group, layer.topk_group, layer.routed_scale, flags, int(wait_limit_ms))
         om = lm = None

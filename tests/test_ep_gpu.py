@@ -122,7 +122,7 @@ def _small_layer(b200, cuda, rng, T, E, K, D, I, ng, tg):
     return layer, (xq, xs, wg, bias, w1q, w1s, w2q, w2s), to
 
 
-@pytest.mark.parametrize("combine_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("combine_dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("packed", [False, True])
 def test_peer_ep_world1_matches_plain_layer_and_oracle(b200, cuda, combine_dtype, packed):
     """The C-ABI expert-parallel object with one rank: dispatch into its own receive region, grouped GEMMs
@@ -145,8 +145,8 @@ def test_peer_ep_world1_matches_plain_layer_and_oracle(b200, cuda, combine_dtype
             assert np.array_equal(ids.cpu().numpy(), oi)
             assert np.abs(wts.cpu().numpy() - ow).max() <= 5e-7
             got = out.cpu().numpy()
-            tol = 1e-4 if combine_dtype == torch.float32 else 2.0 ** -8
-            assert np.allclose(got, plain, rtol=tol, atol=1e-5)
+            tol = 1e-4 if combine_dtype == torch.float32 else 2.0 ** -10
+            assert np.allclose(got, plain, rtol=tol, atol=tol * np.abs(plain).max())   # fp16 is relative to the row maximum
             ref = oracle.moe_fp8_experts(xq[:Ts], xs[:Ts], w1q, w1s, w2q, w2s, oi, ow, np.arange(Ts, dtype=np.int32))
             assert not (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)).any()
     finally:

@@ -58,7 +58,8 @@ def _worker(rank, world, port, placement_name, combine_bf16, ret, impl="nccl"):
         to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
         layer = b200.MoeFp8Layer(to(wg), to(bias), to(w1q[mine]), to(w1s[mine]), to(w2q[mine]), to(w2s[mine]), K,
                                  b200.SCORE_SIGMOID_GROUPED, 4, 2, 2.5)
-        cdt = torch.bfloat16 if combine_bf16 else torch.float32
+        # 16-bit combine: bf16 rows for the torch.distributed path, row-scaled fp16 rows for the C-ABI object
+        cdt = (torch.float16 if impl == "peer" else torch.bfloat16) if combine_bf16 else torch.float32
         xq, xs = _tokens(rank)
         if impl == "peer":
             # the C-ABI object: peer-store data plane, no collective inside a step; three steps in a row

@@ -140,6 +140,37 @@ def test_fp8_layer_against_emulation(b200, cuda, T, E, K, D, I, ng, tg):
     assert np.allclose(out2.cpu().numpy(), 2 * got, rtol=1e-4, atol=1e-5)
 
 
+@pytest.mark.parametrize("flag", ["single", "pair"])
+@pytest.mark.parametrize("packed", [False, True])
+@pytest.mark.parametrize("T,E,K,D,I", [(700, 4, 2, 512, 256), (96, 8, 2, 768, 384)])
+def test_fp8_layer_both_tile_shapes(b200, cuda, T, E, K, D, I, packed, flag):
+    """The grouped GEMMs on single-CTA 128-row tiles and on CTA-pair 256-row tiles (cta_group::2): experts with
+    fewer than 128, between 128 and 256 and more than 256 rows, row-major and pre-tiled weights, the scatter-add
+    and the fixed-order combine."""
+    rng = np.random.default_rng(T + E + (1 if packed else 0))
+    x, wg, bias, w1, w2, xq, xs, w1q, w1s, w2q, w2s = _layer(rng, T, E, D, I)
+    bit = b200.MOE_CTA_PAIR_TILES if flag == "pair" else b200.MOE_SINGLE_CTA_TILES
+    d = {k: _dev(v, cuda) for k, v in dict(xq=xq, xs=xs, wg=wg, bias=bias, w1q=w1q, w1s=w1s, w2q=w2q, w2s=w2s).items()}
+    w1, w2 = d["w1q"], d["w2q"]
+    fwd = b200.moe_fp8_forward
+    if packed:
+        w1, w2 = torch.empty_like(d["w1q"]), torch.empty_like(d["w2q"])
+        b200.moe_fp8_pack_weights(1, d["w1q"], w1, E, D, I)
+        b200.moe_fp8_pack_weights(2, d["w2q"], w2, E, D, I)
+        fwd = b200.moe_fp8_forward_packed
+    ids, wts = oracle.route_grouped(xq, xs, wg, bias, K, 1, 1, 2.5)
+    ref = oracle.moe_fp8_experts(xq, xs, w1q, w1s, w2q, w2s, ids, wts, np.arange(T, dtype=np.int32))
+    for extra in (0, b200.MOE_DETERMINISTIC):
+        cfg = b200.MoeFp8Config(T, E, K, D, I, b200.SCORE_SIGMOID_GROUPED, 1, 1, 2.5, bit | extra)
+        out = torch.full((T, D), float("nan"), dtype=torch.float32, device=cuda)
+        fwd(d["xq"], d["xs"], d["wg"], d["bias"], w1, d["w1s"], w2, d["w2s"], out, cfg)
+        torch.cuda.synchronize()
+        assert b200.device_status() == 0
+        got = out.cpu().numpy()
+        viol = np.abs(got - ref) > ATOL + RTOL * np.abs(ref)
+        assert not viol.any(), (flag, packed, extra, int(viol.sum()), float(np.abs(got - ref).max()))
+
+
 def test_fp8_experts_skips_foreign_ids(b200, cuda):
     """Expert-parallel building block: ids outside [0,E) (experts owned by other ranks) are skipped."""
     rng = np.random.default_rng(3)
