@@ -38,6 +38,7 @@ ZIPF_S, ZIPF_BETA = 1.1, 0.08
 # --ep-placement "strided": expert e lives on GPU e mod N (a group's 32 experts and a run of hot ones spread over
 # all GPUs); "balanced": greedy placement by the expert loads of a calibration batch; "contiguous": blocks of E/N
 EP_PLACEMENT = "balanced"
+MOE_FLAGS = 0          # --moe-tiles: force the grouped GEMMs' tile shape (4 = single CTA, 8 = CTA pairs)
 RTOL, ATOL = 2e-2, 1e-2
 
 
@@ -169,6 +170,7 @@ def build_moe(b200, torch, dev, world, rank):
     layer = b200.MoeFp8Layer(gate_w, bias, w1q, w1s, w2q, w2s, c["K"], b200.SCORE_SIGMOID_GROUPED, c["n_group"],
                              c["topk_group"], c["routed_scale"])
     layer.pack()          # pre-tiled weights for the grouped GEMMs (the row-major copy stays for the CPU check)
+    layer.flags = MOE_FLAGS
     return layer, xq, xs
 
 
@@ -785,14 +787,18 @@ def main():
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized case of the same kernels (32 experts, 512 tokens; 16 queries, short caches): "
                          "inputs still exceed L2 but only ~2 GB live on the device; not a bench value")
+    ap.add_argument("--moe-tiles", default="auto", choices=["auto", "single", "pair"],
+                    help="tile shape of the grouped GEMMs: 128-row tiles on single CTAs, 256-row tiles on CTA pairs, "
+                         "or the library's own choice by rows per expert")
     ap.add_argument("--ep-impl", default="peer", choices=["peer", "nccl"],
                     help="expert-parallel data plane (N > 1): 'peer' = the library's own kernels over peer memory "
                          "(b200_ep_*), 'nccl' = torch.distributed all-to-alls around the kernels (the baseline)")
     ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "strided", "contiguous"],
                     help="expert placement of the expert-parallel layer (N > 1)")
     args = ap.parse_args()
-    global EP_PLACEMENT
+    global EP_PLACEMENT, MOE_FLAGS
     EP_PLACEMENT = args.ep_placement
+    MOE_FLAGS = {"auto": 0, "single": 4, "pair": 8}[args.moe_tiles]
     if args.small:
         MOE.update(T=512, E=32, n_group=4, topk_group=2)
         DSA.update(B=16, seq_min=8192, seq_max=16384)

@@ -90,9 +90,9 @@ enum b200_moe_flags {
      * bit-reproducible from run to run.  Costs T*K*D*4 bytes of workspace and one more pass over them.
      * Without the flag GEMM2 scatter-adds into the output (order varies, results agree to fp32 rounding). */
     B200_MOE_DETERMINISTIC = 1,
-    /* Tile shape of the grouped GEMMs.  By default a call with at least 96 (token, expert) rows per expert on
-     * average runs 256-row tiles on CTA pairs (tcgen05 cta_group::2; half of a weight tile per SM) and a
-     * smaller one 128-row tiles on single CTAs; these flags force one or the other (results are the same). */
+    /* Tile shape of the grouped GEMMs: 128-row tiles on single CTAs (the default, and the faster one at every
+     * shape measured so far) or 256-row tiles on CTA pairs (tcgen05 cta_group::2; each SM stages half of a
+     * weight tile).  Results agree up to the order of the scatter-add. */
     B200_MOE_SINGLE_CTA_TILES = 4,
     B200_MOE_CTA_PAIR_TILES = 8
 };

@@ -138,41 +138,17 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(ptx::smem_u32(p)), "r"(rank));
     return r;
 }
+// Arrival on a barrier of the pair's other CTA.  Relaxed on purpose: what the arrival hands over is a TMEM
+// stage whose reads have completed (tcgen05.wait::ld + tcgen05.fence::before_thread_sync), no memory data, and
+// a cluster-scope release would first wait for every outstanding global load of the thread (the prefetched
+// scales), which put ~1000 cycles into every K block.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
+    asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr),
                  "r"(bytes)
                  : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(ptx::smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// bounded wait with cluster-scope acquire (the barrier is signalled from the peer CTA)
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                                  unsigned sleep_ns) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    uint64_t t0 = 0;
-    uint32_t it = 0;
-    while (!mbar_try_wait_cluster(bar, parity)) {
-        if (sleep_ns) __nanosleep(sleep_ns);
-        if (((++it) & 255u) == 0) {
-            if (*abort_flag) return false;
-            const uint64_t now = ptx::globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > B200_WAIT_LIMIT_NS) { *abort_flag = 1; return false; }
-        }
-    }
-    return true;
 }
 // TMA tile load of one CTA of a pair: data lands in this CTA, completion bytes go to a barrier that may
 // live in the pair's other CTA (no multicast: every CTA fetches its own tile)
@@ -345,8 +321,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 const int row0 = p.offsets[e] + m_tile * TM + (int)crank * BM;
                 const long long wrow0 = (long long)e * w_rows;
                 for (int kb = 0; kb < nkb; kb++) {
-                    if (PAIR) { if (!mbar_wait_cluster(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done; }
-                    else      { if (!ptx::mbar_wait_relaxed(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done; }
+                    if (!ptx::mbar_wait_relaxed(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done;
                     TRACE_STAMP(6, gk); gk++;
                     uint8_t* a_dst = tiles + (size_t)s * STAGE_BYTES;
                     uint8_t* b_dst = a_dst + A_BYTES;
@@ -400,15 +375,11 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             for (int tile = walker; tile < total_tiles; tile += pair_count) {
                 for (int kb = 0; kb < nkb; kb++, g++) {
                     if ((int)(g & 1) == role) {
-                        if (PAIR) {
-                            if (!mbar_wait_cluster(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
-                            TRACE_STAMP(0, g);
-                            if (!mbar_wait_cluster(&sm->full[s], ph, abort_flag, 0)) goto done;
-                        } else {
-                            if (!ptx::mbar_wait_relaxed(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
-                            TRACE_STAMP(0, g);
-                            if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
-                        }
+                        // (waits on barriers that the peer CTA or tcgen05.commit signal need no cluster-scope
+                        // acquire: what they hand over is a TMEM stage or TMA-written tiles, not memory data)
+                        if (!ptx::mbar_wait_relaxed(&sm->tmem_empty[role], acc_ph ^ 1, abort_flag, ISSUER_SLEEP_NS)) goto done;
+                        TRACE_STAMP(0, g);
+                        if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
                         TRACE_STAMP(1, g);
                         ptx::tc_fence_after();
                         const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
@@ -443,7 +414,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // one shared-memory word cost more than the promotion itself)
         auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
             int ok = 1;
-            if (lane == 0) ok = (PAIR ? mbar_wait_cluster(bar, parity, abort_flag, 0) : ptx::mbar_wait(bar, parity, abort_flag)) ? 1 : 0;
+            if (lane == 0) ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
             ok = __shfl_sync(0xffffffffu, ok, 0);
             __syncwarp();
             return ok != 0;
@@ -462,8 +433,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         const uint32_t tmem_empty_addr[2] = {PAIR ? map_to_cta(&sm->tmem_empty[0], 0) : 0u,
                                              PAIR ? map_to_cta(&sm->tmem_empty[1], 0) : 0u};
         auto release_stage = [&](int a) {
-            if (PAIR) mbar_arrive_cluster(tmem_empty_addr[a]);
-            else      ptx::mbar_arrive(&sm->tmem_empty[a]);
+            if (PAIR && crank != 0) mbar_arrive_cluster(tmem_empty_addr[a]);
+            else                    ptx::mbar_arrive(&sm->tmem_empty[a]);
         };
         for (int tile = walker; tile < total_tiles; tile += pair_count) {
             int e, m_tile, n_tile, cnt;
@@ -816,11 +787,13 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     }
     b200_gemm_profile* prof = (ws->gemm_prof && ws->gemm_prof->on) ? ws->gemm_prof : nullptr;
     const int slot = prof ? (int)(prof->calls % PROF_SLOTS) : 0;
-    // CTA pairs (256-row tiles, half of the weight tile per SM) pay off once experts have enough rows; tiny
-    // batches keep one CTA per tile so that more weight streams run side by side
-    bool pair = (TK / E) >= 96;
+    // Single-CTA 128-row tiles unless the caller asks for CTA pairs.  Measured on B200 the pair tiles (256 rows,
+    // half of the weight tile per SM, a third less shared-memory traffic) are slower at every shape tried
+    // (config 3: GEMM1 3.0 vs 2.2 ms; 32 experts x 1024 rows: 1.9 vs 1.3 ms): the K-block period is set by the
+    // promotion of the accumulator stage through tcgen05.ld, which is the same per SM in both shapes, not by
+    // shared-memory bandwidth, and a pair idles half of its rows on experts with fewer than 129 rows.
+    bool pair = (cfg->flags & B200_MOE_CTA_PAIR_TILES) != 0;
     if (cfg->flags & B200_MOE_SINGLE_CTA_TILES) pair = false;
-    if (cfg->flags & B200_MOE_CTA_PAIR_TILES) pair = true;
     if (ws->sm_count < 2) pair = false;
     const unsigned grid = pair ? (unsigned)(ws->sm_count / 2) * 2 : (unsigned)ws->sm_count;
     auto launch = [&](int mode, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p) -> int {

@@ -72,13 +72,14 @@ class MoeFp8Layer:
     """FP8 block-scale MoE layer (extends moe_forward, kernels/moe/naive_moe.cu:400-471)."""
 
     def __init__(self, gate_w, bias, w1q, w1s, w2q, w2s, top_k, scoring=SCORE_SIGMOID_GROUPED, n_group=8,
-                 topk_group=4, routed_scale=2.5):
+                 topk_group=4, routed_scale=2.5, flags=0):
         self.gate_w, self.bias = gate_w, bias
         self.w1q, self.w1s, self.w2q, self.w2s = w1q, w1s, w2q, w2s
         self.E, self.D = gate_w.shape
         self.I = w2q.shape[-1]
         self.K = top_k
         self.scoring, self.n_group, self.topk_group, self.routed_scale = scoring, n_group, topk_group, routed_scale
+        self.flags = flags          # MoeFp8Config.flags (MOE_DETERMINISTIC, tile shape overrides)
         self.w1p = self.w2p = None
         self._dev = {}
         self._pipe = None
@@ -98,7 +99,7 @@ class MoeFp8Layer:
 
     def cfg(self, T, E=None, K=None):
         return MoeFp8Config(T, self.E if E is None else E, self.K if K is None else K, self.D, self.I, self.scoring,
-                            self.n_group, self.topk_group, self.routed_scale)
+                            self.n_group, self.topk_group, self.routed_scale, self.flags)
 
     def forward(self, xq, xs, out=None):
         T = xq.shape[0]
