@@ -54,8 +54,10 @@ typedef struct b200_moe_config {
 } b200_moe_config;
 
 /* kernels/dsa/naive_dsa.cuh:9-17 (struct DsaConfig) — same seven ints, same order.
- * page_size and total_kv_tokens are carried but, as in the reference, not read:
- * the cache is flat [N, D*] and indices are flat physical token ids. */
+ * The cache is flat [N, D*] and indices are flat physical token ids.  The reference carries page_size and
+ * total_kv_tokens without reading them; here total_kv_tokens, when positive, bounds the indices: an index
+ * that is negative or not below it is an empty entry that contributes nothing (the reference would read out
+ * of bounds).  page_size is used by b200_dsa_forward_bf16_paged only. */
 typedef struct b200_dsa_config {
     int num_queries;         /* Q */
     int num_heads;           /* H */
@@ -219,6 +221,20 @@ B200_API int b200_dsa_forward_f32(b200_ws* ws, const float* q_nope, const float*
 B200_API int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe,
                                    const uint16_t* kc, const uint16_t* kp, const uint16_t* v, const int* idx,
                                    float* out, const b200_dsa_config* cfg, b200_stream_t stream);
+/* Paged front end of the same decode (no reference counterpart: the reference's callers translate
+ * positions themselves and pass flat ids, kernels/dsa/naive_dsa.cuh:15-16,28).  positions [Q,S] are logical
+ * token positions inside the query's sequence; block_table [num_seqs, max_blocks] maps a sequence's logical
+ * page (position / page_size) to a physical page of the cache (row = page * page_size + position %
+ * page_size); seq_of_query [Q] names the sequence of each query (NULL: query q reads sequence q);
+ * valid_len [Q] (NULL: all S) is the number of leading entries of a query's list that count.  The
+ * translation runs inside the gather warps of the decode kernel.  Empty entries — beyond valid_len, a
+ * negative position, a negative page, a page index >= max_blocks, a row >= total_kv_tokens — contribute
+ * nothing, as if removed from the list; a query with only empty entries gets a zero row. */
+B200_API int b200_dsa_forward_bf16_paged(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe,
+                                         const uint16_t* kc, const uint16_t* kp, const uint16_t* v,
+                                         const int* positions, const int* block_table, int max_blocks,
+                                         const int* seq_of_query, const int* valid_len, float* out,
+                                         const b200_dsa_config* cfg, b200_stream_t stream);
 /* No counterpart in the reference.  Same computation and arguments as b200_dsa_forward_bf16, for
  * callers that must not allocate device memory: processes whose memory pool owns all of HBM and
  * forbids cudaMalloc after start-up, plugins that are only handed input and output buffers, and

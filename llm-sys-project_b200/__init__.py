@@ -62,7 +62,7 @@ EXPORTED_SYMBOLS = [
     "b200_quant_act_1x128", "b200_quant_weight_128x128", "b200_moe_route_fp8", "b200_moe_fp8_forward",
     "b200_moe_fp8_experts", "b200_moe_fp8_pack_weights", "b200_moe_fp8_forward_packed",
     "b200_moe_fp8_experts_packed", "b200_moe_fp8_gemm1_stage", "b200_moe_fp8_profile", "b200_moe_fp8_profile_read",
-    "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
+    "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_paged", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
     "b200_dsa_softmax_f32", "b200_dsa_output_proj_f32",
     "b200_ep_plan", "b200_ep_sum_rows", "b200_ep_create", "b200_ep_connect", "b200_ep_forward", "b200_ep_stats",
     "b200_ep_workspace", "b200_ep_destroy",
@@ -257,6 +257,17 @@ def dsa_forward_bf16(q_nope, q_pe, kv_cache_compressed, kv_cache_positional, v_c
     _check(lib().b200_dsa_forward_bf16(None, _p(q_nope), _p(q_pe), _p(kv_cache_compressed),
                                        _p(kv_cache_positional), _p(v_cache), _p(sparse_indices), _p(output),
                                        C.byref(cfg), _stream(stream)), "dsa_forward_bf16")
+
+
+def dsa_forward_bf16_paged(q_nope, q_pe, kv_cache_compressed, kv_cache_positional, v_cache, positions, block_table,
+                           output, cfg, seq_of_query=None, valid_len=None, stream=None):
+    """bf16 decode on logical positions: positions [Q,S] int32 (negative = empty slot), block_table
+    [num_seqs, max_blocks] int32 (logical page -> physical page, negative = not mapped), seq_of_query [Q]
+    (None: query q reads sequence q), valid_len [Q] (None: all S entries count)."""
+    _check(lib().b200_dsa_forward_bf16_paged(None, _p(q_nope), _p(q_pe), _p(kv_cache_compressed),
+                                             _p(kv_cache_positional), _p(v_cache), _p(positions), _p(block_table),
+                                             int(block_table.shape[1]), _p(seq_of_query), _p(valid_len), _p(output),
+                                             C.byref(cfg), _stream(stream)), "dsa_forward_bf16_paged")
 
 
 def dsa_forward_bf16_static(q_nope, q_pe, kv_cache_compressed, kv_cache_positional, v_cache, sparse_indices, output,

@@ -26,6 +26,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "dsa_index.cuh"
 
 void b200_count_launch(int n);
 void b200_set_last_error_text(const char* text);
@@ -60,7 +61,7 @@ constexpr size_t DSA_SMEM_BYTES = 1024 + Q_BYTES + K_BYTES + 2 * V_BYTES + P_BYT
 
 struct DsaParams {
     const __nv_bfloat16 *q_nope, *q_pe, *kc, *kp, *v;
-    const int* idx;
+    DsaIndex ix;
     float* out;        // [Q, H, 512]
     float* part_o;     // [Q, NS, 128, 512]   (NS > 1)
     float* part_ml;    // [Q, NS, 128, 2]     log2-domain max, running sum
@@ -139,11 +140,11 @@ __global__ void __launch_bounds__(DSA_THREADS, 1) dsa_decode_bf16_kernel(const D
         for (int u = 0; u < total_units; u++) {
             const int j = u / UNITS, c = u - j * UNITS;
             if (c == 0) {
-                const int* ids = p.idx + (size_t)b * p.S + (size_t)(t_begin + j) * TKV;
-                kid[0] = ids[pt >> 3];
-                kid[1] = ids[(pt >> 3) + 16];
+                const int s0 = (t_begin + j) * TKV;
+                kid[0] = dsa_resolve(p.ix, b, s0 + (pt >> 3));
+                kid[1] = dsa_resolve(p.ix, b, s0 + (pt >> 3) + 16);
 #pragma unroll
-                for (int x = 0; x < 8; x++) vid[x] = ids[(pt >> 5) + 4 * x];
+                for (int x = 0; x < 8; x++) vid[x] = dsa_resolve(p.ix, b, s0 + (pt >> 5) + 4 * x);
             }
             if (c < KBLK) {
                 if (!ptx::mbar_wait(&sm->k_empty[c], (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
@@ -152,9 +153,14 @@ __global__ void __launch_bounds__(DSA_THREADS, 1) dsa_decode_bf16_kernel(const D
 #pragma unroll
                 for (int x = 0; x < 2; x++) {
                     const int r = (pt >> 3) + 16 * x;
-                    const __nv_bfloat16* src = (c < 8) ? p.kc + kid[x] * DC + c * 64 + j16 * 8
-                                                       : p.kp + kid[x] * DP + j16 * 8;
-                    ptx::cp_async_16(slot + r * 128 + ((j16 ^ (r & 7)) << 4), src);
+                    const uint32_t dst = slot + r * 128 + ((j16 ^ (r & 7)) << 4);
+                    if (kid[x] >= 0) {
+                        const __nv_bfloat16* src = (c < 8) ? p.kc + kid[x] * DC + c * 64 + j16 * 8
+                                                           : p.kp + kid[x] * DP + j16 * 8;
+                        ptx::cp_async_16(dst, src);
+                    } else {        // empty entry: zero row, its score is masked by the softmax threads
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
+                    }
                 }
             } else {
                 const int vb = j & 1;
@@ -164,10 +170,9 @@ __global__ void __launch_bounds__(DSA_THREADS, 1) dsa_decode_bf16_kernel(const D
 #pragma unroll
                 for (int x = 0; x < 8; x++) {
                     const int r = (pt >> 5) + 4 * x;
-                    const __nv_bfloat16* src = p.v + vid[x] * DC + hv * DVH + j32 * 8;
-                    ptx::cp_async_16(vbase + cc * VCHUNK_BYTES + (r >> 3) * 1024 + (r & 7) * 128 +
-                                         ((j16 ^ (r & 7)) << 4),
-                                     src);
+                    const uint32_t dst = vbase + cc * VCHUNK_BYTES + (r >> 3) * 1024 + (r & 7) * 128 + ((j16 ^ (r & 7)) << 4);
+                    if (vid[x] >= 0) ptx::cp_async_16(dst, p.v + vid[x] * DC + hv * DVH + j32 * 8);
+                    else asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst), "r"(0) : "memory");
                 }
             }
             ptx::cp_async_commit();
@@ -229,8 +234,13 @@ __global__ void __launch_bounds__(DSA_THREADS, 1) dsa_decode_bf16_kernel(const D
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         float m = -1e30f, l = 0.0f;
         const float thr = 8.0f / p.sl2;                              // 2^8 in raw-score units
+        // which of the tile's 32 rows are empty entries (one bit per row), looked up one tile ahead
+        // (the entry is fetched during the previous tile and only looked at here, so its latency is hidden)
+        int ent_n = (nt > 0) ? dsa_resolve(p.ix, b, t_begin * TKV + lane) : -1;
         for (int j = 0; j < nt; j++) {
             const int sb = j & 1;
+            const unsigned mask = __ballot_sync(0xffffffffu, ent_n >= 0);
+            if (j + 1 < nt) ent_n = dsa_resolve(p.ix, b, (t_begin + j + 1) * TKV + lane);
             if (!ptx::mbar_wait(&sm->s_full[sb], (uint32_t)((j >> 1) & 1), abort_flag)) goto done;
             ptx::tc_fence_after();
             uint32_t r[32];
@@ -238,6 +248,10 @@ __global__ void __launch_bounds__(DSA_THREADS, 1) dsa_decode_bf16_kernel(const D
             ptx::tc_wait_ld();
             ptx::tc_fence_before();
             ptx::mbar_arrive(&sm->s_empty[sb]);
+            if (mask != 0xffffffffu) {
+#pragma unroll
+                for (int i = 0; i < 32; i++) r[i] = ((mask >> i) & 1u) ? r[i] : 0xff800000u;     // -inf
+            }
             float tmax = -FLT_MAX;
 #pragma unroll
             for (int i = 0; i < 32; i++) tmax = fmaxf(tmax, __uint_as_float(r[i]));
@@ -338,7 +352,7 @@ __global__ void __launch_bounds__(128) dsa_merge_kernel(const float* __restrict_
         const float4 o = reinterpret_cast<const float4*>(part_o + (((size_t)b * NS + s) * HEADS + h) * DC)[threadIdx.x];
         acc.x += o.x * w; acc.y += o.y * w; acc.z += o.z * w; acc.w += o.w * w;
     }
-    const float inv = 1.0f / L;
+    const float inv = L > 0.0f ? 1.0f / L : 0.0f;        // a query whose entries are all empty gets zeros
     reinterpret_cast<float4*>(out + ((size_t)b * H + h) * DC)[threadIdx.x] =
         make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
 }
@@ -346,12 +360,13 @@ __global__ void __launch_bounds__(128) dsa_merge_kernel(const float* __restrict_
 }  // namespace
 
 int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, const void* kp, const void* v,
-                         const int* idx, float* out, float* part_o, float* part_ml, int* status, int Q, int H, int S,
+                         const DsaIndex& ix, float* out, float* part_o, float* part_ml, int* status, int Q, int H, int S,
                          int NS, int tiles_per_split, int tile_rows, cudaStream_t stream);
 
-extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
-                                     const uint16_t* kp, const uint16_t* v, const int* idx, float* out,
-                                     const b200_dsa_config* cfg, b200_stream_t stream) {
+namespace {
+
+int check_dsa_bf16(const void* q_nope, const void* q_pe, const void* kc, const void* kp, const void* v, const int* idx,
+                   const float* out, const b200_dsa_config* cfg) {
     if (!cfg) return B200_BAD_ARG;
     if (!q_nope || !q_pe || !kc || !kp || !v || !idx || !out) return B200_BAD_ARG;
     const int Q = cfg->num_queries, H = cfg->num_heads, S = cfg->num_selected_kv;
@@ -359,11 +374,18 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
     if (cfg->head_dim_compressed != DC || cfg->head_dim_positional != DP) return B200_UNSUPPORTED;
     if (H > HEADS) return B200_UNSUPPORTED;
     if (S % TKV) return B200_BAD_SHAPE;
-    if (Q > 65535) return B200_UNSUPPORTED;
     const uintptr_t align = reinterpret_cast<uintptr_t>(q_nope) | reinterpret_cast<uintptr_t>(q_pe) |
                             reinterpret_cast<uintptr_t>(kc) | reinterpret_cast<uintptr_t>(kp) |
                             reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out);
     if (align & 15) return B200_BAD_ARG;
+    return B200_OK;
+}
+
+// Workspace-backed decode on a resolved row selection.
+int dsa_bf16_impl(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc, const uint16_t* kp,
+                  const uint16_t* v, const DsaIndex& ix, float* out, const b200_dsa_config* cfg, cudaStream_t stream) {
+    const int Q = cfg->num_queries, H = cfg->num_heads, S = cfg->num_selected_kv;
+    if (Q > 65535) return B200_UNSUPPORTED;
     if (!ws) ws = b200_default_ws();
     if (!ws) return B200_CUDA_ERROR;
 
@@ -393,7 +415,7 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
         part_ml = cv.take<float>((size_t)Q * NS * HEADS * 2);
     }
     if (use_pair) {
-        int st = b200_launch_dsa_pair(q_nope, q_pe, kc, kp, v, idx, out, part_o, part_ml, ws->d_status, Q, H, S, NS, tps,
+        int st = b200_launch_dsa_pair(q_nope, q_pe, kc, kp, v, ix, out, part_o, part_ml, ws->d_status, Q, H, S, NS, tps,
                                       pair_tile, stream);
         if (st) return st;
         if (NS > 1) {
@@ -414,7 +436,7 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
     p.kc = reinterpret_cast<const __nv_bfloat16*>(kc);
     p.kp = reinterpret_cast<const __nv_bfloat16*>(kp);
     p.v = reinterpret_cast<const __nv_bfloat16*>(v);
-    p.idx = idx; p.out = out; p.part_o = part_o; p.part_ml = part_ml; p.status = ws->d_status;
+    p.ix = ix; p.out = out; p.part_o = part_o; p.part_ml = part_ml; p.status = ws->d_status;
     p.H = H; p.S = S; p.NS = NS; p.tiles_per_split = tps;
     p.sl2 = 1.4426950408889634f / sqrtf((float)(DC + DP));
     dim3 grid(2, NS, Q);
@@ -427,6 +449,37 @@ extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const 
         B200_CUDA_TRY(cudaGetLastError());
     }
     return B200_OK;
+}
+
+DsaIndex flat_index(const int* idx, const b200_dsa_config* cfg) {
+    DsaIndex ix{};
+    ix.idx = idx; ix.S = cfg->num_selected_kv; ix.page = cfg->page_size > 0 ? cfg->page_size : 1;
+    ix.N = cfg->total_kv_tokens;        // 0 or negative: rows are not range-checked (the reference never reads it)
+    return ix;
+}
+
+}  // namespace
+
+extern "C" int b200_dsa_forward_bf16(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
+                                     const uint16_t* kp, const uint16_t* v, const int* idx, float* out,
+                                     const b200_dsa_config* cfg, b200_stream_t stream) {
+    int st = check_dsa_bf16(q_nope, q_pe, kc, kp, v, idx, out, cfg);
+    if (st) return st;
+    return dsa_bf16_impl(ws, q_nope, q_pe, kc, kp, v, flat_index(idx, cfg), out, cfg, stream);
+}
+
+extern "C" int b200_dsa_forward_bf16_paged(b200_ws* ws, const uint16_t* q_nope, const uint16_t* q_pe, const uint16_t* kc,
+                                           const uint16_t* kp, const uint16_t* v, const int* positions,
+                                           const int* block_table, int max_blocks, const int* seq_of_query,
+                                           const int* valid_len, float* out, const b200_dsa_config* cfg,
+                                           b200_stream_t stream) {
+    int st = check_dsa_bf16(q_nope, q_pe, kc, kp, v, positions, out, cfg);
+    if (st) return st;
+    if (!block_table || max_blocks <= 0) return B200_BAD_ARG;
+    if (cfg->page_size <= 0) return B200_BAD_SHAPE;
+    DsaIndex ix = flat_index(positions, cfg);
+    ix.block_table = block_table; ix.max_blocks = max_blocks; ix.seq_of_query = seq_of_query; ix.valid_len = valid_len;
+    return dsa_bf16_impl(ws, q_nope, q_pe, kc, kp, v, ix, out, cfg, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -536,7 +589,7 @@ extern "C" int b200_dsa_forward_bf16_static(const uint16_t* q_nope, const uint16
     p.kc = reinterpret_cast<const __nv_bfloat16*>(kc);
     p.kp = reinterpret_cast<const __nv_bfloat16*>(kp);
     p.v = reinterpret_cast<const __nv_bfloat16*>(v);
-    p.idx = idx; p.out = out; p.status = status_word;
+    p.ix = flat_index(idx, cfg); p.out = out; p.status = status_word;
     p.part_ml = reinterpret_cast<float*>(scratch + 256);
     p.part_o = reinterpret_cast<float*>(scratch + 256 + ml_bytes);
     p.H = H; p.S = S; p.NS = NS; p.tiles_per_split = tps;

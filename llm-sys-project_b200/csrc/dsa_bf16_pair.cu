@@ -17,6 +17,7 @@
 #include <cfloat>
 
 #include "common.cuh"
+#include "dsa_index.cuh"
 
 void b200_count_launch(int n);
 
@@ -61,12 +62,22 @@ constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + 2 * K_STAGE_BYTES + 2 * V_STAGE_B
 
 struct Params {
     const __nv_bfloat16 *q_nope, *q_pe, *kc, *kp, *v;
-    const int* idx;
+    DsaIndex ix;
     float *out, *part_o, *part_ml;
     int* status;
     int H, S, NS, tiles_per_split;
     float sl2;
 };
+
+__device__ __forceinline__ void zero16(uint32_t smem_addr) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(smem_addr), "r"(0) : "memory");
+}
+// 16 bytes of a selected row into shared memory, or zeros for an empty entry (row < 0)
+__device__ __forceinline__ void fetch16(uint32_t smem_addr, const __nv_bfloat16* base, long long row, int row_elems,
+                                        int elem_off) {
+    if (row >= 0) ptx::cp_async_16(smem_addr, base + row * row_elems + elem_off);
+    else          zero16(smem_addr);
+}
 
 // ---- cluster-scope helpers --------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -225,13 +236,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
         const int gw = pt >> 5;                                   // gather warp 0..3
         auto load_ids = [&](int j, long long (&k8)[8], long long (&kp2)[2], long long (&v16)[16]) {
             if (j < nt) {
-                const int* ids = p.idx + (size_t)b * p.S + (size_t)(t_begin + j) * TKV;
+                const int s0 = (t_begin + j) * TKV;
 #pragma unroll
-                for (int x = 0; x < 8; x++) k8[x] = ids[rank * KROWS + 8 * gw + x];
-                kp2[0] = ids[rank * KROWS + 8 * gw + (lane >> 3)];
-                kp2[1] = ids[rank * KROWS + 8 * gw + (lane >> 3) + 4];
+                for (int x = 0; x < 8; x++) k8[x] = dsa_resolve(p.ix, b, s0 + (int)rank * KROWS + 8 * gw + x);
+                kp2[0] = dsa_resolve(p.ix, b, s0 + (int)rank * KROWS + 8 * gw + (lane >> 3));
+                kp2[1] = dsa_resolve(p.ix, b, s0 + (int)rank * KROWS + 8 * gw + (lane >> 3) + 4);
 #pragma unroll
-                for (int x = 0; x < 16; x++) v16[x] = ids[gw + 4 * x];
+                for (int x = 0; x < 16; x++) v16[x] = dsa_resolve(p.ix, b, s0 + gw + 4 * x);
             }
         };
         long long kid[8], kpid[2] = {0, 0}, vid[16], kid_n[8], kpid_n[2] = {0, 0}, vid_n[16];
@@ -259,17 +270,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
 #pragma unroll
                     for (int hf = 0; hf < 2; hf++) {
                         const int ch = lane + 32 * hf;
-                        ptx::cp_async_16(kst + (ch >> 3) * KSLOT_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4),
-                                         p.kc + kid[x] * DC + ch * 8);
+                        fetch16(kst + (ch >> 3) * KSLOT_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4), p.kc, kid[x], DC, ch * 8);
                     }
                 }
                 // Kp (128 bytes per row, slot 8): four rows per instruction
 #pragma unroll
                 for (int x = 0; x < 2; x++) {
                     const int r = 8 * gw + (lane >> 3) + 4 * x, j16 = lane & 7;
-                    ptx::cp_async_16(kst + 8 * KSLOT_BYTES + r * 128 + ((j16 ^ (r & 7)) << 4), p.kp + kpid[x] * DP + j16 * 8);
+                    fetch16(kst + 8 * KSLOT_BYTES + r * 128 + ((j16 ^ (r & 7)) << 4), p.kp, kpid[x], DP, j16 * 8);
                 }
             }
+            __threadfence_block();                 // zero-filled rows of empty entries are written before the arrival
             ptx::cp_async_arrive_noinc(&sm->k_full[st]);
             {
                 if (!ptx::mbar_wait(&sm->v_empty[st], par, abort_flag)) goto done;
@@ -281,9 +292,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
 #pragma unroll
                 for (int x = 0; x < 16; x++) {
                     const int r = gw + 4 * x;
-                    ptx::cp_async_16(chunk + (r >> 3) * 1024 + (r & 7) * 128 + ((v16 ^ (r & 7)) << 4),
-                                     p.v + vid[x] * DC + 256 * (int)rank + lane * 8);
+                    fetch16(chunk + (r >> 3) * 1024 + (r & 7) * 128 + ((v16 ^ (r & 7)) << 4), p.v, vid[x], DC,
+                            256 * (int)rank + lane * 8);
                 }
+                __threadfence_block();
                 ptx::cp_async_arrive_noinc(&sm->v_full[st]);
             }
         }
@@ -364,8 +376,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         float m = -1e30f, l = 0.0f;
         const float thr = 8.0f / p.sl2;
+        // which of this lane's 32 score columns (tile rows 32 hh .. +31) are empty entries: one bit per row,
+        // looked up one tile ahead
+        // (the entry is fetched during the previous tile and only looked at here, so its latency is hidden)
+        int ent_n = (nt > 0) ? dsa_resolve(p.ix, b, t_begin * TKV + 32 * hh + lane) : -1;
         for (int j = 0; j < nt; j++) {
             const int sb = j & 1;
+            const unsigned mask = __ballot_sync(0xffffffffu, ent_n >= 0);
+            if (j + 1 < nt) ent_n = dsa_resolve(p.ix, b, (t_begin + j + 1) * TKV + 32 * hh + lane);
             if (!ptx::mbar_wait(&sm->s_full[sb], (uint32_t)((j >> 1) & 1), abort_flag)) goto done;
             ptx::tc_fence_after();
             uint32_t r[32];
@@ -373,6 +391,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1) dsa_deco
             ptx::tc_wait_ld();
             ptx::tc_fence_before();
             ptx::mbar_arrive(&sm->s_empty[sb]);
+            if (mask != 0xffffffffu) {
+#pragma unroll
+                for (int i = 0; i < 32; i++) r[i] = ((mask >> i) & 1u) ? r[i] : 0xff800000u;     // -inf
+            }
             float tmax = -FLT_MAX;
 #pragma unroll
             for (int i = 0; i < 32; i++) tmax = fmaxf(tmax, __uint_as_float(r[i]));
@@ -581,40 +603,62 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
         // more than twice the rate of scattered 128-byte ones).  Each lane fetches the ids of the rows
         // its warp owns one tile ahead and hands them round by shuffle; the copies of a tile signal its
         // barrier by themselves when they land, so these threads never wait for data.
-        const int* ids = p.idx + (size_t)b * p.S + (size_t)t_begin * TKV;
+        const int s_begin = t_begin * TKV;
         if (pt < 32 * NKW) {
             constexpr int RPW = KROWS / NKW;                      // K rows per warp
             const int kw = pt >> 5;                               // rows RPW kw .. RPW kw + RPW - 1 of this CTA's 64
             const int my = (int)rank * KROWS + RPW * kw + (lane % RPW);
-            int id_n = (nt > 0) ? ids[my] : 0;
+            int id_n = (nt > 0) ? dsa_resolve(p.ix, b, s_begin + my) : -1;
             const uint32_t kst = ptx::smem_u32(sK);
             for (int j = 0; j < nt; j++) {
                 const int id = id_n;
-                if (j + 1 < nt) id_n = ids[(size_t)(j + 1) * TKV + my];
+                if (j + 1 < nt) id_n = dsa_resolve(p.ix, b, s_begin + (j + 1) * TKV + my);
                 if (!ptx::mbar_wait(&sm->k_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
                 // Kc: row r, 16-byte chunk ch = lane (+32): slot ch/8, position (ch%8) ^ (r%8)
+                if (__all_sync(0xffffffffu, id >= 0)) {
+                    // every row of this warp is live (the usual case): copies only, no per-row test
 #pragma unroll 8
-                for (int x = 0; x < RPW; x++) {
-                    const size_t rid = (size_t)__shfl_sync(0xffffffffu, id, x);
-                    const int r = RPW * kw + x;
+                    for (int x = 0; x < RPW; x++) {
+                        const size_t rid = (size_t)__shfl_sync(0xffffffffu, id, x);
+                        const int r = RPW * kw + x;
 #pragma unroll
-                    for (int hf = 0; hf < 2; hf++) {
-                        const int ch = lane + 32 * hf;
-                        ptx::cp_async_16(kst + (ch >> 3) * KSLOT_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4),
-                                         p.kc + rid * DC + ch * 8);
+                        for (int hf = 0; hf < 2; hf++) {
+                            const int ch = lane + 32 * hf;
+                            ptx::cp_async_16(kst + (ch >> 3) * KSLOT_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4),
+                                             p.kc + rid * DC + ch * 8);
+                        }
                     }
-                }
-                // Kp (128 bytes per row, slot 8): four rows per instruction
+                    // Kp (128 bytes per row, slot 8): four rows per instruction
 #pragma unroll
-                for (int x = 0; x < RPW / 4; x++) {
-                    const int rr = 4 * x + (lane >> 3), j16 = lane & 7;
-                    const size_t rid = (size_t)__shfl_sync(0xffffffffu, id, rr);
-                    const int r = RPW * kw + rr;
-                    ptx::cp_async_16(kst + 8 * KSLOT_BYTES + r * 128 + ((j16 ^ (r & 7)) << 4), p.kp + rid * DP + j16 * 8);
+                    for (int x = 0; x < RPW / 4; x++) {
+                        const int rr = 4 * x + (lane >> 3), j16 = lane & 7;
+                        const size_t rid = (size_t)__shfl_sync(0xffffffffu, id, rr);
+                        const int r = RPW * kw + rr;
+                        ptx::cp_async_16(kst + 8 * KSLOT_BYTES + r * 128 + ((j16 ^ (r & 7)) << 4), p.kp + rid * DP + j16 * 8);
+                    }
+                } else {
+#pragma unroll 4
+                    for (int x = 0; x < RPW; x++) {
+                        const long long rid = __shfl_sync(0xffffffffu, id, x);
+                        const int r = RPW * kw + x;
+#pragma unroll
+                        for (int hf = 0; hf < 2; hf++) {
+                            const int ch = lane + 32 * hf;
+                            fetch16(kst + (ch >> 3) * KSLOT_BYTES + r * 128 + (((ch & 7) ^ (r & 7)) << 4), p.kc, rid, DC, ch * 8);
+                        }
+                    }
+#pragma unroll
+                    for (int x = 0; x < RPW / 4; x++) {
+                        const int rr = 4 * x + (lane >> 3), j16 = lane & 7;
+                        const long long rid = __shfl_sync(0xffffffffu, id, rr);
+                        const int r = RPW * kw + rr;
+                        fetch16(kst + 8 * KSLOT_BYTES + r * 128 + ((j16 ^ (r & 7)) << 4), p.kp, rid, DP, j16 * 8);
+                    }
+                    __threadfence_block();         // zero-filled rows are written before the arrival
                 }
                 ptx::cp_async_arrive_noinc(&sm->k_full);
                 // pull the next tile's rows into L2 while this tile is on its way
-                if (j + 1 < nt && lane < RPW) {
+                if (j + 1 < nt && lane < RPW && id_n >= 0) {
                     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kc + (size_t)id_n * DC), "r"(DC * 2) : "memory");
                     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.kp + (size_t)id_n * DP), "r"(DP * 2) : "memory");
                 }
@@ -623,8 +667,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
             constexpr int VPW = TKV / NVW;                        // V rows per warp (32 or 64)
             const int vw = (pt - 32 * NKW) >> 5;                  // V rows vw, vw + NVW, ... of the tile's 128
             const int my0 = vw + NVW * lane, my1 = (VPW > 32) ? vw + NVW * (lane + 32) : my0;
-            int id0_n = 0, id1_n = 0;
-            if (nt > 0) { id0_n = ids[my0]; id1_n = ids[my1]; }
+            int id0_n = -1, id1_n = -1;
+            if (nt > 0) { id0_n = dsa_resolve(p.ix, b, s_begin + my0); id1_n = dsa_resolve(p.ix, b, s_begin + my1); }
             // this CTA's 512 contiguous bytes of a V row: columns [256 rank, 256 rank + 256);
             // 64-column chunk q = lane / 8 (MMA q/2, half q%2)
             const int q = lane >> 3, v16 = lane & 7;
@@ -632,21 +676,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
             for (int j = 0; j < nt; j++) {
                 const int id0 = id0_n, id1 = id1_n;
                 if (j + 1 < nt) {
-                    id0_n = ids[(size_t)(j + 1) * TKV + my0];
-                    id1_n = ids[(size_t)(j + 1) * TKV + my1];
+                    id0_n = dsa_resolve(p.ix, b, s_begin + (j + 1) * TKV + my0);
+                    id1_n = dsa_resolve(p.ix, b, s_begin + (j + 1) * TKV + my1);
                 }
                 if (!ptx::mbar_wait(&sm->v_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) goto done;
+                if (__all_sync(0xffffffffu, (id0 >= 0) && (id1 >= 0))) {
 #pragma unroll 8
-                for (int x = 0; x < VPW; x++) {
-                    const size_t rid = (size_t)__shfl_sync(0xffffffffu, (x < 32) ? id0 : id1, x & 31);
-                    const int r = vw + NVW * x;
-                    ptx::cp_async_16(chunk + (r >> 3) * 1024 + (r & 7) * 128 + ((v16 ^ (r & 7)) << 4),
-                                     p.v + rid * DC + 256 * (int)rank + lane * 8);
+                    for (int x = 0; x < VPW; x++) {
+                        const size_t rid = (size_t)__shfl_sync(0xffffffffu, (x < 32) ? id0 : id1, x & 31);
+                        const int r = vw + NVW * x;
+                        ptx::cp_async_16(chunk + (r >> 3) * 1024 + (r & 7) * 128 + ((v16 ^ (r & 7)) << 4),
+                                         p.v + rid * DC + 256 * (int)rank + lane * 8);
+                    }
+                } else {
+#pragma unroll 4
+                    for (int x = 0; x < VPW; x++) {
+                        const long long rid = __shfl_sync(0xffffffffu, (x < 32) ? id0 : id1, x & 31);
+                        const int r = vw + NVW * x;
+                        fetch16(chunk + (r >> 3) * 1024 + (r & 7) * 128 + ((v16 ^ (r & 7)) << 4), p.v, rid, DC,
+                                256 * (int)rank + lane * 8);
+                    }
+                    __threadfence_block();
                 }
                 ptx::cp_async_arrive_noinc(&sm->v_full);
                 if (j + 1 < nt) {
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v + (size_t)id0_n * DC + 256 * (int)rank), "r"(512) : "memory");
-                    if (VPW > 32)
+                    if (id0_n >= 0)
+                        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v + (size_t)id0_n * DC + 256 * (int)rank), "r"(512) : "memory");
+                    if (VPW > 32 && id1_n >= 0)
                         asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.v + (size_t)id1_n * DC + 256 * (int)rank), "r"(512) : "memory");
                 }
             }
@@ -720,8 +776,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         float m = -1e30f, l = 0.0f;
         const float thr = 8.0f / p.sl2;
+        // which of this lane's 64 score columns (tile rows 64 hh .. +63) are empty entries: one bit per row,
+        // looked up one tile ahead (two index loads per lane and tile)
+        // (the entries are fetched during the previous tile and only looked at here, so their latency is hidden)
+        int e0_n = -1, e1_n = -1;
+        if (nt > 0) {
+            e0_n = dsa_resolve(p.ix, b, t_begin * TKV + 64 * hh + lane);
+            e1_n = dsa_resolve(p.ix, b, t_begin * TKV + 64 * hh + 32 + lane);
+        }
         for (int j = 0; j < nt; j++) {
             const int sb = j & 1;
+            const unsigned mlo = __ballot_sync(0xffffffffu, e0_n >= 0), mhi = __ballot_sync(0xffffffffu, e1_n >= 0);
+            if (j + 1 < nt) {
+                e0_n = dsa_resolve(p.ix, b, (t_begin + j + 1) * TKV + 64 * hh + lane);
+                e1_n = dsa_resolve(p.ix, b, (t_begin + j + 1) * TKV + 64 * hh + 32 + lane);
+            }
             if (!ptx::mbar_wait(&sm->s_full[sb], (uint32_t)((j >> 1) & 1), abort_flag)) goto done;
             ptx::tc_fence_after();
             uint32_t r[64];
@@ -729,6 +798,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS128, 1) dsa_d
             ptx::tc_wait_ld();
             ptx::tc_fence_before();
             ptx::mbar_arrive(&sm->s_empty[sb]);
+            if ((mlo & mhi) != 0xffffffffu) {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    r[i] = ((mlo >> i) & 1u) ? r[i] : 0xff800000u;              // -inf
+                    r[32 + i] = ((mhi >> i) & 1u) ? r[32 + i] : 0xff800000u;
+                }
+            }
             float tmax = -FLT_MAX;
 #pragma unroll
             for (int i = 0; i < 64; i++) tmax = fmaxf(tmax, __uint_as_float(r[i]));
@@ -843,7 +919,7 @@ done:
 // Host side: called by b200_dsa_forward_bf16 with tile_rows = 128 (S % 128 == 0) or 64 (S % 64 == 0);
 // tiles_per_split counts tiles of that size.
 int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, const void* kp, const void* v,
-                         const int* idx, float* out, float* part_o, float* part_ml, int* status, int Q, int H, int S,
+                         const DsaIndex& ix, float* out, float* part_o, float* part_ml, int* status, int Q, int H, int S,
                          int NS, int tiles_per_split, int tile_rows, cudaStream_t stream) {
     static bool attr_done[64] = {false};
     if (b200_first_call_on_device(attr_done)) {
@@ -858,7 +934,7 @@ int b200_launch_dsa_pair(const void* q_nope, const void* q_pe, const void* kc, c
     p.kc = static_cast<const __nv_bfloat16*>(kc);
     p.kp = static_cast<const __nv_bfloat16*>(kp);
     p.v = static_cast<const __nv_bfloat16*>(v);
-    p.idx = idx; p.out = out; p.part_o = part_o; p.part_ml = part_ml; p.status = status;
+    p.ix = ix; p.out = out; p.part_o = part_o; p.part_ml = part_ml; p.status = status;
     p.H = H; p.S = S; p.NS = NS; p.tiles_per_split = tiles_per_split;
     p.sl2 = 1.4426950408889634f / sqrtf((float)(pair::DC + pair::DP));
     if (tile_rows == 128) {

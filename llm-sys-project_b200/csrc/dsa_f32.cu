@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(DSA_HB * 32)
 dsa_fused_f32_kernel(const float* __restrict__ q_nope, const float* __restrict__ q_pe,
                      const float* __restrict__ kc, const float* __restrict__ kp, const float* __restrict__ v,
                      const int* __restrict__ idx, float* __restrict__ out,
-                     int H, int Dc, int Dp, int S, int TS, float scale) {
+                     int H, int Dc, int Dp, int S, int TS, float scale, int N) {
     extern __shared__ float sm[];
     const int Dk = Dc + Dp;
     const int ldk = Dk | 1;                       // odd row stride: lanes hit distinct banks
@@ -53,22 +53,28 @@ dsa_fused_f32_kernel(const float* __restrict__ q_nope, const float* __restrict__
     for (int s0 = 0; s0 < S; s0 += TS) {
         const int rows = min(TS, S - s0);
         __syncthreads();                          // previous tile fully consumed (and qs visible)
-        if (threadIdx.x < rows) row_id[threadIdx.x] = (long long)idx[(size_t)q * S + s0 + threadIdx.x];
+        // an index that is negative or, when the cache size N is given, not below N is an empty entry: it
+        // is not read and contributes nothing (the reference reads it unchecked, kernels/dsa/naive_dsa.cu:19-24)
+        if (threadIdx.x < rows) {
+            const int id = idx[(size_t)q * S + s0 + threadIdx.x];
+            row_id[threadIdx.x] = (id < 0 || (N > 0 && id >= N)) ? -1ll : (long long)id;
+        }
         __syncthreads();
         for (int i = threadIdx.x; i < rows * Dk; i += blockDim.x) {
             int r = i / Dk, d = i % Dk;
             long long id = row_id[r];
-            ks[(size_t)r * ldk + d] = (d < Dc) ? kc[id * Dc + d] : kp[id * Dp + (d - Dc)];
+            ks[(size_t)r * ldk + d] = id < 0 ? 0.0f : ((d < Dc) ? kc[id * Dc + d] : kp[id * Dp + (d - Dc)]);
         }
         for (int i = threadIdx.x; i < rows * Dc; i += blockDim.x) {
             int r = i / Dc, d = i % Dc;
-            vs[(size_t)r * Dc + d] = v[row_id[r] * Dc + d];
+            vs[(size_t)r * Dc + d] = row_id[r] < 0 ? 0.0f : v[row_id[r] * Dc + d];
         }
         __syncthreads();
 
         // scores: lane = row
         float sc = -FLT_MAX;
-        if (lane < rows) {
+        const bool row_live = lane < rows && row_id[lane] >= 0;
+        if (row_live) {
             const float* kr = ks + (size_t)lane * ldk;
             const float* qr = qs + warp * Dk;
             float sum = 0.0f;
@@ -80,7 +86,7 @@ dsa_fused_f32_kernel(const float* __restrict__ q_nope, const float* __restrict__
         for (int o = 16; o > 0; o >>= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, o));
         const float m_new = fmaxf(m, tile_max);
         const float corr = expf(m - m_new);       // first tile: exp(-huge) = 0, acc and l are 0 anyway
-        const float p = (lane < rows) ? expf(sc - m_new) : 0.0f;
+        const float p = row_live ? expf(sc - m_new) : 0.0f;
         float psum = p;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, o);
@@ -100,7 +106,7 @@ dsa_fused_f32_kernel(const float* __restrict__ q_nope, const float* __restrict__
         }
     }
     if (head_ok) {
-        const float inv = 1.0f / l;
+        const float inv = l > 0.0f ? 1.0f / l : 0.0f;      // every entry empty: zero row
 #pragma unroll
         for (int j = 0; j < NJ; j++) {
             int d = lane + 32 * j;
@@ -203,7 +209,7 @@ static int launch_dsa_f32(const float* qn, const float* qp, const float* kc, con
     dim3 grid(c->num_queries, ceil_div(c->num_heads, DSA_HB));
     float scale = 1.0f / sqrtf((float)Dk);        // naive_dsa.cu:464
     dsa_fused_f32_kernel<NJ><<<grid, DSA_HB * 32, smem, stream>>>(qn, qp, kc, kp, v, idx, out, c->num_heads, Dc, Dp,
-                                                                   c->num_selected_kv, TS, scale);
+                                                                   c->num_selected_kv, TS, scale, c->total_kv_tokens);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
