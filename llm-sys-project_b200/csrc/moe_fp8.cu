@@ -14,22 +14,22 @@
 //                          in ascending expert order (the reference's order, naive_moe.cu:424):
 //                          the bit-reproducible alternative to the scatter-add.
 //
-// GEMM structure (one CTA per SM, 640 threads, tiles 128 x 256 x 128 handed out round-robin,
+// GEMM structure (one CTA per SM, 384 threads, tiles 128 x 256 x 128 handed out round-robin,
 // expert-major):
-//   warp 16      TMA producer: A tile (128 rows x 128 B) and B tile (256 rows x 128 B) per
+//   warp 8       TMA producer: A tile (128 rows x 128 B) and B tile (256 rows x 128 B) per
 //                K block into a 4-stage shared-memory ring (128-byte swizzle, K-major).
-//   warps 17,18  MMA issuers, one per 256-column TMEM accumulator stage (K blocks alternate between
+//   warps 9,10   MMA issuers, one per 256-column TMEM accumulator stage (K blocks alternate between
 //                them): 4 x tcgen05.mma kind::f8f6f4 (K = 32 each) per K block, started fresh for
 //                every K block.  Everything that waits next to the promotion warps sleeps between
 //                polls: a warp that spins takes issue slots from the promotion warps that share
 //                its scheduler.
-//   warps 0-15   promotion + epilogue: tcgen05.ld the K block's partial sums and fold them
+//   warps 0-7    promotion + epilogue: tcgen05.ld the K block's partial sums and fold them
 //                into fp32 registers with a_scale[row,kb] * w_scale[nblk,kb] (the scales are
 //                arbitrary fp32 values, so the scaling cannot be left to the tensor core).
 //                Warp w owns TMEM lanes 32 (w % 4) .. +31 (the tile rows) and accumulator columns
-//                64 (w / 4) .. +63: 64 running sums per thread, updated by packed fma.rn.f32x2.
-//                Four promotion warps per scheduler (instead of two with 128 sums each) hide the
-//                commit -> tcgen05.ld -> FMA latency chain of one warp behind the others' work.
+//                128 (w / 4) .. +127: 128 running sums per thread.  (A build with 16 promotion warps
+//                and 64 sums each, -DB200_GEMM_PROMO_WARPS=16, measured no faster; neither did packed
+//                fma.rn.f32x2 arithmetic, -DB200_GEMM_PACKED_FMA.)
 // Every mbarrier wait is bounded; on give-up the CTA flags B200_TIMEOUT and winds down.
 #include "common.cuh"
 #include "moe_internal.cuh"
@@ -191,20 +191,21 @@ __device__ __forceinline__ void mma2_f8(uint32_t d_tmem, uint64_t adesc, uint64_
         : "memory");
 }
 
-// acc[0..N-1] += v[0..N-1] * s  as N/2 packed fused multiply-adds
+// acc[0..N-1] += v[0..N-1] * s  (B200_GEMM_PACKED_FMA: as N/2 fma.rn.f32x2, same bits)
 template <int N>
-__device__ __forceinline__ void promote(unsigned long long* acc2, const uint32_t (&v)[N], unsigned long long s2) {
+__device__ __forceinline__ void promote(float* acc, const uint32_t (&v)[N], float s) {
+#ifdef B200_GEMM_PACKED_FMA
+    const unsigned long long s2 = ptx::pack_f32x2(s, s);
 #pragma unroll
     for (int i = 0; i < N / 2; i++) {
-#ifdef B200_GEMM_SCALAR_FMA
-        float a0, a1, s, s_;
-        ptx::unpack_f32x2(acc2[i], a0, a1);
-        ptx::unpack_f32x2(s2, s, s_);
-        acc2[i] = ptx::pack_f32x2(fmaf(__uint_as_float(v[2 * i]), s, a0), fmaf(__uint_as_float(v[2 * i + 1]), s, a1));
-#else
-        acc2[i] = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), s2, acc2[i]);
-#endif
+        const unsigned long long r = ptx::fma_f32x2(ptx::pack_f32x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), s2,
+                                                    ptx::pack_f32x2(acc[2 * i], acc[2 * i + 1]));
+        ptx::unpack_f32x2(r, acc[2 * i], acc[2 * i + 1]);
     }
+#else
+#pragma unroll
+    for (int i = 0; i < N; i++) acc[i] = fmaf(__uint_as_float(v[i]), s, acc[i]);
+#endif
 }
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&r)[N]) {
@@ -455,9 +456,9 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 w_sc0 = base + (size_t)(n_tile * 2 + (wq * QCOLS) / 128) * nkb_w;
                 w_sc1 = w_sc0;
             }
-            unsigned long long acc2[QCOLS / 2];
+            float accv[QCOLS];
 #pragma unroll
-            for (int i = 0; i < QCOLS / 2; i++) acc2[i] = 0ull;
+            for (int i = 0; i < QCOLS; i++) accv[i] = 0.0f;
 
             // scales of K block kb+1 are fetched while block kb is being promoted
             float sa_n = row_ok ? a_sc[0] : 0.0f, w0_n = w_sc0[0], w1_n = (MODE == 1) ? w_sc1[0] : 0.0f;
@@ -476,16 +477,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 if (warp_valid) {
                     // warps whose 32 rows are all padding only hand the stage back
                     ptx::tc_fence_after();
-                    const unsigned long long s0p = ptx::pack_f32x2(s0, s0), s1p = ptx::pack_f32x2(s1, s1);
                     const uint32_t t0 = tmem_base + lane_addr + acc * BN + wq * QCOLS;
                     // QCOLS columns in chunks of CH, two loads in flight; columns [0, QCOLS/2) take s0 (MODE 1:
                     // gate), the rest s1 (MODE 1: up)
                     constexpr int NPAIR = QCOLS / (2 * CH);
                     uint32_t ra[CH], rb[CH];
-                    tmem_ld_cols<CH>(t0, ra);
-                    tmem_ld_cols<CH>(t0 + CH, rb);
 #pragma unroll
                     for (int c = 0; c < NPAIR; c++) {
+                        tmem_ld_cols<CH>(t0 + 2 * c * CH, ra);
+                        tmem_ld_cols<CH>(t0 + 2 * c * CH + CH, rb);
                         ptx::tc_wait_ld();
                         if (c == NPAIR - 1) {
                             ptx::tc_fence_before();
@@ -495,10 +495,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                             if (trw) TRACE_STAMP(4, gp);
 #endif
                         }
-                        promote<CH>(acc2 + c * CH, ra, (2 * c * CH < QCOLS / 2) ? s0p : s1p);
-                        if (c < NPAIR - 1) tmem_ld_cols<CH>(t0 + 2 * (c + 1) * CH, ra);
-                        promote<CH>(acc2 + c * CH + CH / 2, rb, ((2 * c + 1) * CH < QCOLS / 2) ? s0p : s1p);
-                        if (c < NPAIR - 1) tmem_ld_cols<CH>(t0 + 2 * (c + 1) * CH + CH, rb);
+                        promote<CH>(accv + 2 * c * CH, ra, (2 * c * CH < QCOLS / 2) ? s0 : s1);
+                        promote<CH>(accv + (2 * c + 1) * CH, rb, ((2 * c + 1) * CH < QCOLS / 2) ? s0 : s1);
                     }
                 } else {
                     ptx::tc_fence_before();
@@ -519,17 +517,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                 // Fast exp / reciprocal: the result is rounded to e4m3 next, an ulp of fp32 does not matter.
                 constexpr int AC = QCOLS / 2;          // activation columns of this thread
                 float amax = 0.0f;
+                if (warp_valid) {
 #pragma unroll
-                for (int i = 0; i < AC / 2; i++) {
-                    float g0, g1, u0, u1;
-                    ptx::unpack_f32x2(acc2[i], g0, g1);
-                    ptx::unpack_f32x2(acc2[AC / 2 + i], u0, u1);
-                    const float a0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
-                    const float a1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
-                    acc2[i] = ptx::pack_f32x2(a0, a1);
-                    amax = fmaxf(amax, fmaxf(fabsf(a0), fabsf(a1)));
+                    for (int i = 0; i < AC; i++) {
+                        const float g = accv[i], u = accv[AC + i];
+                        const float a = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        accv[i] = a;
+                        amax = fmaxf(amax, fabsf(a));
+                    }
                 }
-                if (!warp_valid) amax = 0.0f;
                 sm->amax[tile_par][wq][row] = amax;
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&sm->amax_bar[tile_par]);
@@ -543,9 +539,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     uint32_t packed[AC / 4];
 #pragma unroll
                     for (int i = 0; i < AC / 4; i++) {
-                        float a0, a1, a2, a3;
-                        ptx::unpack_f32x2(acc2[2 * i], a0, a1);
-                        ptx::unpack_f32x2(acc2[2 * i + 1], a2, a3);
+                        const float a0 = accv[4 * i], a1 = accv[4 * i + 1], a2 = accv[4 * i + 2], a3 = accv[4 * i + 3];
                         packed[i] = (uint32_t)__nv_cvt_float_to_fp8(a0 * inv, __NV_SATFINITE, __NV_E4M3) |
                                     ((uint32_t)__nv_cvt_float_to_fp8(a1 * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
                                     ((uint32_t)__nv_cvt_float_to_fp8(a2 * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
@@ -576,10 +570,8 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
                     __syncwarp();
 #pragma unroll
                     for (int q = 0; q < SEGS; q++) {
-                        float v0, v1, v2, v3;
-                        ptx::unpack_f32x2(acc2[pass * (SW / 2) + 2 * q], v0, v1);
-                        ptx::unpack_f32x2(acc2[pass * (SW / 2) + 2 * q + 1], v2, v3);
-                        *reinterpret_cast<float4*>(&st[lane][q * 4]) = make_float4(w * v0, w * v1, w * v2, w * v3);
+                        const float* a4 = accv + pass * SW + q * 4;
+                        *reinterpret_cast<float4*>(&st[lane][q * 4]) = make_float4(w * a4[0], w * a4[1], w * a4[2], w * a4[3]);
                     }
                     __syncwarp();
 #pragma unroll
