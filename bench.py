@@ -246,6 +246,7 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     r1.record()
     torch.cuda.synchronize()
     route_ms = r0.elapsed_time(r1) / 5
+    route_flagged = b200.moe_route_last_flagged()       # tokens the tensor-core router handed to its exact pass
 
     b200.moe_fp8_profile(True)
     b200.launch_count(reset=True)
@@ -357,7 +358,7 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
                            "algorithmic_bytes": int(g2_bytes),
                            "note": "weights + requantised activations read, output written once; the fp32 "
                                    "scatter-add traffic (rows x D x 4 bytes) is implementation traffic"},
-        "roofline_routing": {"kernel": "gate_logits_fp8 + route_select", "bound": "hbm",
+        "roofline_routing": {"kernel": "router logits + selection (+ exact pass)", "bound": "hbm",
                              "achieved": route_bytes / (route_ms * 1e-3) / 1e9, "peak": hbm, "unit": "GB/s",
                              "frac": route_bytes / (route_ms * 1e-3) / 1e9 / hbm, "kernel_ms": route_ms,
                              "algorithmic_bytes": int(route_bytes)},
@@ -380,7 +381,10 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
                     "routing_hbm_gbs": (c["T"] * (c["D"] + 4 * c["D"] // 128) + 4 * c["E"] * c["D"] + 8 * c["T"] * c["K"])
                                        / (route_ms * 1e-3) / 1e9,
                     "routing_fp32_tflops": 2.0 * c["T"] * c["E"] * c["D"] / (route_ms * 1e-3) / 1e12,
-                    "routing_bound_note": "bit-reproducible fp32 FMA chains on the SIMT pipes, not HBM",
+                    "routing_exact_pass_tokens": route_flagged,
+                    "routing_note": "router logits on the tensor cores (tf32 split operands), ids certified by decision "
+                                    "margins, the listed number of tokens recomputed with the fixed-order FMA chains"
+                                    if route_flagged >= 0 else "fixed-order fp32 FMA chains on the SIMT pipes",
                     "active_experts": active,
                     "max_tokens_per_expert": int(counts.max()), "mean_tokens_per_expert": float(counts.mean())},
         "cpu_baseline": {"value": cpu["tokens"] / cpu["seconds"], "unit": "tokens/s", "cores": threads, "kind": "port",

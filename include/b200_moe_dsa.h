@@ -96,7 +96,13 @@ enum b200_moe_flags {
      * shape measured so far) or 256-row tiles on CTA pairs (tcgen05 cta_group::2; each SM stages half of a
      * weight tile).  Results agree up to the order of the scatter-add. */
     B200_MOE_SINGLE_CTA_TILES = 4,
-    B200_MOE_CTA_PAIR_TILES = 8
+    B200_MOE_CTA_PAIR_TILES = 8,
+    /* Router logits of grouped sigmoid routing.  By default batches of 256 or more tokens compute them on the
+     * tensor cores (tf32 split operands: approximate to a few 1e-6) and accept a token's routing only when all
+     * its decision margins are far larger than that error; the other tokens (a few per cent) are recomputed with
+     * the fixed-order FMA chains, so the expert ids are the same as with exact logits for every token, the
+     * weights agree to ~1e-6 relative.  This flag forces the exact chains for all tokens. */
+    B200_MOE_EXACT_ROUTER_LOGITS = 16
 };
 
 /* --------------------------------------------------------------------------- */

@@ -42,7 +42,8 @@ class MoeFp8Config(C.Structure):
 
 
 MOE_DETERMINISTIC = 1      # MoeFp8Config.flags: fixed-order (experts ascending) combine, bit-reproducible
-MOE_SINGLE_CTA_TILES, MOE_CTA_PAIR_TILES = 4, 8      # force the grouped GEMMs' tile shape (default: by size)
+MOE_SINGLE_CTA_TILES, MOE_CTA_PAIR_TILES = 4, 8      # force the grouped GEMMs' tile shape
+MOE_EXACT_ROUTER_LOGITS = 16                         # fixed-order FMA router logits for every token
 
 
 class EpConfig(C.Structure):
@@ -69,7 +70,8 @@ EXPORTED_SYMBOLS = [
     "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128",
 ]
 # exported for the test suite only (declared in csrc/selftest.h, not in the public header)
-TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest", "b200_ep_connect_loopback", "b200_fp8_mma_rate"]
+TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest", "b200_ep_connect_loopback", "b200_fp8_mma_rate",
+                     "b200_moe_gate_logits_tc", "b200_moe_route_last_flagged"]
 
 
 def lib():
@@ -375,6 +377,27 @@ def fp8_mma_rate(pair=False, iters=20000, stream=None):
     _check(lib().b200_fp8_mma_rate(1 if pair else 0, int(iters), C.byref(tf), C.byref(ms), _stream(stream)),
            "fp8_mma_rate")
     return tf.value, ms.value
+
+
+def moe_gate_logits_tc(xq, xs, gate_w, splits=0, stream=None):
+    """Test hook: the approximate router logits [T, E] of the tensor-core path (sum of its partial sums).
+    splits: number of partial sums along D (0 = the library's own choice; 1 = one accumulation chain over all of D,
+    which shows how the tensor core's accumulation error grows with the chain)."""
+    import torch
+    T, D = xq.shape
+    E = gate_w.shape[0]
+    parts = torch.zeros((max(int(splits), D // 128), T, E), dtype=torch.float32, device=xq.device)
+    n = C.c_int(int(splits))
+    _check(lib().b200_moe_gate_logits_tc(_p(xq), _p(xs), _p(gate_w), _p(parts), T, E, D, C.byref(n), _stream(stream)),
+           "moe_gate_logits_tc")
+    return parts[: n.value].sum(dim=0)
+
+
+def moe_route_last_flagged(stream=None, ws=None):
+    """Tokens the last tensor-core routing call handed to its exact pass (-1: the call took the exact path)."""
+    n = C.c_int(0)
+    _check(lib().b200_moe_route_last_flagged(C.c_void_p(ws), _stream(stream), C.byref(n)), "moe_route_last_flagged")
+    return n.value
 
 
 def wait_selftest(elapsed_ns, stream=None):

@@ -40,6 +40,7 @@ struct b200_ws {
     int sm_count = 0;
     size_t max_smem_optin = 0;
     b200_gemm_profile* gemm_prof = nullptr;
+    const int* route_flag_n = nullptr;    // device counter of the last tensor-core routing call (NULL: exact path)
 };
 
 b200_ws* b200_default_ws();                        // lazily created, one per device

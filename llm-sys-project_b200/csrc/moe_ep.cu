@@ -210,7 +210,8 @@ struct b200_ep {
     int *ids = nullptr, *hist = nullptr, *send_tok = nullptr, *pos = nullptr, *send_counts = nullptr, *slot_ids = nullptr;
     int *recv_counts = nullptr;
     unsigned int* done = nullptr;     // [2] block counters of the dispatch / push kernels
-    float *wts = nullptr, *slot_w = nullptr, *partials = nullptr, *y = nullptr;
+    float *wts = nullptr, *slot_w = nullptr, *y = nullptr;
+    RouteScratch route{};
     char** d_peer = nullptr;          // device copy of peer[]
     unsigned int step = 0;
     int sm_count = 0;
@@ -518,7 +519,15 @@ int b200_ep_create(b200_ep** out, const b200_ep_config* cfg, const int* owner_ma
         ep->slot_ids = c.take<int>(WT * K); ep->slot_w = c.take<float>(WT * K);
         ep->recv_counts = c.take<int>(64);
         ep->done = c.take<unsigned int>(2);
-        ep->partials = c.take<float>((size_t)nch * Tm * E);
+        {
+            const bool tc = moe_gate_tc_supported(Tm, E, D);
+            const int nparts = nch > moe_gate_tc_splits(D) ? nch : moe_gate_tc_splits(D);
+            ep->route.partials = c.take<float>((size_t)nparts * Tm * E);
+            ep->route.whi = tc ? c.take<float>((size_t)E * D) : nullptr;
+            ep->route.wlo = tc ? c.take<float>((size_t)E * D) : nullptr;
+            ep->route.flag_list = tc ? c.take<int>((size_t)Tm) : nullptr;
+            ep->route.flag_n = tc ? c.take<int>(1) : nullptr;
+        }
         ep->d_peer = c.take<char*>(64);
         ep->y = c.take<float>(WT * D);
     };
@@ -596,12 +605,13 @@ int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float*
     const bool half = !(c.flags & B200_EP_COMBINE_F32);
 
     // route (replicated router) and plan
-    const int nch = moe_gate_chunks(D, true);
-    int st = launch_gate_logits(xq, xs, gate_w, ep->partials, T, E, D, true, stream);
-    if (st) return st;
-    B200_CUDA_TRY(cudaMemsetAsync(ep->hist, 0, sizeof(int) * E, stream));
-    st = launch_route_select(ep->partials, nch, bias, ep->ids, ep->wts, ep->hist, nullptr, T, E, K, c.scoring,
-                             c.n_group, c.topk_group, c.routed_scale, stream);
+    b200_moe_fp8_config rc{};
+    rc.num_tokens = T; rc.num_experts = E; rc.top_k = K; rc.hidden_dim = D; rc.intermediate_dim = c.intermediate_dim;
+    rc.scoring = c.scoring; rc.n_group = c.n_group; rc.topk_group = c.topk_group; rc.routed_scale = c.routed_scale;
+    rc.flags = c.flags & B200_MOE_EXACT_ROUTER_LOGITS;
+    RouteScratch rs = ep->route;
+    if (!moe_gate_tc_supported(T, E, D)) rs.whi = nullptr;      // this step's batch is too small for the tensor-core router
+    int st = moe_route_fp8_run(rs, xq, xs, gate_w, bias, ep->ids, ep->wts, ep->hist, nullptr, &rc, ep->ws->d_status, stream);
     if (st) return st;
     st = b200_ep_plan(ep->ids, ep->wts, T, K, ep->E_local, W, 0, ep->d_owner, ep->d_local, ep->send_tok, ep->pos,
                       ep->send_counts, ep->slot_ids, ep->slot_w, stream);

@@ -698,7 +698,7 @@ __global__ void pack_weights_kernel(int which, const uint8_t* __restrict__ src, 
 bool g_regs_ok = true;
 
 struct Fp8Scratch {
-    float* partials; int* ids; float* wts; int* hist; int* counts; int* offsets; int* row_pair;
+    RouteScratch route; int* ids; float* wts; int* hist; int* counts; int* offsets; int* row_pair;
     uint8_t* sq; float* ss; int* row_tok; float* row_w; uint8_t* act_q; float* act_s;
     int* pair_row; float* rows;     // deterministic combine only
 };
@@ -707,7 +707,15 @@ void carve_fp8(WsCarver& c, const b200_moe_fp8_config* cfg, bool with_route, Fp8
     const size_t T = cfg->num_tokens, E = cfg->num_experts, K = cfg->top_k, D = cfg->hidden_dim,
                  I = cfg->intermediate_dim;
     const size_t TK = T * K;
-    s.partials = with_route ? c.take<float>((size_t)moe_gate_chunks((int)D, true) * T * E) : nullptr;
+    s.route = RouteScratch{};
+    if (with_route) {
+        const bool tc = moe_gate_tc_supported((int)T, (int)E, (int)D);
+        s.route.partials = c.take<float>((size_t)max(moe_gate_chunks((int)D, true), moe_gate_tc_splits((int)D)) * T * E);
+        s.route.whi = tc ? c.take<float>(E * D) : nullptr;
+        s.route.wlo = tc ? c.take<float>(E * D) : nullptr;
+        s.route.flag_list = tc ? c.take<int>(T) : nullptr;
+        s.route.flag_n = tc ? c.take<int>(1) : nullptr;
+    }
     s.ids = c.take<int>(TK);
     s.wts = c.take<float>(TK);
     s.hist = c.take<int>(E);
@@ -976,13 +984,10 @@ static int forward_impl(b200_ws* ws, const uint8_t* xq, const float* xs, const f
     if (st) return st;
     WsCarver cv(ws->base);
     carve_fp8(cv, cfg, true, s);
-    const int nch = moe_gate_chunks(D, true);
-    st = launch_gate_logits(xq, xs, gate_w, s.partials, T, E, D, true, stream);
+    st = moe_route_fp8_run(s.route, xq, xs, gate_w, bias, s.ids, s.wts, s.hist, nullptr, cfg, ws->d_status, stream);
     if (st) return st;
-    B200_CUDA_TRY(cudaMemsetAsync(s.hist, 0, sizeof(int) * E, stream));
-    st = launch_route_select(s.partials, nch, bias, s.ids, s.wts, s.hist, nullptr, T, E, K, cfg->scoring,
-                             cfg->n_group, cfg->topk_group, cfg->routed_scale, stream);
-    if (st) return st;
+    ws->route_flag_n = (s.route.whi && cfg->scoring == B200_SCORE_SIGMOID_GROUPED && !(cfg->flags & B200_MOE_EXACT_ROUTER_LOGITS))
+                           ? s.route.flag_n : nullptr;
     return run_experts(ws, s, xq, xs, s.ids, s.wts, s.hist, w1q, w1s, w2q, w2s, out, cfg, true, packed, stream);
 }
 

@@ -10,9 +10,42 @@ void b200_count_launch(int n);
 int moe_gate_chunks(int D, bool fp8);
 int launch_gate_logits(const void* x, const float* xs, const float* wg, float* partials, int T, int E, int D,
                        bool fp8, cudaStream_t stream);
+// Selection on approximate logits (tensor-core router): a token is accepted only if every decision margin (kept
+// vs dropped group scores, the order of the K selected selection scores, the K-th against the best unselected)
+// exceeds tau; the others are appended to flag_list (count in *flag_n) for the exact pass.  tau = 0: exact
+// logits, nothing is flagged.  list / list_n: the rows of `partials` are the tokens list[0 .. *list_n) (the exact
+// pass over the flagged tokens); results go to the tokens' own slots of ids / wts.
+struct RouteCert {
+    float tau = 0.0f;
+    int* flag_list = nullptr;
+    int* flag_n = nullptr;
+    const int* list = nullptr;
+    const int* list_n = nullptr;
+};
 int launch_route_select(const float* partials, int n_chunks, const float* bias, int* ids, float* wts, int* counts,
                         float* logits_out, int T, int E, int K, int scoring, int n_group, int topk_group,
-                        float routed_scale, cudaStream_t stream);
+                        float routed_scale, cudaStream_t stream, RouteCert cert = RouteCert());
+// Tensor-core router logits (moe_route_tc.cu): approximate, for the certified selection above.
+bool moe_gate_tc_supported(int T, int E, int D);
+int moe_gate_tc_splits(int D);
+int launch_gate_logits_tc(const uint8_t* xq, const float* xs, const float* wg, float* whi, float* wlo, float* partials,
+                          int T, int E, int D, int* status, cudaStream_t stream);
+// Exact router logits (the fixed-order FMA chains) for the tokens list[0 .. *list_n): partials[(chunk * T + i) * E + e]
+// for list entry i.
+int launch_gate_logits_list(const uint8_t* xq, const float* xs, const float* wg, float* partials, const int* list,
+                            const int* list_n, int T, int E, int D, cudaStream_t stream);
+// Whole routing step of the FP8 layer into caller-provided scratch; picks the tensor-core path when it applies.
+struct RouteScratch {
+    float* partials;     // max(moe_gate_chunks(D), splits) * T * E floats
+    float* whi;          // E * D floats (tensor-core path)
+    float* wlo;          // E * D floats
+    int* flag_list;      // T ints
+    int* flag_n;         // 1 int
+};
+size_t moe_route_scratch_floats(int T, int E, int D);
+int moe_route_fp8_run(const RouteScratch& rs, const uint8_t* xq, const float* xs, const float* gate_w, const float* bias,
+                      int* ids, float* wts, int* counts, float* logits_out, const b200_moe_fp8_config* cfg,
+                      int* status, cudaStream_t stream);
 // counts_in: the router's per-expert histogram (may be NULL: counted from ids).  trusted: ids come from
 // this library's router (an expert appears at most once per token), so the duplicate check is skipped.
 int launch_permute(const int* ids, int T, int K, int E, const int* counts_in, bool trusted, int* counts,

@@ -17,6 +17,7 @@
 
 #include "common.cuh"
 #include "moe_internal.cuh"
+#include "selftest.h"
 
 // ---------------------------------------------------------------------------
 // gate logits
@@ -162,22 +163,26 @@ __device__ __forceinline__ ValIdx warp_argmax(ValIdx x) {
     return x;
 }
 
-// smem per warp: E floats (scores s) + E floats (selection scores c)
-__global__ void __launch_bounds__(128)
-route_select_kernel(const float* __restrict__ partials, int n_chunks, const float* __restrict__ bias,
-                    int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
-                    float* __restrict__ logits_out, int T, int E, int K, int scoring, int n_group,
-                    int topk_group, float routed_scale) {
-    extern __shared__ float sm[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= T) return;
-    float* s = sm + (size_t)warp * 2 * E;
-    float* c = s + E;
-
+// One token's selection, executed by one warp.  s / c: E floats each of this warp's shared memory.
+__device__ __forceinline__ void
+route_select_row(const float* __restrict__ partials, int n_chunks, const float* __restrict__ bias,
+                 int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
+                 float* __restrict__ logits_out, int T, int E, int K, int scoring, int n_group,
+                 int topk_group, float routed_scale, const RouteCert& cert, int row, int t, float* s, float* c,
+                 int lane) {
+    // logit = the partial sums added in chunk order; the loads of eight chunks are issued together so that their
+    // latencies overlap (the adds stay in order)
     for (int e = lane; e < E; e += 32) {
-        float l = partials[(size_t)t * E + e];
-        for (int ch = 1; ch < n_chunks; ch++) l = __fadd_rn(l, partials[((size_t)ch * T + t) * E + e]);
+        float l = 0.0f;
+        for (int ch0 = 0; ch0 < n_chunks; ch0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                v[j] = (ch0 + j < n_chunks) ? __ldg(&partials[((size_t)(ch0 + j) * T + row) * E + e]) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (ch0 + j < n_chunks) l = (ch0 + j == 0) ? v[j] : __fadd_rn(l, v[j]);
+        }
         s[e] = l;
         if (logits_out) logits_out[(size_t)t * E + e] = l;
     }
@@ -218,8 +223,21 @@ route_select_kernel(const float* __restrict__ partials, int n_chunks, const floa
     }
 
     // ---- sigmoid + bias, group-limited top-K ---------------------------------
+    // Certification threshold of this token: the tensor core's summation error grows with the size of the sums,
+    // so the threshold scales with the root mean square of the token's logits (never below the base value).
+    float tau = cert.tau;
+    if (cert.tau > 0.0f) {
+        float ss = 0.0f;
+        for (int e = lane; e < E; e += 32) ss = fmaf(s[e], s[e], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        tau *= fmaxf(1.0f, sqrtf(ss / (float)E));
+    }
     for (int e = lane; e < E; e += 32) {
-        float sg = (float)(1.0 / (1.0 + exp(-(double)s[e])));
+        // exact logits: correctly rounded sigmoid; approximate logits: the fp32 formula (its error, about 1e-7,
+        // is far below the threshold that sends a token to the exact pass)
+        float sg = (cert.tau > 0.0f) ? __fdividef(1.0f, 1.0f + __expf(-s[e]))
+                                     : (float)(1.0 / (1.0 + exp(-(double)s[e])));
         s[e] = sg;
         c[e] = __fadd_rn(sg, bias ? bias[e] : 0.0f);
     }
@@ -250,16 +268,36 @@ route_select_kernel(const float* __restrict__ partials, int n_chunks, const floa
         keep_mask |= 1u << cand.i;
         if (lane == cand.i) mine_taken = true;
     }
+    // Certification (approximate logits only): the smallest gap between the kept and the dropped group scores.
+    // A group score is the sum of two selection scores, so its error is twice theirs.
+    float min_margin = FLT_MAX;
+    if (cert.tau > 0.0f && topk_group < n_group) {
+        float kept = (lane < n_group && ((keep_mask >> lane) & 1u)) ? my_gscore : FLT_MAX;
+        float dropped = (lane < n_group && !((keep_mask >> lane) & 1u)) ? my_gscore : -FLT_MAX;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            kept = fminf(kept, __shfl_xor_sync(0xffffffffu, kept, o));
+            dropped = fmaxf(dropped, __shfl_xor_sync(0xffffffffu, dropped, o));
+        }
+        min_margin = 0.5f * (kept - dropped);
+    }
     // top-K experts among kept groups.  Taken experts get c = -inf marker via NaN-free flag array:
     // reuse the sign of s? Keep a separate taken bit by setting c[e] to -FLT_MAX after selection.
     float sum = 0.0f;
     float my_w = 0.0f;      // lane k keeps slot k's unnormalised weight (K <= 32)
     int my_id = -1;
-    for (int k = 0; k < K; k++) {
+    float prev_v = FLT_MAX;
+    const int rounds = (cert.tau > 0.0f) ? K + 1 : K;       // one more round: the best expert that is NOT selected
+    for (int k = 0; k < rounds; k++) {
         ValIdx b = {0.0f, -1};
         for (int e = lane; e < E; e += 32)
             if (((keep_mask >> (e / gs)) & 1u) && c[e] != -FLT_MAX) b = better(b, ValIdx{c[e], e});
         b = warp_argmax(b);
+        if (cert.tau > 0.0f && b.i >= 0) {
+            if (k > 0) min_margin = fminf(min_margin, prev_v - b.v);     // order of the selected, and K-th vs (K+1)-th
+            prev_v = b.v;
+        }
+        if (k == K) break;
         float sv = (b.i >= 0) ? s[b.i] : 0.0f;
         __syncwarp();
         if (lane == 0 && b.i >= 0) c[b.i] = -FLT_MAX;
@@ -267,10 +305,198 @@ route_select_kernel(const float* __restrict__ partials, int n_chunks, const floa
         sum = __fadd_rn(sum, sv);
         if (lane == k) { my_w = sv; my_id = b.i; }
     }
+    // A token whose decisions are not certain at the approximation's accuracy goes on the list of the exact pass
+    // (which overwrites its ids / weights and counts it in the histogram).
+    const bool uncertain = cert.tau > 0.0f && !(min_margin > tau);
+    if (uncertain && lane == 0) cert.flag_list[atomicAdd(cert.flag_n, 1)] = t;
     if (lane < K) {
         oi[lane] = my_id;
         ow[lane] = __fmul_rn(__fdiv_rn(my_w, sum), routed_scale);
-        if (counts && my_id >= 0) atomicAdd(&counts[my_id], 1);
+        if (counts && my_id >= 0 && !uncertain) atomicAdd(&counts[my_id], 1);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Grouped sigmoid selection with the token's scores in registers: lane L holds the PER = E / 32 experts
+// L * PER .. L * PER + PER - 1, a group is a run of LPG = (E / n_group) / PER lanes (a power of two).  Same
+// decisions and the same arithmetic as route_select_row, several times fewer instructions: the group scores of
+// all groups are formed at once by a butterfly over each group's lanes, the kept groups by ranking.
+// ---------------------------------------------------------------------------
+template <int PER>
+__device__ __forceinline__ void load_run(const float* p, float* v) {
+    if constexpr (PER % 4 == 0) {
+#pragma unroll
+        for (int j = 0; j < PER; j += 4) {
+            const float4 x = __ldg(reinterpret_cast<const float4*>(p + j));
+            v[j] = x.x; v[j + 1] = x.y; v[j + 2] = x.z; v[j + 3] = x.w;
+        }
+    } else if constexpr (PER == 2) {
+        const float2 x = __ldg(reinterpret_cast<const float2*>(p));
+        v[0] = x.x; v[1] = x.y;
+    } else {
+#pragma unroll
+        for (int j = 0; j < PER; j++) v[j] = __ldg(p + j);
+    }
+}
+
+template <int PER>
+__device__ __forceinline__ void
+route_select_row_regs(const float* __restrict__ partials, int n_chunks, const float* __restrict__ bias,
+                      int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
+                      float* __restrict__ logits_out, int T, int E, int K, int n_group, int topk_group,
+                      float routed_scale, const RouteCert& cert, int row, int t, int lane) {
+    const int e_lo = lane * PER;
+    float lg[PER];
+    // logit = the partial sums added in chunk order (loads of four chunks in flight, adds in order)
+    for (int ch0 = 0; ch0 < n_chunks; ch0 += 4) {
+        float v[4][PER];
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (ch0 + i < n_chunks) load_run<PER>(partials + ((size_t)(ch0 + i) * T + row) * E + e_lo, v[i]);
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            if (ch0 + i < n_chunks) {
+#pragma unroll
+                for (int j = 0; j < PER; j++) lg[j] = (ch0 + i == 0) ? v[i][j] : __fadd_rn(lg[j], v[i][j]);
+            }
+    }
+    if (logits_out) {
+#pragma unroll
+        for (int j = 0; j < PER; j++) logits_out[(size_t)t * E + e_lo + j] = lg[j];
+    }
+    float tau = cert.tau;
+    if (cert.tau > 0.0f) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PER; j++) ss = fmaf(lg[j], lg[j], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        tau *= fmaxf(1.0f, sqrtf(ss / (float)E));
+    }
+    float sg[PER], c[PER];
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        sg[j] = (cert.tau > 0.0f) ? __fdividef(1.0f, 1.0f + __expf(-lg[j]))
+                                  : (float)(1.0 / (1.0 + exp(-(double)lg[j])));
+        c[j] = __fadd_rn(sg[j], bias ? bias[e_lo + j] : 0.0f);
+    }
+    // ---- group scores: best two selection scores of every group ----
+    const int gs = E / n_group, lpg = gs / PER, g = lane / lpg;
+    ValIdx b1 = {0.0f, -1}, b2 = {0.0f, -1};
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const ValIdx v = {c[j], e_lo + j};
+        const ValIdx top = better(b1, v);
+        b2 = (top.i == v.i) ? b1 : better(b2, v);
+        b1 = top;
+    }
+    for (int o = 1; o < lpg; o <<= 1) {
+        ValIdx o1, o2;
+        o1.v = __shfl_xor_sync(0xffffffffu, b1.v, o); o1.i = __shfl_xor_sync(0xffffffffu, b1.i, o);
+        o2.v = __shfl_xor_sync(0xffffffffu, b2.v, o); o2.i = __shfl_xor_sync(0xffffffffu, b2.i, o);
+        const ValIdx top = better(b1, o1);
+        b2 = (top.i == b1.i) ? better(b2, o1) : better(b1, o2);
+        b1 = top;
+    }
+    const float gscore = (gs > 1) ? __fadd_rn(b1.v, b2.v) : b1.v;
+    // ---- kept groups: group g stays if fewer than topk_group groups beat it (ties: the lower group wins) ----
+    int beaten_by = 0;
+    for (int h = 0; h < n_group; h++) {
+        const float sh = __shfl_sync(0xffffffffu, gscore, h * lpg);
+        beaten_by += (sh > gscore || (sh == gscore && h < g)) ? 1 : 0;
+    }
+    const bool keep = beaten_by < topk_group;
+    float min_margin = FLT_MAX;
+    if (cert.tau > 0.0f && topk_group < n_group) {
+        float kept = keep ? gscore : FLT_MAX, dropped = keep ? -FLT_MAX : gscore;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            kept = fminf(kept, __shfl_xor_sync(0xffffffffu, kept, o));
+            dropped = fmaxf(dropped, __shfl_xor_sync(0xffffffffu, dropped, o));
+        }
+        min_margin = 0.5f * (kept - dropped);
+    }
+    // ---- top-K experts among the kept groups, best first ----
+    unsigned taken = keep ? 0u : 0xffffffffu;
+    float sum = 0.0f, my_w = 0.0f, prev_v = FLT_MAX;
+    int my_id = -1;
+    const int rounds = (cert.tau > 0.0f) ? K + 1 : K;       // one more round: the best expert that is NOT selected
+    for (int k = 0; k < rounds; k++) {
+        ValIdx b = {0.0f, -1};
+#pragma unroll
+        for (int j = 0; j < PER; j++)
+            if (!((taken >> j) & 1u)) b = better(b, ValIdx{c[j], e_lo + j});
+        b = warp_argmax(b);
+        if (cert.tau > 0.0f && b.i >= 0) {
+            if (k > 0) min_margin = fminf(min_margin, prev_v - b.v);
+            prev_v = b.v;
+        }
+        if (k == K) break;
+        const int owner = (b.i >= 0) ? b.i / PER : 0, slot = (b.i >= 0) ? b.i % PER : 0;
+        float mine = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PER; j++) mine = (j == slot) ? sg[j] : mine;
+        float sv = __shfl_sync(0xffffffffu, mine, owner);
+        if (b.i < 0) sv = 0.0f;
+        if (b.i >= 0 && lane == owner) taken |= 1u << slot;
+        sum = __fadd_rn(sum, sv);
+        if (lane == k) { my_w = sv; my_id = b.i; }
+    }
+    const bool uncertain = cert.tau > 0.0f && !(min_margin > tau);
+    if (uncertain && lane == 0) cert.flag_list[atomicAdd(cert.flag_n, 1)] = t;
+    if (lane < K) {
+        ids[(size_t)t * K + lane] = my_id;
+        wts[(size_t)t * K + lane] = __fmul_rn(__fdiv_rn(my_w, sum), routed_scale);
+        if (counts && my_id >= 0 && !uncertain) atomicAdd(&counts[my_id], 1);
+    }
+}
+
+// The register path serves: E = 32 * PER with PER in {2, 4, 8}, groups that are whole runs of lanes
+// (power-of-two many), K <= 32.
+__host__ __device__ inline int route_regs_per(int E, int K, int scoring, int n_group) {
+    if (scoring != B200_SCORE_SIGMOID_GROUPED || E % 32 || K > 32 || n_group < 1 || n_group > 32 || E % n_group) return 0;
+    const int per = E / 32, gs = E / n_group;
+    if (per != 2 && per != 4 && per != 8) return 0;
+    if (gs % per) return 0;
+    const int lpg = gs / per;
+    if (lpg & (lpg - 1)) return 0;
+    return per;
+}
+
+// smem per warp: E floats (scores s) + E floats (selection scores c).  One warp per row of `partials`, rows
+// taken with the grid's stride.  List mode (cert.list): the rows are the tokens of cert.list, in list order, and
+// only the first *cert.list_n rows exist (a count known only on the device).
+__global__ void __launch_bounds__(128)
+route_select_kernel(const float* __restrict__ partials, int n_chunks, const float* __restrict__ bias,
+                    int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
+                    float* __restrict__ logits_out, int T, int E, int K, int scoring, int n_group,
+                    int topk_group, float routed_scale, RouteCert cert) {
+    extern __shared__ float sm[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* s = sm + (size_t)warp * 2 * E;
+    float* c = s + E;
+    const int rows = cert.list ? min(*cert.list_n, T) : T;
+    const int per = route_regs_per(E, K, scoring, n_group);
+    for (int row = blockIdx.x * 4 + warp; row < rows; row += gridDim.x * 4) {
+        const int t = cert.list ? cert.list[row] : row;
+        if (per == 8) {
+            route_select_row_regs<8>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, n_group, topk_group,
+                                     routed_scale, cert, row, t, lane);
+            continue;
+        }
+        if (per == 4) {
+            route_select_row_regs<4>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, n_group, topk_group,
+                                     routed_scale, cert, row, t, lane);
+            continue;
+        }
+        if (per == 2) {
+            route_select_row_regs<2>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, n_group, topk_group,
+                                     routed_scale, cert, row, t, lane);
+            continue;
+        }
+        route_select_row(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, scoring, n_group,
+                         topk_group, routed_scale, cert, row, t, s, c, lane);
+        __syncwarp();
     }
 }
 
@@ -538,6 +764,90 @@ gate_logits_fp8_small_kernel(const uint8_t* __restrict__ xq, const float* __rest
     }
 }
 
+// The same chains for a list of tokens (the exact pass of the tensor-core router).  Block = 64 threads = 32
+// experts x 8 list entries per round x one chunk of d; thread = one expert x four entries, so that one 16-byte
+// read of the expert's weights serves sixteen multiply-adds (the entries' activations are warp-wide broadcasts).
+// k-tiles of 128 d: the next tile is fetched into registers while the current one is multiplied.  A bounded
+// grid walks the list, whose length is known only on the device.
+constexpr int GL2_E = 32, GL2_K = 128, GL2_T = 8, GL2_LDW = GL2_K + 4, GL2_THREADS = 64;
+__global__ void __launch_bounds__(GL2_THREADS)
+gate_logits_fp8_list_kernel(const uint8_t* __restrict__ xq, const float* __restrict__ xs, const float* __restrict__ wg,
+                            float* __restrict__ partials, const int* __restrict__ list, const int* __restrict__ list_n,
+                            int T, int E, int D, int chunk) {
+    __shared__ __align__(16) float w_s[GL2_E][GL2_LDW];
+    __shared__ __align__(16) float x_s[GL2_T][GL2_K];
+    __shared__ int tok_s[GL2_T];
+    const int n = min(*list_n, T);
+    const int e0 = blockIdx.x * GL2_E, c = blockIdx.y;
+    const int d_begin = c * chunk, d_end = min(D, d_begin + chunk);      // multiples of 128 (D % 128 == 0)
+    const int el = threadIdx.x & 31, tg = threadIdx.x >> 5;
+    const int nb = D / 128;
+    constexpr int WREP = GL2_E * GL2_K / 4 / GL2_THREADS;                 // 16 float4 of the weight tile per thread
+    const int xr = threadIdx.x >> 3, xp = threadIdx.x & 7;               // activation tile: entry xr, bytes 16*xp..
+    for (int i0 = blockIdx.z * GL2_T; i0 < n; i0 += gridDim.z * GL2_T) {
+        __syncthreads();
+        if (threadIdx.x < GL2_T) tok_s[threadIdx.x] = (i0 + threadIdx.x < n) ? list[i0 + threadIdx.x] : -1;
+        __syncthreads();
+        const int xt = tok_s[xr];
+        const bool x_live = xt >= 0 && xt < T;
+        float4 w_reg[WREP];
+        uint4 x_raw = make_uint4(0, 0, 0, 0);
+        float x_sc = 0.0f;
+        auto fetch = [&](int d0) {
+#pragma unroll
+            for (int rep = 0; rep < WREP; rep++) {
+                const int idx = threadIdx.x + rep * GL2_THREADS, r = idx >> 5, kq = (idx & 31) * 4;
+                w_reg[rep] = (e0 + r < E) ? __ldg(reinterpret_cast<const float4*>(wg + (size_t)(e0 + r) * D + d0 + kq))
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            if (x_live) {
+                x_raw = __ldg(reinterpret_cast<const uint4*>(xq + (size_t)xt * D + d0 + xp * 16));
+                x_sc = xs[(size_t)xt * nb + d0 / 128];
+            }
+        };
+        auto stage = [&]() {
+#pragma unroll
+            for (int rep = 0; rep < WREP; rep++) {
+                const int idx = threadIdx.x + rep * GL2_THREADS, r = idx >> 5, kq = (idx & 31) * 4;
+                *reinterpret_cast<float4*>(&w_s[r][kq]) = w_reg[rep];
+            }
+            const uint8_t* b = reinterpret_cast<const uint8_t*>(&x_raw);
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                __nv_fp8_e4m3 q;
+                q.__x = b[i];
+                x_s[xr][xp * 16 + i] = x_live ? __fmul_rn(float(q), x_sc) : 0.0f;
+            }
+        };
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        fetch(d_begin);
+        for (int d0 = d_begin; d0 < d_end; d0 += GL2_K) {
+            __syncthreads();                      // the previous tile has been read
+            stage();
+            __syncthreads();
+            if (d0 + GL2_K < d_end) fetch(d0 + GL2_K);
+#pragma unroll 8
+            for (int k = 0; k < GL2_K; k += 4) {
+                const float4 w4 = *reinterpret_cast<const float4*>(&w_s[el][k]);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float4 x4 = *reinterpret_cast<const float4*>(&x_s[tg * 4 + i][k]);
+                    acc[i] = __fmaf_rn(x4.x, w4.x, acc[i]);
+                    acc[i] = __fmaf_rn(x4.y, w4.y, acc[i]);
+                    acc[i] = __fmaf_rn(x4.z, w4.z, acc[i]);
+                    acc[i] = __fmaf_rn(x4.w, w4.w, acc[i]);
+                }
+            }
+        }
+        const int e = e0 + el;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int li = i0 + tg * 4 + i;
+            if (li < n && e < E) partials[((size_t)c * T + li) * E + e] = acc[i];
+        }
+    }
+}
+
 template <int TY>
 static int gate_fp8_try(int want_ty, int& blocks_per_sm) {
     if (want_ty != TY) return 0;
@@ -625,20 +935,83 @@ int launch_gate_logits(const void* x, const float* xs, const float* wg, float* p
     return B200_OK;
 }
 
+int launch_gate_logits_list(const uint8_t* xq, const float* xs, const float* wg, float* partials, const int* list,
+                            const int* list_n, int T, int E, int D, cudaStream_t stream) {
+    if (D % 128) return B200_BAD_SHAPE;
+    if ((reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wg) & 15)) return B200_BAD_ARG;
+    dim3 grid(ceil_div(E, GL2_E), moe_gate_chunks(D, true), min(ceil_div(T, GL2_T), 32));
+    gate_logits_fp8_list_kernel<<<grid, GL2_THREADS, 0, stream>>>(xq, xs, wg, partials, list, list_n, T, E, D, MOE_GATE_CHUNK);
+    b200_count_launch(1);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
+}
+
 int launch_route_select(const float* partials, int n_chunks, const float* bias, int* ids, float* wts, int* counts,
                         float* logits_out, int T, int E, int K, int scoring, int n_group, int topk_group,
-                        float routed_scale, cudaStream_t stream) {
+                        float routed_scale, cudaStream_t stream, RouteCert cert) {
     size_t smem = (size_t)4 * 2 * E * sizeof(float);
     if (smem > 48 * 1024) {
         B200_CUDA_TRY(cudaFuncSetAttribute(route_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)smem));
     }
-    route_select_kernel<<<ceil_div(T, 4), 128, smem, stream>>>(partials, n_chunks, bias, ids, wts, counts,
+    // list mode: the length of the list is known only on the device; a modest grid walks it with a stride
+    const int blocks = cert.list ? min(ceil_div(T, 4), 4 * 148) : ceil_div(T, 4);
+    route_select_kernel<<<blocks, 128, smem, stream>>>(partials, n_chunks, bias, ids, wts, counts,
                                                               logits_out, T, E, K, scoring, n_group, topk_group,
-                                                              routed_scale);
+                                                              routed_scale, cert);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
+}
+
+// Minimum decision margin (in selection-score units) a token must show on the approximate logits.  The tensor
+// core adds each product into its fp32 accumulator with truncation, so the error of a logit grows with the length
+// of the accumulation chain: with chains of four 128-deep blocks (moe_gate_tc_splits) and unit-variance logits the
+// largest |approximate - exact| measured on the full-size router is 2.1e-5 (a single chain over D = 7168: 2.4e-4).
+// Assumed bound: 2^-14 = 6.1e-5 per unit of logit rms.  A selection score moves by at most a quarter of the logit
+// error (sigmoid), so two scores can close in on each other by 2 * 2^-14 / 4 = 3.05e-5; a token whose smallest
+// decision margin is not above that is recomputed exactly.  tests/test_moe_router_tc_gpu.py holds the measured
+// error below half of the assumed bound.
+constexpr float ROUTE_TC_TAU = 3.06e-5f;
+
+size_t moe_route_scratch_floats(int T, int E, int D) {
+    const size_t nch = (size_t)max(moe_gate_chunks(D, true), moe_gate_tc_splits(D));
+    size_t n = nch * T * E;                              // partials
+    if (moe_gate_tc_supported(T, E, D)) n += 2 * (size_t)E * D + (size_t)T + 64;      // whi, wlo, flag list, counter
+    return n + 256;
+}
+
+int moe_route_fp8_run(const RouteScratch& rs, const uint8_t* xq, const float* xs, const float* gate_w, const float* bias,
+                      int* ids, float* wts, int* counts, float* logits_out, const b200_moe_fp8_config* cfg,
+                      int* status, cudaStream_t stream) {
+    const int T = cfg->num_tokens, E = cfg->num_experts, K = cfg->top_k, D = cfg->hidden_dim;
+    if (counts) B200_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * E, stream));
+    const int nch = moe_gate_chunks(D, true);
+    // Tensor-core path: grouped sigmoid routing, no logits requested (the logits it computes are approximate),
+    // a batch large enough to fill 128-token tiles
+    const bool tc = rs.whi && !logits_out && cfg->scoring == B200_SCORE_SIGMOID_GROUPED && !(cfg->flags & B200_MOE_EXACT_ROUTER_LOGITS) &&
+                    moe_gate_tc_supported(T, E, D) && !((reinterpret_cast<uintptr_t>(xq) | reinterpret_cast<uintptr_t>(gate_w)) & 15);
+    if (!tc) {
+        int st = launch_gate_logits(xq, xs, gate_w, rs.partials, T, E, D, true, stream);
+        if (st) return st;
+        return launch_route_select(rs.partials, nch, bias, ids, wts, counts, logits_out, T, E, K, cfg->scoring,
+                                   cfg->n_group, cfg->topk_group, cfg->routed_scale, stream);
+    }
+    B200_CUDA_TRY(cudaMemsetAsync(rs.flag_n, 0, sizeof(int), stream));
+    int st = launch_gate_logits_tc(xq, xs, gate_w, rs.whi, rs.wlo, rs.partials, T, E, D, status, stream);
+    if (st) return st;
+    RouteCert approx;
+    approx.tau = ROUTE_TC_TAU; approx.flag_list = rs.flag_list; approx.flag_n = rs.flag_n;
+    st = launch_route_select(rs.partials, moe_gate_tc_splits(D), bias, ids, wts, counts, nullptr, T, E, K, cfg->scoring,
+                             cfg->n_group, cfg->topk_group, cfg->routed_scale, stream, approx);
+    if (st) return st;
+    // exact pass over the flagged tokens (usually a few per cent): the fixed-order chains, then the same selection
+    st = launch_gate_logits_list(xq, xs, gate_w, rs.partials, rs.flag_list, rs.flag_n, T, E, D, stream);
+    if (st) return st;
+    RouteCert exact;
+    exact.list = rs.flag_list; exact.list_n = rs.flag_n;
+    return launch_route_select(rs.partials, nch, bias, ids, wts, counts, nullptr, T, E, K, cfg->scoring, cfg->n_group,
+                               cfg->topk_group, cfg->routed_scale, stream, exact);
 }
 
 int launch_permute(const int* ids, int T, int K, int E, const int* counts_in, bool trusted, int* counts,
@@ -707,18 +1080,38 @@ int b200_moe_route_fp8(b200_ws* ws, const uint8_t* xq, const float* xs, const fl
     if (D % 128) return B200_BAD_SHAPE;
     if (!ws) ws = b200_default_ws();
     if (!ws) return B200_CUDA_ERROR;
-    const int nch = moe_gate_chunks(D, true);
+    auto carve = [&](WsCarver& c, RouteScratch& rs) {
+        const bool tc = moe_gate_tc_supported(T, E, D);
+        rs.partials = c.take<float>((size_t)max(moe_gate_chunks(D, true), moe_gate_tc_splits(D)) * T * E);
+        rs.whi = tc ? c.take<float>((size_t)E * D) : nullptr;
+        rs.wlo = tc ? c.take<float>((size_t)E * D) : nullptr;
+        rs.flag_list = tc ? c.take<int>((size_t)T) : nullptr;
+        rs.flag_n = tc ? c.take<int>(1) : nullptr;
+    };
+    RouteScratch rs;
     WsCarver sz(nullptr);
-    sz.take<float>((size_t)nch * T * E);
+    carve(sz, rs);
     st = b200_ws_ensure(ws, sz.total());
     if (st) return st;
     WsCarver cv(ws->base);
-    float* partials = cv.take<float>((size_t)nch * T * E);
-    if (counts) B200_CUDA_TRY(cudaMemsetAsync(counts, 0, sizeof(int) * E, stream));
-    st = launch_gate_logits(xq, xs, gate_w, partials, T, E, D, true, stream);
-    if (st) return st;
-    return launch_route_select(partials, nch, bias, expert_ids, expert_w, counts, logits_out, T, E, K, cfg->scoring,
-                               cfg->n_group, cfg->topk_group, cfg->routed_scale, stream);
+    carve(cv, rs);
+    ws->route_flag_n = nullptr;
+    st = moe_route_fp8_run(rs, xq, xs, gate_w, bias, expert_ids, expert_w, counts, logits_out, cfg, ws->d_status, stream);
+    if (st == B200_OK && rs.whi && !logits_out && cfg->scoring == B200_SCORE_SIGMOID_GROUPED &&
+        !(cfg->flags & B200_MOE_EXACT_ROUTER_LOGITS))
+        ws->route_flag_n = rs.flag_n;
+    return st;
+}
+
+int b200_moe_route_last_flagged(b200_ws* ws, b200_stream_t stream, int* n) {
+    if (!n) return B200_BAD_ARG;
+    if (!ws) ws = b200_default_ws();
+    if (!ws) return B200_CUDA_ERROR;
+    *n = -1;
+    if (!ws->route_flag_n) return B200_OK;
+    B200_CUDA_TRY(cudaStreamSynchronize(stream));
+    B200_CUDA_TRY(cudaMemcpy(n, ws->route_flag_n, sizeof(int), cudaMemcpyDeviceToHost));
+    return B200_OK;
 }
 
 int b200_moe_permute(b200_ws*, const int* expert_ids, int T, int K, int E, int* counts, int* offsets,
