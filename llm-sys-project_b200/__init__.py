@@ -379,18 +379,17 @@ def fp8_mma_rate(pair=False, iters=20000, stream=None):
     return tf.value, ms.value
 
 
-def moe_gate_logits_tc(xq, xs, gate_w, splits=0, stream=None):
-    """Test hook: the approximate router logits [T, E] of the tensor-core path (sum of its partial sums).
-    splits: number of partial sums along D (0 = the library's own choice; 1 = one accumulation chain over all of D,
-    which shows how the tensor core's accumulation error grows with the chain)."""
+def moe_gate_logits_tc(xq, xs, gate_w, chain_blocks=0, stream=None):
+    """Test hook: the approximate router logits [T, E] of the tensor-core path.
+    chain_blocks: length of the accumulation chains in 128-deep blocks of d (0 = the library's own choice;
+    D // 128 = one chain over all of d, which shows how the tensor core's accumulation error grows with the chain)."""
     import torch
     T, D = xq.shape
     E = gate_w.shape[0]
-    parts = torch.zeros((max(int(splits), D // 128), T, E), dtype=torch.float32, device=xq.device)
-    n = C.c_int(int(splits))
-    _check(lib().b200_moe_gate_logits_tc(_p(xq), _p(xs), _p(gate_w), _p(parts), T, E, D, C.byref(n), _stream(stream)),
-           "moe_gate_logits_tc")
-    return parts[: n.value].sum(dim=0)
+    logits = torch.empty((T, E), dtype=torch.float32, device=xq.device)
+    _check(lib().b200_moe_gate_logits_tc(_p(xq), _p(xs), _p(gate_w), _p(logits), T, E, D, int(chain_blocks),
+                                         _stream(stream)), "moe_gate_logits_tc")
+    return logits
 
 
 def moe_route_last_flagged(stream=None, ws=None):

@@ -521,7 +521,7 @@ int b200_ep_create(b200_ep** out, const b200_ep_config* cfg, const int* owner_ma
         ep->done = c.take<unsigned int>(2);
         {
             const bool tc = moe_gate_tc_supported(Tm, E, D);
-            const int nparts = nch > moe_gate_tc_splits(D) ? nch : moe_gate_tc_splits(D);
+            const int nparts = nch > moe_gate_tc_slots(D) ? nch : moe_gate_tc_slots(D);
             ep->route.partials = c.take<float>((size_t)nparts * Tm * E);
             ep->route.whi = tc ? c.take<float>((size_t)E * D) : nullptr;
             ep->route.wlo = tc ? c.take<float>((size_t)E * D) : nullptr;

@@ -710,7 +710,7 @@ void carve_fp8(WsCarver& c, const b200_moe_fp8_config* cfg, bool with_route, Fp8
     s.route = RouteScratch{};
     if (with_route) {
         const bool tc = moe_gate_tc_supported((int)T, (int)E, (int)D);
-        s.route.partials = c.take<float>((size_t)max(moe_gate_chunks((int)D, true), moe_gate_tc_splits((int)D)) * T * E);
+        s.route.partials = c.take<float>((size_t)max(moe_gate_chunks((int)D, true), moe_gate_tc_slots((int)D)) * T * E);
         s.route.whi = tc ? c.take<float>(E * D) : nullptr;
         s.route.wlo = tc ? c.take<float>(E * D) : nullptr;
         s.route.flag_list = tc ? c.take<int>(T) : nullptr;

@@ -172,6 +172,7 @@ route_select_row(const float* __restrict__ partials, int n_chunks, const float* 
                  int lane) {
     // logit = the partial sums added in chunk order; the loads of eight chunks are issued together so that their
     // latencies overlap (the adds stay in order)
+    if (cert.plan.L > 0) n_chunks = tc_slots_before(cert.plan, row / 128, (row / 128 + 1) * cert.plan.nblk);
     for (int e = lane; e < E; e += 32) {
         float l = 0.0f;
         for (int ch0 = 0; ch0 < n_chunks; ch0 += 8) {
@@ -346,6 +347,7 @@ route_select_row_regs(const float* __restrict__ partials, int n_chunks, const fl
                       float* __restrict__ logits_out, int T, int E, int K, int n_group, int topk_group,
                       float routed_scale, const RouteCert& cert, int row, int t, int lane) {
     const int e_lo = lane * PER;
+    if (cert.plan.L > 0) n_chunks = tc_slots_before(cert.plan, row / 128, (row / 128 + 1) * cert.plan.nblk);
     float lg[PER];
     // logit = the partial sums added in chunk order (loads of four chunks in flight, adds in order)
     for (int ch0 = 0; ch0 < n_chunks; ch0 += 4) {
@@ -966,7 +968,7 @@ int launch_route_select(const float* partials, int n_chunks, const float* bias, 
 
 // Minimum decision margin (in selection-score units) a token must show on the approximate logits.  The tensor
 // core adds each product into its fp32 accumulator with truncation, so the error of a logit grows with the length
-// of the accumulation chain: with chains of four 128-deep blocks (moe_gate_tc_splits) and unit-variance logits the
+// of the accumulation chain: with chains of at most four 128-deep blocks (moe_route_tc.cu) and unit-variance logits the
 // largest |approximate - exact| measured on the full-size router is 2.1e-5 (a single chain over D = 7168: 2.4e-4).
 // Assumed bound: 2^-14 = 6.1e-5 per unit of logit rms.  A selection score moves by at most a quarter of the logit
 // error (sigmoid), so two scores can close in on each other by 2 * 2^-14 / 4 = 3.05e-5; a token whose smallest
@@ -975,7 +977,7 @@ int launch_route_select(const float* partials, int n_chunks, const float* bias, 
 constexpr float ROUTE_TC_TAU = 3.06e-5f;
 
 size_t moe_route_scratch_floats(int T, int E, int D) {
-    const size_t nch = (size_t)max(moe_gate_chunks(D, true), moe_gate_tc_splits(D));
+    const size_t nch = (size_t)max(moe_gate_chunks(D, true), moe_gate_tc_slots(D));
     size_t n = nch * T * E;                              // partials
     if (moe_gate_tc_supported(T, E, D)) n += 2 * (size_t)E * D + (size_t)T + 64;      // whi, wlo, flag list, counter
     return n + 256;
@@ -998,11 +1000,11 @@ int moe_route_fp8_run(const RouteScratch& rs, const uint8_t* xq, const float* xs
                                    cfg->n_group, cfg->topk_group, cfg->routed_scale, stream);
     }
     B200_CUDA_TRY(cudaMemsetAsync(rs.flag_n, 0, sizeof(int), stream));
-    int st = launch_gate_logits_tc(xq, xs, gate_w, rs.whi, rs.wlo, rs.partials, T, E, D, status, stream);
-    if (st) return st;
     RouteCert approx;
+    int st = launch_gate_logits_tc(xq, xs, gate_w, rs.whi, rs.wlo, rs.partials, T, E, D, status, stream, &approx.plan);
+    if (st) return st;
     approx.tau = ROUTE_TC_TAU; approx.flag_list = rs.flag_list; approx.flag_n = rs.flag_n;
-    st = launch_route_select(rs.partials, moe_gate_tc_splits(D), bias, ids, wts, counts, nullptr, T, E, K, cfg->scoring,
+    st = launch_route_select(rs.partials, 0, bias, ids, wts, counts, nullptr, T, E, K, cfg->scoring,
                              cfg->n_group, cfg->topk_group, cfg->routed_scale, stream, approx);
     if (st) return st;
     // exact pass over the flagged tokens (usually a few per cent): the fixed-order chains, then the same selection
@@ -1082,7 +1084,7 @@ int b200_moe_route_fp8(b200_ws* ws, const uint8_t* xq, const float* xs, const fl
     if (!ws) return B200_CUDA_ERROR;
     auto carve = [&](WsCarver& c, RouteScratch& rs) {
         const bool tc = moe_gate_tc_supported(T, E, D);
-        rs.partials = c.take<float>((size_t)max(moe_gate_chunks(D, true), moe_gate_tc_splits(D)) * T * E);
+        rs.partials = c.take<float>((size_t)max(moe_gate_chunks(D, true), moe_gate_tc_slots(D)) * T * E);
         rs.whi = tc ? c.take<float>((size_t)E * D) : nullptr;
         rs.wlo = tc ? c.take<float>((size_t)E * D) : nullptr;
         rs.flag_list = tc ? c.take<int>((size_t)T) : nullptr;

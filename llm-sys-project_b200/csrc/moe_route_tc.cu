@@ -20,9 +20,11 @@
 // the selection kernel adds the CTAs' partial sums with ordinary fp32 additions.
 //
 //   wsplit_kernel        wg -> (hi, lo), once per call (the weights are a caller-owned buffer that may change)
-//   gate_tc_kernel       CTA = 128 tokens x all experts x 512 of d; warps 0-3 dequantise and split the
-//                        token rows into the swizzled A tiles (and read the accumulator out at the end), warp
-//                        4 fetches the weight tiles by TMA, warp 5 issues the MMAs; two 32-wide stages.
+//   gate_tc_kernel       one persistent CTA per SM over an equal share of the (128-token tile, 128-deep block)
+//                        units; warps 0-3 dequantise and split the token rows into the swizzled A tiles (rows
+//                        fetched one block ahead), warps 4-7 store finished partial sums from one of two TMEM
+//                        accumulators while the other one is being multiplied, warp 8 fetches the weight tiles
+//                        by TMA, warp 9 issues the MMAs; two 32-wide stages.
 // Every mbarrier wait is bounded; on give-up the CTA flags B200_TIMEOUT and winds down.
 #include "common.cuh"
 #include "moe_internal.cuh"
@@ -31,15 +33,16 @@
 
 namespace {
 
-constexpr int TM = 128;              // tokens per CTA (TMEM lanes)
+constexpr int TM = 128;              // tokens per tile (TMEM lanes)
 constexpr int KS = 32;               // d per stage: 128 bytes of tf32 = one swizzle row
 constexpr int NSTAGE = 2;
 constexpr int A_TILE = TM * KS * 4;  // 16384 bytes (hi or lo)
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;      // warps 0-3 convert, 4-7 read accumulators out, 8 TMA, 9 MMA
 constexpr int MAX_N = 256;
+constexpr int TC_CHAIN = 4;          // longest accumulation chain, in 128-deep blocks
 
 struct TcSmem {
-    uint64_t a_full[NSTAGE], b_full[NSTAGE], empty[NSTAGE], done;
+    uint64_t a_full[NSTAGE], b_full[NSTAGE], empty[NSTAGE], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -64,11 +67,13 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t adesc, uint64
         : "memory");
 }
 
-// partials[(split * T + t) * E + e] = sum over the split's d of x[t,d] * w[e,d]
+// Persistent CTA over the units [blockIdx.x * L, (blockIdx.x + 1) * L) of the plan (moe_internal.cuh).  Two
+// 256-column accumulators in TMEM alternate between pieces, so that a finished piece is stored while the next
+// one is multiplied.
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constant__ CUtensorMap tmap_lo,
                const uint8_t* __restrict__ xq, const float* __restrict__ xs, float* __restrict__ partials, int T, int E,
-               int D, int N, int kb_per_split, int* status) {
+               int D, int N, TcPlan plan, int n_units, int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int b_tile = N * KS * 4;                                  // bytes of one weight tile (hi or lo)
@@ -76,11 +81,9 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     TcSmem* sm = reinterpret_cast<TcSmem*>(base + (size_t)NSTAGE * stage_bytes);
     volatile int* abort_flag = &sm->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t0 = blockIdx.x * TM, split = blockIdx.y;
-    const int nb = D / 128;
-    const int kb0 = split * kb_per_split, kb1 = min(nb, kb0 + kb_per_split);
-    const int nstages = max(0, kb1 - kb0) * (128 / KS);
-    const int d_begin = kb0 * 128;
+    const int nb = plan.nblk;
+    const int u0 = blockIdx.x * plan.L, u1 = min(n_units, u0 + plan.L);
+    constexpr int SPB = 128 / KS;                                   // stages per 128-deep block
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) {
@@ -88,15 +91,18 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             ptx::mbar_init(&sm->b_full[s], 1);
             ptx::mbar_init(&sm->empty[s], 1);
         }
-        ptx::mbar_init(&sm->done, 1);
+        for (int s = 0; s < 2; s++) {
+            ptx::mbar_init(&sm->acc_full[s], 1);
+            ptx::mbar_init(&sm->acc_empty[s], 128);
+        }
         sm->abort_flag = 0;
         ptx::fence_mbar_init();
     }
-    if (warp == 5) {
-        ptx::tmem_alloc(&sm->tmem_base, 256);
+    if (warp == 9) {
+        ptx::tmem_alloc(&sm->tmem_base, 512);
         ptx::tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) {
+    if (warp == 8 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_hi);
         ptx::prefetch_tensormap(&tmap_lo);
     }
@@ -107,60 +113,79 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
 
     if (warp < 4) {
         // ===================== A tiles: dequantise, split, swizzle (thread = token row) =====================
+        // The row's 128 bytes of one block are fetched one block ahead of their conversion.
         const int r = threadIdx.x;
-        const int t = t0 + r;
-        const uint8_t* xrow = xq + (size_t)min(t, T - 1) * D;
-        const float* srow = xs + (size_t)min(t, T - 1) * nb;
-        const bool live = t < T;
-        for (int i = 0; i < nstages; i++) {
-            const int s = i % NSTAGE;
-            const uint32_t par = (uint32_t)((i / NSTAGE) & 1);
-            const int d0 = d_begin + i * KS;
-            // fetch before waiting for the slot
-            const uint4 q0 = *reinterpret_cast<const uint4*>(xrow + d0);
-            const uint4 q1 = *reinterpret_cast<const uint4*>(xrow + d0 + 16);
-            const float sc = live ? srow[d0 / 128] : 0.0f;
-            if (!ptx::mbar_wait(&sm->empty[s], par ^ 1, abort_flag)) goto done;
-            {
-            const uint32_t a_hi = ptx::smem_u32(base + (size_t)s * stage_bytes) + r * 128;
-            const uint32_t a_lo = a_hi + A_TILE;
-            const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        uint4 nxt[8];
+        float nxt_sc = 0.0f;
+        bool nxt_live = false;
+        auto fetch = [&](int u) {
+            const int tile = u / nb, kb = u - tile * nb;
+            const int t = tile * TM + r;
+            nxt_live = t < T;
+            const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)min(t, T - 1) * D + (size_t)kb * 128);
 #pragma unroll
-            for (int j = 0; j < 8; j++) {                       // 16-byte chunk j = 4 consecutive d
-                float h[4], l[4];
+            for (int j = 0; j < 8; j++) nxt[j] = __ldg(src + j);
+            nxt_sc = nxt_live ? xs[(size_t)t * nb + kb] : 0.0f;
+        };
+        if (u0 < u1) fetch(u0);
+        int i = 0;
+        for (int u = u0; u < u1; u++) {
+            uint4 cur[8];
 #pragma unroll
-                for (int b = 0; b < 4; b++) {
-                    __nv_fp8_e4m3 q;
-                    q.__x = (unsigned char)((words[j] >> (8 * b)) & 0xFF);
-                    // the dequantised activation, as the exact kernels form it (rows beyond T: zero)
-                    const float x = live ? __fmul_rn(float(q), sc) : 0.0f;
-                    h[b] = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
-                    l[b] = __fsub_rn(x, h[b]);
+            for (int j = 0; j < 8; j++) cur[j] = nxt[j];
+            const float sc = nxt_sc;
+            const bool live = nxt_live;
+            if (u + 1 < u1) fetch(u + 1);
+#pragma unroll
+            for (int q4 = 0; q4 < SPB; q4++, i++) {
+                const int s = i % NSTAGE;
+                const uint32_t par = (uint32_t)((i / NSTAGE) & 1);
+                if (!ptx::mbar_wait(&sm->empty[s], par ^ 1, abort_flag)) goto done;
+                {
+                const uint32_t a_hi = ptx::smem_u32(base + (size_t)s * stage_bytes) + r * 128;
+                const uint32_t a_lo = a_hi + A_TILE;
+                const uint32_t words[8] = {cur[2 * q4].x, cur[2 * q4].y, cur[2 * q4].z, cur[2 * q4].w,
+                                           cur[2 * q4 + 1].x, cur[2 * q4 + 1].y, cur[2 * q4 + 1].z, cur[2 * q4 + 1].w};
+#pragma unroll
+                for (int j = 0; j < 8; j++) {                       // 16-byte chunk j = 4 consecutive d
+                    float h[4], l[4];
+#pragma unroll
+                    for (int b = 0; b < 4; b++) {
+                        __nv_fp8_e4m3 q;
+                        q.__x = (unsigned char)((words[j] >> (8 * b)) & 0xFF);
+                        // the dequantised activation, as the exact kernels form it (rows beyond T: zero)
+                        const float x = live ? __fmul_rn(float(q), sc) : 0.0f;
+                        h[b] = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+                        l[b] = __fsub_rn(x, h[b]);
+                    }
+                    const uint32_t off = (uint32_t)((j ^ (r & 7)) << 4);
+                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a_hi + off), "f"(h[0]), "f"(h[1]), "f"(h[2]), "f"(h[3]) : "memory");
+                    asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a_lo + off), "f"(l[0]), "f"(l[1]), "f"(l[2]), "f"(l[3]) : "memory");
                 }
-                const uint32_t off = (uint32_t)((j ^ (r & 7)) << 4);
-                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a_hi + off), "f"(h[0]), "f"(h[1]), "f"(h[2]), "f"(h[3]) : "memory");
-                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a_lo + off), "f"(l[0]), "f"(l[1]), "f"(l[2]), "f"(l[3]) : "memory");
+                }
+                ptx::fence_proxy_async_smem();                      // generic-proxy stores -> visible to the MMA (async proxy)
+                ptx::mbar_arrive(&sm->a_full[s]);
             }
-            }
-            ptx::fence_proxy_async_smem();                      // generic-proxy stores -> visible to the MMA (async proxy)
-            ptx::mbar_arrive(&sm->a_full[s]);
         }
-        // ---- epilogue: accumulator row -> partial logits ----
-        if (!ptx::mbar_wait(&sm->done, 0, abort_flag)) goto done;
-        ptx::tc_fence_after();
-        {
-            const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-            float* dst = partials + ((size_t)split * T + t) * E;
+    } else if (warp < 8) {
+        // ===================== accumulators -> partial sums (thread = token row of the tile) =====================
+        const int ew = warp - 4;                                    // = warp % 4: the TMEM lanes this warp may read
+        const uint32_t lane_addr = (uint32_t)(ew * 32) << 16;
+        int pc = 0;
+        for (int u = u0; u < u1; pc++) {
+            const int tile = u / nb, kb = u - tile * nb;
+            const int len = min(plan.ch, min(nb - kb, u1 - u));
+            const int slot = tc_slots_before(plan, tile, u);
+            const int buf = pc & 1;
+            if (!ptx::mbar_wait(&sm->acc_full[buf], (uint32_t)((pc >> 1) & 1), abort_flag)) goto done;
+            ptx::tc_fence_after();
+            const int t = tile * TM + ew * 32 + lane;
+            float* dst = partials + ((size_t)slot * T + min(t, T - 1)) * E;
             for (int c0 = 0; c0 < N; c0 += 32) {
                 uint32_t v[32];
-                if (nstages > 0) {
-                    ptx::tmem_ld_32x32(tmem + lane_addr + c0, v);
-                    ptx::tc_wait_ld();
-                } else {
-#pragma unroll
-                    for (int k = 0; k < 32; k++) v[k] = 0;
-                }
-                if (live) {
+                ptx::tmem_ld_32x32(tmem + lane_addr + buf * 256 + c0, v);
+                ptx::tc_wait_ld();
+                if (t < T) {
 #pragma unroll
                     for (int k = 0; k < 32; k += 4)
                         if (c0 + k < E)          // E % 4 == 0
@@ -169,52 +194,80 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
                                             __uint_as_float(v[k + 3]));
                 }
             }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&sm->acc_empty[buf]);
+            u += len;
         }
-    } else if (warp == 4) {
+    } else if (warp == 8) {
         // ===================== weight tiles by TMA =====================
         if (lane == 0) {
-            for (int i = 0; i < nstages; i++) {
-                const int s = i % NSTAGE;
-                const uint32_t par = (uint32_t)((i / NSTAGE) & 1);
-                if (!ptx::mbar_wait_relaxed(&sm->empty[s], par ^ 1, abort_flag, 100)) goto done;
-                uint8_t* bh = base + (size_t)s * stage_bytes + 2 * A_TILE;
-                ptx::mbar_expect_tx(&sm->b_full[s], 2 * b_tile);
-                ptx::tma_load_2d(bh, &tmap_hi, &sm->b_full[s], d_begin + i * KS, 0);
-                ptx::tma_load_2d(bh + b_tile, &tmap_lo, &sm->b_full[s], d_begin + i * KS, 0);
+            int i = 0;
+            for (int u = u0; u < u1; u++) {
+                const int kb = u % nb;
+                for (int q4 = 0; q4 < SPB; q4++, i++) {
+                    const int s = i % NSTAGE;
+                    const uint32_t par = (uint32_t)((i / NSTAGE) & 1);
+                    if (!ptx::mbar_wait_relaxed(&sm->empty[s], par ^ 1, abort_flag, 100)) goto done;
+                    uint8_t* bh = base + (size_t)s * stage_bytes + 2 * A_TILE;
+                    ptx::mbar_expect_tx(&sm->b_full[s], 2 * b_tile);
+                    ptx::tma_load_2d(bh, &tmap_hi, &sm->b_full[s], kb * 128 + q4 * KS, 0);
+                    ptx::tma_load_2d(bh + b_tile, &tmap_lo, &sm->b_full[s], kb * 128 + q4 * KS, 0);
+                }
             }
         }
     } else {
         // ===================== MMA issuer =====================
         if (lane == 0) {
             const uint32_t idesc = ptx::make_idesc(2, 2, 0, 0, TM, N);      // tf32 x tf32 -> f32, both K-major
-            for (int i = 0; i < nstages; i++) {
-                const int s = i % NSTAGE;
-                const uint32_t par = (uint32_t)((i / NSTAGE) & 1);
-                if (!ptx::mbar_wait(&sm->a_full[s], par, abort_flag)) goto done;
-                if (!ptx::mbar_wait(&sm->b_full[s], par, abort_flag)) goto done;
+            int i = 0, pc = 0;
+            for (int u = u0; u < u1; pc++) {
+                const int kb = u % nb;
+                const int len = min(plan.ch, min(nb - kb, u1 - u));
+                const int buf = pc & 1;
+                if (!ptx::mbar_wait(&sm->acc_empty[buf], (uint32_t)(((pc >> 1) & 1) ^ 1), abort_flag)) goto done;
                 ptx::tc_fence_after();
-                const uint32_t ah = ptx::smem_u32(base + (size_t)s * stage_bytes), al = ah + A_TILE;
-                const uint32_t bh = al + A_TILE, bl = bh + b_tile;
+                const uint32_t acc = tmem + buf * 256;
+                for (int st = 0; st < len * SPB; st++, i++) {
+                    const int s = i % NSTAGE;
+                    const uint32_t par = (uint32_t)((i / NSTAGE) & 1);
+                    if (!ptx::mbar_wait(&sm->a_full[s], par, abort_flag)) goto done;
+                    if (!ptx::mbar_wait(&sm->b_full[s], par, abort_flag)) goto done;
+                    ptx::tc_fence_after();
+                    const uint32_t ah = ptx::smem_u32(base + (size_t)s * stage_bytes), al = ah + A_TILE;
+                    const uint32_t bh = al + A_TILE, bl = bh + b_tile;
 #pragma unroll
-                for (int kk = 0; kk < KS / 8; kk++) {              // 8 tf32 = 32 bytes of K per MMA
-                    const uint64_t dah = ptx::make_smem_desc(ah + kk * 32, 16, 1024, 2);
-                    const uint64_t dal = ptx::make_smem_desc(al + kk * 32, 16, 1024, 2);
-                    const uint64_t dbh = ptx::make_smem_desc(bh + kk * 32, 16, 1024, 2);
-                    const uint64_t dbl = ptx::make_smem_desc(bl + kk * 32, 16, 1024, 2);
-                    mma_tf32(tmem, dah, dbh, idesc, (i > 0 || kk > 0) ? 1u : 0u);
-                    mma_tf32(tmem, dah, dbl, idesc, 1u);
-                    mma_tf32(tmem, dal, dbh, idesc, 1u);
+                    for (int kk = 0; kk < KS / 8; kk++) {              // 8 tf32 = 32 bytes of K per MMA
+                        const uint64_t dah = ptx::make_smem_desc(ah + kk * 32, 16, 1024, 2);
+                        const uint64_t dal = ptx::make_smem_desc(al + kk * 32, 16, 1024, 2);
+                        const uint64_t dbh = ptx::make_smem_desc(bh + kk * 32, 16, 1024, 2);
+                        const uint64_t dbl = ptx::make_smem_desc(bl + kk * 32, 16, 1024, 2);
+                        mma_tf32(acc, dah, dbh, idesc, (st > 0 || kk > 0) ? 1u : 0u);
+                        mma_tf32(acc, dah, dbl, idesc, 1u);
+                        mma_tf32(acc, dal, dbh, idesc, 1u);
+                    }
+                    ptx::tc_commit(&sm->empty[s]);
                 }
-                ptx::tc_commit(&sm->empty[s]);
+                ptx::tc_commit(&sm->acc_full[buf]);
+                u += len;
             }
-            ptx::tc_commit(&sm->done);
         }
     }
 done:
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 5) ptx::tmem_dealloc(tmem, 256);
+    if (warp == 9) ptx::tmem_dealloc(tmem, 512);
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(status, B200_TIMEOUT);
+}
+
+// Sum of a token's slots in order: the approximate logits themselves (test hook only).
+__global__ void tc_sum_kernel(const float* __restrict__ partials, float* __restrict__ logits, int T, int E, TcPlan plan) {
+    const int t = blockIdx.x;
+    const int n = tc_slots_before(plan, t / TM, (t / TM + 1) * plan.nblk);
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        float l = partials[(size_t)t * E + e];
+        for (int s = 1; s < n; s++) l = __fadd_rn(l, partials[((size_t)s * T + t) * E + e]);
+        logits[(size_t)t * E + e] = l;
+    }
 }
 
 // Row-major fp32 matrix [rows, cols], tile = box_rows x 32 floats (128 bytes), 128-byte swizzle.
@@ -238,15 +291,15 @@ int make_tmap_f32_sw128(CUtensorMap* map, const void* basep, unsigned long long 
 bool moe_gate_tc_supported(int T, int E, int D) {
     return T >= 256 && E >= 16 && E <= MAX_N && E % 16 == 0 && D % 128 == 0 && D >= 512;
 }
-static int g_tc_splits_override = 0;      // set only inside b200_moe_gate_logits_tc (test hook)
-int moe_gate_tc_splits(int D) {
-    if (g_tc_splits_override > 0) return g_tc_splits_override;
-    return ceil_div(D / 128, 4);      // chains of at most four 128-deep blocks: the accumulation error grows with the chain
-}
+static int g_tc_chain_override = 0;      // set only inside b200_moe_gate_logits_tc (test hook)
+static int tc_chain() { return g_tc_chain_override > 0 ? g_tc_chain_override : TC_CHAIN; }
+// A CTA never takes fewer than TC_CHAIN units, so a tile is cut by at most nblk / TC_CHAIN range boundaries on top
+// of its own nblk / TC_CHAIN chains.
+int moe_gate_tc_slots(int D) { return 2 * ceil_div(D / 128, TC_CHAIN) + 1; }
 
-// whi / wlo: E * D floats each (workspace); partials: splits * T * E floats.
+// whi / wlo: E * D floats each (workspace); partials: moe_gate_tc_slots(D) * T * E floats.
 int launch_gate_logits_tc(const uint8_t* xq, const float* xs, const float* wg, float* whi, float* wlo, float* partials,
-                          int T, int E, int D, int* status, cudaStream_t stream) {
+                          int T, int E, int D, int* status, cudaStream_t stream, TcPlan* plan_out) {
     const long long n = (long long)E * D;
     wsplit_kernel<<<592, 256, 0, stream>>>(wg, whi, wlo, n);
     b200_count_launch(1);
@@ -259,38 +312,60 @@ int launch_gate_logits_tc(const uint8_t* xq, const float* xs, const float* wg, f
     const int N = E;
     const size_t smem = 1024 + (size_t)NSTAGE * (2 * A_TILE + 2 * (size_t)N * KS * 4) + sizeof(TcSmem) + 64;
     static bool attr_done[64] = {false};
-    if (b200_first_call_on_device(attr_done))
+    static int sm_count[64] = {0};
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    if (b200_first_call_on_device(attr_done)) {
         B200_CUDA_TRY(cudaFuncSetAttribute(gate_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)(1024 + (size_t)NSTAGE * (2 * A_TILE + 2 * (size_t)MAX_N * KS * 4) + sizeof(TcSmem) + 64)));
-    const int splits = moe_gate_tc_splits(D);
-    const int kbps = ceil_div(D / 128, splits);
-    dim3 grid(ceil_div(T, TM), splits);
-    gate_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(th, tl, xq, xs, partials, T, E, D, N, kbps, status);
+        B200_CUDA_TRY(cudaDeviceGetAttribute(&sm_count[dev & 63], cudaDevAttrMultiProcessorCount, dev));
+    }
+    TcPlan plan;
+    plan.nblk = D / 128;
+    plan.ch = min(tc_chain(), plan.nblk);
+    const long long units = (long long)ceil_div(T, TM) * plan.nblk;
+    if (units > 0x3fffffff) return B200_UNSUPPORTED;
+    const int sms = max(1, sm_count[dev & 63]);
+    plan.L = max((int)((units + sms - 1) / sms), plan.ch);         // one CTA per SM, never below one whole chain
+    const int grid = (int)((units + plan.L - 1) / plan.L);
+    gate_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(th, tl, xq, xs, partials, T, E, D, N, plan, (int)units, status);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
+    *plan_out = plan;
     return B200_OK;
 }
 
-// Test hook: the tensor-core logits as partial sums [splits, T, E] (the caller adds them up and compares with the
-// exact chains).  *splits_out > 0 on entry asks for that many partial sums along D (at most D / 128) instead of
-// the library's choice; on return it holds the number written.  Not thread-safe (the override is a global).
-extern "C" int b200_moe_gate_logits_tc(const uint8_t* xq, const float* xs, const float* gate_w, float* partials_out,
-                                       int T, int E, int D, int* splits_out, b200_stream_t stream) {
-    if (!xq || !xs || !gate_w || !partials_out || !splits_out) return B200_BAD_ARG;
+// Test hook: the tensor-core logits [T, E] (a token's partial sums added in slot order).  chain_blocks > 0 asks
+// for accumulation chains of that many 128-deep blocks instead of the library's choice (D / 128: one chain over
+// all of d, which shows how the tensor core's accumulation error grows with the chain).  Not thread-safe (the
+// override is a global).
+extern "C" int b200_moe_gate_logits_tc(const uint8_t* xq, const float* xs, const float* gate_w, float* logits_out,
+                                       int T, int E, int D, int chain_blocks, b200_stream_t stream) {
+    if (!xq || !xs || !gate_w || !logits_out) return B200_BAD_ARG;
     if (!moe_gate_tc_supported(T, E, D)) return B200_UNSUPPORTED;
-    g_tc_splits_override = (*splits_out > 0 && *splits_out <= D / 128) ? *splits_out : 0;
+    if (chain_blocks < 0 || chain_blocks > D / 128) return B200_BAD_ARG;
     b200_ws* ws = b200_default_ws();
     if (!ws) return B200_CUDA_ERROR;
+    // chains longer than the default need no more slots than the default's bound
+    const size_t slots = (size_t)max(moe_gate_tc_slots(D), 2 * ceil_div(D / 128, max(1, chain_blocks)) + 1);
     WsCarver sz(nullptr);
     sz.take<float>((size_t)E * D);
     sz.take<float>((size_t)E * D);
+    sz.take<float>(slots * T * E);
     int st = b200_ws_ensure(ws, sz.total());
     if (st) return st;
     WsCarver cv(ws->base);
     float* whi = cv.take<float>((size_t)E * D);
     float* wlo = cv.take<float>((size_t)E * D);
-    *splits_out = moe_gate_tc_splits(D);
-    st = launch_gate_logits_tc(xq, xs, gate_w, whi, wlo, partials_out, T, E, D, ws->d_status, stream);
-    g_tc_splits_override = 0;
-    return st;
+    float* partials = cv.take<float>(slots * T * E);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    TcPlan plan;
+    g_tc_chain_override = chain_blocks;
+    st = launch_gate_logits_tc(xq, xs, gate_w, whi, wlo, partials, T, E, D, ws->d_status, s, &plan);
+    g_tc_chain_override = 0;
+    if (st) return st;
+    tc_sum_kernel<<<T, 128, 0, s>>>(partials, logits_out, T, E, plan);
+    b200_count_launch(1);
+    B200_CUDA_TRY(cudaGetLastError());
+    return B200_OK;
 }

@@ -26,11 +26,11 @@ B200_API int b200_wait_selftest(b200_ws* ws, long long* elapsed_ns, b200_stream_
  * Synchronises the stream (timed with CUDA events inside the call); iters K blocks of four MMAs per CTA. */
 B200_API int b200_fp8_mma_rate(int pair, int iters, float* tflops, float* ms, b200_stream_t stream);
 
-/* The approximate router logits of the tensor-core path as partial sums [splits, T, E] (sum them to get the
- * logits), for the test that bounds their distance from the fixed-order FMA chains.  B200_UNSUPPORTED when
- * the shape does not take that path. */
-B200_API int b200_moe_gate_logits_tc(const uint8_t* xq, const float* xs, const float* gate_w, float* partials_out,
-                                     int T, int E, int D, int* splits_out, b200_stream_t stream);
+/* The approximate router logits [T, E] of the tensor-core path, for the test that bounds their distance from the
+ * fixed-order FMA chains.  chain_blocks: length of the accumulation chains in 128-deep blocks of d (0 = the
+ * library's choice, D / 128 = one chain over all of d).  B200_UNSUPPORTED when the shape does not take that path. */
+B200_API int b200_moe_gate_logits_tc(const uint8_t* xq, const float* xs, const float* gate_w, float* logits_out,
+                                     int T, int E, int D, int chain_blocks, b200_stream_t stream);
 /* Number of tokens the last tensor-core routing call on this workspace handed to its exact pass (synchronises
  * the stream); -1 when the last routing call took the exact path for all tokens. */
 B200_API int b200_moe_route_last_flagged(b200_ws* ws, b200_stream_t stream, int* n);

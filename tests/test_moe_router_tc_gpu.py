@@ -42,7 +42,7 @@ def test_tc_logits_stay_within_the_assumed_error(b200, cuda):
     xq, xs = oracle.quant_act(x)
     ref = oracle.gate_logits_fp8(xq, xs, wg)
     got = b200.moe_gate_logits_tc(_dev(xq, cuda), _dev(xs, cuda), _dev(wg, cuda)).cpu().numpy()
-    one = b200.moe_gate_logits_tc(_dev(xq, cuda), _dev(xs, cuda), _dev(wg, cuda), splits=1).cpu().numpy()
+    one = b200.moe_gate_logits_tc(_dev(xq, cuda), _dev(xs, cuda), _dev(wg, cuda), chain_blocks=D // 128).cpu().numpy()
     torch.cuda.synchronize()
     assert b200.device_status() == 0
     err, err_one = np.abs(got - ref).max(), np.abs(one - ref).max()
