@@ -174,6 +174,38 @@ def build_moe(b200, torch, dev, world, rank):
     return layer, xq, xs
 
 
+def bench_route_only(b200, torch, dev, args):
+    """The routing call alone at the full token count (no expert weights: a few hundred MB on the device), for
+    profiler captures of the router kernels.  Prints its own JSON line; not a bench value."""
+    c = MOE
+    gate_w = torch.empty((c["E"], c["D"]), dtype=torch.float32, device=dev)
+    b200.fill_normal_(gate_w, 3000, c["D"] ** -0.5)
+    bias = torch.from_numpy(b200.synth_normal_host(3001, 0, c["E"], 0.01)).to(dev)
+    x = torch.empty((c["T"], c["D"]), dtype=torch.float32, device=dev)
+    b200.fill_normal_(x, 4000, 1.0)
+    xq = torch.empty((c["T"], c["D"]), dtype=torch.uint8, device=dev)
+    xs = torch.empty((c["T"], c["D"] // 128), dtype=torch.float32, device=dev)
+    b200.quant_act_1x128(x, xq, xs)
+    del x
+    ids = torch.zeros((c["T"], c["K"]), dtype=torch.int32, device=dev)
+    wts = torch.zeros((c["T"], c["K"]), dtype=torch.float32, device=dev)
+    counts = torch.zeros(c["E"], dtype=torch.int32, device=dev)
+    cfg = b200.MoeFp8Config(c["T"], c["E"], c["K"], c["D"], c["I"], b200.SCORE_SIGMOID_GROUPED, c["n_group"],
+                            c["topk_group"], c["routed_scale"], 0)
+    steps = max(1, args.steps)
+    for _ in range(max(args.warmup, 3)):
+        b200.moe_route_fp8(xq, xs, gate_w, bias, ids, wts, cfg, counts=counts)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        b200.moe_route_fp8(xq, xs, gate_w, bias, ids, wts, cfg, counts=counts)
+    e1.record()
+    torch.cuda.synchronize()
+    assert b200.device_status() == 0, "device-side wait timed out"
+    print(json.dumps({"routing_only": True, "tokens": c["T"], "ms_per_call": e0.elapsed_time(e1) / steps, "steps": steps,
+                      "exact_pass_tokens": b200.moe_route_last_flagged()}))
+
+
 def moe_gemm1_bytes(counts):
     """Algorithmic HBM bytes of one GEMM1 launch: FP8 weights + block scales of the active experts,
     the sorted FP8 rows + 1x128 scales read, the requantised activations + scales written."""
@@ -788,6 +820,8 @@ def main():
     ap.add_argument("--skip-moe", action="store_true")
     ap.add_argument("--cpu-tokens", type=int, default=96)
     ap.add_argument("--cpu-queries", type=int, default=16)
+    ap.add_argument("--route-only", action="store_true",
+                    help="run only the routing call of the MoE layer at the full token count (profiler captures)")
     ap.add_argument("--small", action="store_true",
                     help="profiling-sized case of the same kernels (32 experts, 512 tokens; 16 queries, short caches): "
                          "inputs still exceed L2 but only ~2 GB live on the device; not a bench value")
@@ -823,6 +857,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+    if args.route_only:
+        if rank == 0:
+            bench_route_only(b200, torch, dev, args)
+        return
     sampler = ClockSampler(local_rank)
 
     if args.skip_moe:

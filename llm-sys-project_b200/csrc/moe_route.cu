@@ -453,12 +453,12 @@ route_select_row_regs(const float* __restrict__ partials, int n_chunks, const fl
     }
 }
 
-// The register path serves: E = 32 * PER with PER in {2, 4, 8}, groups that are whole runs of lanes
+// The register path serves: E = 32 * PER with PER in {1, 2, 4, 8}, groups that are whole runs of lanes
 // (power-of-two many), K <= 32.
 __host__ __device__ inline int route_regs_per(int E, int K, int scoring, int n_group) {
     if (scoring != B200_SCORE_SIGMOID_GROUPED || E % 32 || K > 32 || n_group < 1 || n_group > 32 || E % n_group) return 0;
     const int per = E / 32, gs = E / n_group;
-    if (per != 2 && per != 4 && per != 8) return 0;
+    if (per != 1 && per != 2 && per != 4 && per != 8) return 0;
     if (gs % per) return 0;
     const int lpg = gs / per;
     if (lpg & (lpg - 1)) return 0;
@@ -478,27 +478,27 @@ route_select_kernel(const float* __restrict__ partials, int n_chunks, const floa
     float* s = sm + (size_t)warp * 2 * E;
     float* c = s + E;
     const int rows = cert.list ? min(*cert.list_n, T) : T;
-    const int per = route_regs_per(E, K, scoring, n_group);
     for (int row = blockIdx.x * 4 + warp; row < rows; row += gridDim.x * 4) {
         const int t = cert.list ? cert.list[row] : row;
-        if (per == 8) {
-            route_select_row_regs<8>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, n_group, topk_group,
-                                     routed_scale, cert, row, t, lane);
-            continue;
-        }
-        if (per == 4) {
-            route_select_row_regs<4>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, n_group, topk_group,
-                                     routed_scale, cert, row, t, lane);
-            continue;
-        }
-        if (per == 2) {
-            route_select_row_regs<2>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, n_group, topk_group,
-                                     routed_scale, cert, row, t, lane);
-            continue;
-        }
         route_select_row(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, scoring, n_group,
                          topk_group, routed_scale, cert, row, t, s, c, lane);
         __syncwarp();
+    }
+}
+
+// The register path as a kernel of its own (fewer registers than the generic kernel: more resident warps).
+template <int PER>
+__global__ void __launch_bounds__(128, 5)
+route_select_regs_kernel(const float* __restrict__ partials, int n_chunks, const float* __restrict__ bias,
+                         int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
+                         float* __restrict__ logits_out, int T, int E, int K, int n_group, int topk_group,
+                         float routed_scale, RouteCert cert) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rows = cert.list ? min(*cert.list_n, T) : T;
+    for (int row = blockIdx.x * 4 + warp; row < rows; row += gridDim.x * 4) {
+        const int t = cert.list ? cert.list[row] : row;
+        route_select_row_regs<PER>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K, n_group, topk_group,
+                                   routed_scale, cert, row, t, lane);
     }
 }
 
@@ -786,6 +786,16 @@ gate_logits_fp8_list_kernel(const uint8_t* __restrict__ xq, const float* __restr
     const int nb = D / 128;
     constexpr int WREP = GL2_E * GL2_K / 4 / GL2_THREADS;                 // 16 float4 of the weight tile per thread
     const int xr = threadIdx.x >> 3, xp = threadIdx.x & 7;               // activation tile: entry xr, bytes 16*xp..
+    // The block's slab of weights (32 experts x the chunk's d) is walked in eight dependent steps; asking L2 for
+    // all of it up front pays the DRAM latency once instead of once per step.
+    if (blockIdx.z * GL2_T < n) {
+        const int lines_per_row = (d_end - d_begin) / 32;                // 128-byte lines of one expert's chunk
+        for (int i = threadIdx.x; i < GL2_E * lines_per_row; i += GL2_THREADS) {
+            const int r = i / lines_per_row, l = i - r * lines_per_row;
+            if (e0 + r < E)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(wg + (size_t)(e0 + r) * D + d_begin + l * 32));
+        }
+    }
     for (int i0 = blockIdx.z * GL2_T; i0 < n; i0 += gridDim.z * GL2_T) {
         __syncthreads();
         if (threadIdx.x < GL2_T) tok_s[threadIdx.x] = (i0 + threadIdx.x < n) ? list[i0 + threadIdx.x] : -1;
@@ -958,9 +968,23 @@ int launch_route_select(const float* partials, int n_chunks, const float* bias, 
     }
     // list mode: the length of the list is known only on the device; a modest grid walks it with a stride
     const int blocks = cert.list ? min(ceil_div(T, 4), 4 * 148) : ceil_div(T, 4);
-    route_select_kernel<<<blocks, 128, smem, stream>>>(partials, n_chunks, bias, ids, wts, counts,
-                                                              logits_out, T, E, K, scoring, n_group, topk_group,
-                                                              routed_scale, cert);
+    const int per = route_regs_per(E, K, scoring, n_group);
+    if (per == 8)
+        route_select_regs_kernel<8><<<blocks, 128, 0, stream>>>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K,
+                                                                n_group, topk_group, routed_scale, cert);
+    else if (per == 4)
+        route_select_regs_kernel<4><<<blocks, 128, 0, stream>>>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K,
+                                                                n_group, topk_group, routed_scale, cert);
+    else if (per == 2)
+        route_select_regs_kernel<2><<<blocks, 128, 0, stream>>>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K,
+                                                                n_group, topk_group, routed_scale, cert);
+    else if (per == 1)
+        route_select_regs_kernel<1><<<blocks, 128, 0, stream>>>(partials, n_chunks, bias, ids, wts, counts, logits_out, T, E, K,
+                                                                n_group, topk_group, routed_scale, cert);
+    else
+        route_select_kernel<<<blocks, 128, smem, stream>>>(partials, n_chunks, bias, ids, wts, counts,
+                                                           logits_out, T, E, K, scoring, n_group, topk_group,
+                                                           routed_scale, cert);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;

@@ -21,10 +21,10 @@
 //
 //   wsplit_kernel        wg -> (hi, lo), once per call (the weights are a caller-owned buffer that may change)
 //   gate_tc_kernel       one persistent CTA per SM over an equal share of the (128-token tile, 128-deep block)
-//                        units; warps 0-3 dequantise and split the token rows into the swizzled A tiles (rows
-//                        fetched one block ahead), warps 4-7 store finished partial sums from one of two TMEM
-//                        accumulators while the other one is being multiplied, warp 8 fetches the weight tiles
-//                        by TMA, warp 9 issues the MMAs; two 32-wide stages.
+//                        units; warps 0-7 dequantise and split the token rows into the swizzled A tiles (rows
+//                        fetched one block ahead), warps 8-11 store finished partial sums from one of two TMEM
+//                        accumulators while the other one is being multiplied, warp 12 fetches the weight tiles
+//                        by TMA, warp 13 issues the MMAs; two 32-wide stages.
 // Every mbarrier wait is bounded; on give-up the CTA flags B200_TIMEOUT and winds down.
 #include "common.cuh"
 #include "moe_internal.cuh"
@@ -37,7 +37,7 @@ constexpr int TM = 128;              // tokens per tile (TMEM lanes)
 constexpr int KS = 32;               // d per stage: 128 bytes of tf32 = one swizzle row
 constexpr int NSTAGE = 2;
 constexpr int A_TILE = TM * KS * 4;  // 16384 bytes (hi or lo)
-constexpr int TC_THREADS = 320;      // warps 0-3 convert, 4-7 read accumulators out, 8 TMA, 9 MMA
+constexpr int TC_THREADS = 448;      // warps 0-7 convert, 8-11 read accumulators out, 12 TMA, 13 MMA
 constexpr int MAX_N = 256;
 constexpr int TC_CHAIN = 4;          // longest accumulation chain, in 128-deep blocks
 
@@ -87,7 +87,7 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) {
-            ptx::mbar_init(&sm->a_full[s], 128);
+            ptx::mbar_init(&sm->a_full[s], 256);
             ptx::mbar_init(&sm->b_full[s], 1);
             ptx::mbar_init(&sm->empty[s], 1);
         }
@@ -98,11 +98,11 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
         sm->abort_flag = 0;
         ptx::fence_mbar_init();
     }
-    if (warp == 9) {
+    if (warp == 13) {
         ptx::tmem_alloc(&sm->tmem_base, 512);
         ptx::tmem_relinquish();
     }
-    if (warp == 8 && lane == 0) {
+    if (warp == 12 && lane == 0) {
         ptx::prefetch_tensormap(&tmap_hi);
         ptx::prefetch_tensormap(&tmap_lo);
     }
@@ -111,28 +111,30 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
     ptx::tc_fence_after();
     const uint32_t tmem = sm->tmem_base;
 
-    if (warp < 4) {
-        // ===================== A tiles: dequantise, split, swizzle (thread = token row) =====================
-        // The row's 128 bytes of one block are fetched one block ahead of their conversion.
-        const int r = threadIdx.x;
-        uint4 nxt[8];
+    if (warp < 8) {
+        // ===================== A tiles: dequantise, split, swizzle =====================
+        // Two threads per token row, 16 of a stage's 32 d each; the row's bytes of one 128-deep block are fetched
+        // one block ahead of their conversion.  (With one thread per row the conversion of a stage took nearly as
+        // long as its MMAs, and with two stages the two do not overlap fully.)
+        const int r = threadIdx.x & 127, half = threadIdx.x >> 7;
+        uint4 nxt[SPB];
         float nxt_sc = 0.0f;
         bool nxt_live = false;
         auto fetch = [&](int u) {
             const int tile = u / nb, kb = u - tile * nb;
             const int t = tile * TM + r;
             nxt_live = t < T;
-            const uint4* src = reinterpret_cast<const uint4*>(xq + (size_t)min(t, T - 1) * D + (size_t)kb * 128);
+            const uint8_t* src = xq + (size_t)min(t, T - 1) * D + (size_t)kb * 128 + half * 16;
 #pragma unroll
-            for (int j = 0; j < 8; j++) nxt[j] = __ldg(src + j);
+            for (int j = 0; j < SPB; j++) nxt[j] = __ldg(reinterpret_cast<const uint4*>(src + j * KS));
             nxt_sc = nxt_live ? xs[(size_t)t * nb + kb] : 0.0f;
         };
         if (u0 < u1) fetch(u0);
         int i = 0;
         for (int u = u0; u < u1; u++) {
-            uint4 cur[8];
+            uint4 cur[SPB];
 #pragma unroll
-            for (int j = 0; j < 8; j++) cur[j] = nxt[j];
+            for (int j = 0; j < SPB; j++) cur[j] = nxt[j];
             const float sc = nxt_sc;
             const bool live = nxt_live;
             if (u + 1 < u1) fetch(u + 1);
@@ -141,18 +143,17 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
                 const int s = i % NSTAGE;
                 const uint32_t par = (uint32_t)((i / NSTAGE) & 1);
                 if (!ptx::mbar_wait(&sm->empty[s], par ^ 1, abort_flag)) goto done;
-                {
                 const uint32_t a_hi = ptx::smem_u32(base + (size_t)s * stage_bytes) + r * 128;
                 const uint32_t a_lo = a_hi + A_TILE;
-                const uint32_t words[8] = {cur[2 * q4].x, cur[2 * q4].y, cur[2 * q4].z, cur[2 * q4].w,
-                                           cur[2 * q4 + 1].x, cur[2 * q4 + 1].y, cur[2 * q4 + 1].z, cur[2 * q4 + 1].w};
+                const uint32_t words[4] = {cur[q4].x, cur[q4].y, cur[q4].z, cur[q4].w};
 #pragma unroll
-                for (int j = 0; j < 8; j++) {                       // 16-byte chunk j = 4 consecutive d
+                for (int jj = 0; jj < 4; jj++) {                    // 16-byte chunk j = 4 consecutive d
+                    const int j = half * 4 + jj;
                     float h[4], l[4];
 #pragma unroll
                     for (int b = 0; b < 4; b++) {
                         __nv_fp8_e4m3 q;
-                        q.__x = (unsigned char)((words[j] >> (8 * b)) & 0xFF);
+                        q.__x = (unsigned char)((words[jj] >> (8 * b)) & 0xFF);
                         // the dequantised activation, as the exact kernels form it (rows beyond T: zero)
                         const float x = live ? __fmul_rn(float(q), sc) : 0.0f;
                         h[b] = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
@@ -162,14 +163,13 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
                     asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a_hi + off), "f"(h[0]), "f"(h[1]), "f"(h[2]), "f"(h[3]) : "memory");
                     asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(a_lo + off), "f"(l[0]), "f"(l[1]), "f"(l[2]), "f"(l[3]) : "memory");
                 }
-                }
                 ptx::fence_proxy_async_smem();                      // generic-proxy stores -> visible to the MMA (async proxy)
                 ptx::mbar_arrive(&sm->a_full[s]);
             }
         }
-    } else if (warp < 8) {
+    } else if (warp < 12) {
         // ===================== accumulators -> partial sums (thread = token row of the tile) =====================
-        const int ew = warp - 4;                                    // = warp % 4: the TMEM lanes this warp may read
+        const int ew = warp - 8;                                    // = warp % 4: the TMEM lanes this warp may read
         const uint32_t lane_addr = (uint32_t)(ew * 32) << 16;
         int pc = 0;
         for (int u = u0; u < u1; pc++) {
@@ -198,7 +198,7 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
             ptx::mbar_arrive(&sm->acc_empty[buf]);
             u += len;
         }
-    } else if (warp == 8) {
+    } else if (warp == 12) {
         // ===================== weight tiles by TMA =====================
         if (lane == 0) {
             int i = 0;
@@ -255,7 +255,7 @@ gate_tc_kernel(const __grid_constant__ CUtensorMap tmap_hi, const __grid_constan
 done:
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 9) ptx::tmem_dealloc(tmem, 512);
+    if (warp == 13) ptx::tmem_dealloc(tmem, 512);
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(status, B200_TIMEOUT);
 }
 
