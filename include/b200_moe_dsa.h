@@ -97,11 +97,13 @@ enum b200_moe_flags {
      * weight tile).  Results agree up to the order of the scatter-add. */
     B200_MOE_SINGLE_CTA_TILES = 4,
     B200_MOE_CTA_PAIR_TILES = 8,
-    /* Router logits of grouped sigmoid routing.  By default batches of 256 or more tokens compute them on the
-     * tensor cores (tf32 split operands: approximate to a few 1e-6) and accept a token's routing only when all
-     * its decision margins are far larger than that error; the other tokens (a few per cent) are recomputed with
-     * the fixed-order FMA chains, so the expert ids are the same as with exact logits for every token, the
-     * weights agree to ~1e-6 relative.  This flag forces the exact chains for all tokens. */
+    /* Router logits of grouped sigmoid routing.  By default batches of 256 or more tokens (E <= 256, no logits
+     * requested) compute them on the tensor cores (tf32 split operands, accumulation chains of 512 d: within
+     * about 2e-5 of the fixed-order chains at unit logit scale) and accept a token's routing only when all its
+     * decision margins exceed what an error of 2^-14 per unit of the token's logit rms could close; the other
+     * tokens (about 2 %) are recomputed with the fixed-order FMA chains.  The expert ids of every token are the
+     * ones exact logits give; the weights of accepted tokens agree with the exact ones to ~1e-6.  This flag
+     * forces the exact chains for all tokens (as does a non-NULL logits_out of b200_moe_route_fp8). */
     B200_MOE_EXACT_ROUTER_LOGITS = 16
 };
 
