@@ -41,7 +41,9 @@ enum b200_status {
     B200_CUDA_ERROR = 3,  /* a CUDA runtime/driver call failed; see b200_last_error_string */
     B200_TIMEOUT = 4,     /* a bounded device-side wait ran out (read back by b200_ws_device_status) */
     B200_NCCL_ERROR = 5,
-    B200_BAD_ARG = 6      /* null pointer / misaligned pointer */
+    B200_BAD_ARG = 6,     /* null pointer / misaligned pointer */
+    B200_BAD_SCALE = 7    /* B200_MOE_POW2_SCALES: a scale that is not a power of two was met on the device
+                           * (read back by b200_ws_device_status; the output is then wrong) */
 };
 
 /* kernels/moe/naive_moe.cuh:9-15 (struct MoeConfig) — same five ints, same order. */
@@ -104,7 +106,14 @@ enum b200_moe_flags {
      * tokens (about 2 %) are recomputed with the fixed-order FMA chains.  The expert ids of every token are the
      * ones exact logits give; the weights of accepted tokens agree with the exact ones to ~1e-6.  This flag
      * forces the exact chains for all tokens (as does a non-NULL logits_out of b200_moe_route_fp8). */
-    B200_MOE_EXACT_ROUTER_LOGITS = 16
+    B200_MOE_EXACT_ROUTER_LOGITS = 16,
+    /* Every scale (activations, weights) is a power of two, as the *_pow2 quantisers below produce them (the
+     * UE8M0 scale format of DeepSeek-V3.1-style checkpoints).  The grouped GEMMs then run on the hardware
+     * block-scaled MMA (tcgen05.mma kind::mxf8f6f4.block_scale): the scales are applied inside the tensor core,
+     * the accumulator stays in TMEM for the whole K loop and the software promotion per 128-deep K block
+     * disappears.  The requantisation between the two GEMMs also takes power-of-two scales.  Same tolerance as the
+     * default path against the fp32 emulation with the same scale rule.  Single GPU entry points only. */
+    B200_MOE_POW2_SCALES = 32
 };
 
 /* --------------------------------------------------------------------------- */
@@ -161,6 +170,12 @@ B200_API int b200_quant_act_1x128(const float* x, uint8_t* q, float* scales, lon
                                   b200_stream_t stream);
 B200_API int b200_quant_weight_128x128(const float* w, uint8_t* q, float* scales, long long rows, int cols,
                                        b200_stream_t stream);
+/* The same quantisers with power-of-two scales: scale = the smallest power of two >= amax/448 (at least 2^-126;
+ * 1 for an all-zero block), still stored as fp32.  For B200_MOE_POW2_SCALES. */
+B200_API int b200_quant_act_1x128_pow2(const float* x, uint8_t* q, float* scales, long long rows, int cols,
+                                       b200_stream_t stream);
+B200_API int b200_quant_weight_128x128_pow2(const float* w, uint8_t* q, float* scales, long long rows, int cols,
+                                            b200_stream_t stream);
 /* Router on the dequantised FP8 activations: logits (fp32 fma chain over d), then
  * softmax / top-K as moe_gate, or sigmoid + bias + group-limited top-K.  Also fills
  * counts[E] (tokens per expert; may be NULL). bias may be NULL. logits_out may be NULL. */
@@ -361,6 +376,8 @@ B200_API int b200_fill_normal_bf16(uint16_t* dst, long long n, unsigned long lon
  * (weights: 128x128 blocks; activations: 1x128) without an fp32 copy in memory. */
 B200_API int b200_fill_normal_fp8_w128(uint8_t* q, float* scales, long long rows, int cols,
                                        unsigned long long seed, float sigma, b200_stream_t stream);
+B200_API int b200_fill_normal_fp8_w128_pow2(uint8_t* q, float* scales, long long rows, int cols,
+                                       unsigned long long seed, float sigma, b200_stream_t stream);   /* power-of-two scales */
 
 #ifdef __cplusplus
 }

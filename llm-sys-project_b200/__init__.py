@@ -44,6 +44,8 @@ class MoeFp8Config(C.Structure):
 MOE_DETERMINISTIC = 1      # MoeFp8Config.flags: fixed-order (experts ascending) combine, bit-reproducible
 MOE_SINGLE_CTA_TILES, MOE_CTA_PAIR_TILES = 4, 8      # force the grouped GEMMs' tile shape
 MOE_EXACT_ROUTER_LOGITS = 16                         # fixed-order FMA router logits for every token
+MOE_POW2_SCALES = 32                                 # all scales are powers of two: hardware block-scaled MMA
+BAD_SCALE = 7                                        # device status: a scale was not a power of two
 
 
 class EpConfig(C.Structure):
@@ -60,18 +62,19 @@ EXPORTED_SYMBOLS = [
     "b200_ws_capacity", "b200_ws_device_status", "b200_launch_count",
     "b200_moe_forward_f32", "b200_moe_gate_f32", "b200_moe_permute", "b200_moe_gather_f32", "b200_gemm_f32",
     "b200_swiglu_f32", "b200_moe_scatter_f32",
-    "b200_quant_act_1x128", "b200_quant_weight_128x128", "b200_moe_route_fp8", "b200_moe_fp8_forward",
+    "b200_quant_act_1x128", "b200_quant_weight_128x128", "b200_quant_act_1x128_pow2", "b200_quant_weight_128x128_pow2",
+    "b200_moe_route_fp8", "b200_moe_fp8_forward",
     "b200_moe_fp8_experts", "b200_moe_fp8_pack_weights", "b200_moe_fp8_forward_packed",
     "b200_moe_fp8_experts_packed", "b200_moe_fp8_gemm1_stage", "b200_moe_fp8_profile", "b200_moe_fp8_profile_read",
     "b200_dsa_forward_f32", "b200_dsa_forward_bf16", "b200_dsa_forward_bf16_paged", "b200_dsa_forward_bf16_static", "b200_dsa_kv_gather_f32", "b200_dsa_dot_f32",
     "b200_dsa_softmax_f32", "b200_dsa_output_proj_f32",
     "b200_ep_plan", "b200_ep_sum_rows", "b200_ep_create", "b200_ep_connect", "b200_ep_forward", "b200_ep_stats",
     "b200_ep_workspace", "b200_ep_destroy",
-    "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128",
+    "b200_fill_normal_f32", "b200_fill_normal_bf16", "b200_fill_normal_fp8_w128", "b200_fill_normal_fp8_w128_pow2",
 ]
 # exported for the test suite only (declared in csrc/selftest.h, not in the public header)
 TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest", "b200_ep_connect_loopback", "b200_fp8_mma_rate",
-                     "b200_moe_gate_logits_tc", "b200_moe_route_last_flagged"]
+                     "b200_moe_gate_logits_tc", "b200_moe_route_last_flagged", "b200_mx_selftest"]
 
 
 def lib():
@@ -165,17 +168,18 @@ def moe_scatter(expert_out, token_map, expert_weights, expert_indices, expert_id
 # ---------------------------------------------------------------------------
 # MoE, FP8 block-scale
 # ---------------------------------------------------------------------------
-def quant_act_1x128(x, q, scales, stream=None):
+def quant_act_1x128(x, q, scales, stream=None, pow2=False):
+    """pow2: power-of-two scales (for MOE_POW2_SCALES)."""
     rows, cols = x.shape
-    _check(lib().b200_quant_act_1x128(_p(x), _p(q), _p(scales), C.c_longlong(rows), cols, _stream(stream)),
-           "quant_act_1x128")
+    fn = lib().b200_quant_act_1x128_pow2 if pow2 else lib().b200_quant_act_1x128
+    _check(fn(_p(x), _p(q), _p(scales), C.c_longlong(rows), cols, _stream(stream)), "quant_act_1x128")
 
 
-def quant_weight_128x128(w, q, scales, stream=None):
+def quant_weight_128x128(w, q, scales, stream=None, pow2=False):
     cols = w.shape[-1]
     rows = w.numel() // cols
-    _check(lib().b200_quant_weight_128x128(_p(w), _p(q), _p(scales), C.c_longlong(rows), cols, _stream(stream)),
-           "quant_weight_128x128")
+    fn = lib().b200_quant_weight_128x128_pow2 if pow2 else lib().b200_quant_weight_128x128
+    _check(fn(_p(w), _p(q), _p(scales), C.c_longlong(rows), cols, _stream(stream)), "quant_weight_128x128")
 
 
 def moe_route_fp8(xq, xs, gate_w, bias, expert_ids, expert_w, cfg, counts=None, logits_out=None, stream=None):
@@ -335,11 +339,12 @@ def fill_normal_(t, seed, sigma, stream=None):
     return t
 
 
-def fill_normal_fp8_w128_(q, scales, seed, sigma, stream=None):
+def fill_normal_fp8_w128_(q, scales, seed, sigma, stream=None, pow2=False):
     cols = q.shape[-1]
     rows = q.numel() // cols
-    _check(lib().b200_fill_normal_fp8_w128(_p(q), _p(scales), C.c_longlong(rows), cols, C.c_ulonglong(seed),
-                                           C.c_float(sigma), _stream(stream)), "fill_normal_fp8_w128")
+    fn = lib().b200_fill_normal_fp8_w128_pow2 if pow2 else lib().b200_fill_normal_fp8_w128
+    _check(fn(_p(q), _p(scales), C.c_longlong(rows), cols, C.c_ulonglong(seed), C.c_float(sigma), _stream(stream)),
+           "fill_normal_fp8_w128")
 
 
 def _splitmix64(x):
@@ -377,6 +382,12 @@ def fp8_mma_rate(pair=False, iters=20000, stream=None):
     _check(lib().b200_fp8_mma_rate(1 if pair else 0, int(iters), C.byref(tf), C.byref(ms), _stream(stream)),
            "fp8_mma_rate")
     return tf.value, ms.value
+
+
+def mx_selftest(a, b, sfa, sfb, d, stream=None):
+    """Test hook: block-scaled FP8 MMA, d[128, N] = sum_k a 2^(sfa-127) b 2^(sfb-127) (e4m3 bytes, UE8M0 bytes)."""
+    N, K = b.shape
+    _check(lib().b200_mx_selftest(_p(a), _p(b), _p(sfa), _p(sfb), _p(d), N, K, _stream(stream)), "mx_selftest")
 
 
 def moe_gate_logits_tc(xq, xs, gate_w, chain_blocks=0, stream=None):

@@ -21,7 +21,7 @@ OBJDIR = os.path.join(HERE, "build")
 LIB = os.path.join(LIBDIR, "libb200moedsa.so")
 
 SOURCES = ["runtime.cu", "moe_route.cu", "moe_route_tc.cu", "moe_f32.cu", "moe_fp8.cu", "moe_ep.cu", "dsa_f32.cu", "dsa_bf16.cu", "dsa_bf16_pair.cu",
-           "umma_selftest.cu", "wait_selftest.cu", "ref_shims.cu"]
+           "umma_selftest.cu", "wait_selftest.cu", "mx_selftest.cu", "ref_shims.cu"]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

@@ -227,6 +227,39 @@ __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t adesc, uint64_t
         ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Block-scaled FP8 MMA (kind::mxf8f6f4): D (+)= (A * SFA) * (B * SFB)^T over K = 32, one UE8M0 scale (2^(byte-127))
+// per row of A and per row of B.  The scales live in TMEM: a 32-bit column holds the scale bytes of four
+// consecutive K = 32 steps, byte `sf_id` of the instruction descriptor picks the step; rows r of a 128-row
+// operand sit on lane r % 32 of column r / 32 (same data in all four lane quadrants).
+__device__ __forceinline__ void mma_mxf8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+// Power-of-two block scale: the smallest power of two >= amax / 448 (at least 2^-126, at most 2^127; 1 for an
+// all-zero block).  Bit arithmetic on the correctly rounded quotient, so that host and device agree exactly.
+__host__ __device__ inline float pow2_scale_bits(float quotient) {
+    union { float f; uint32_t u; } c;
+    c.f = quotient;
+    uint32_t e = (c.u >> 23) & 0xFFu;
+    if (e == 0) e = 1;
+    else if (c.u & 0x7FFFFFu) e += 1;
+    if (e > 254) e = 254;
+    c.u = e << 23;
+    return c.f;
+}
+// Instruction descriptor of the block-scaled MMA: e4m3 x e4m3, both K-major, UE8M0 scales, fp32 accumulate.
+__host__ __device__ constexpr uint32_t make_idesc_mx(uint32_t M, uint32_t N, uint32_t a_sf_id, uint32_t b_sf_id) {
+    return (b_sf_id << 4) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24) | (a_sf_id << 29);
+}
+// Shared memory -> TMEM: 32 rows x 16 bytes (four core matrices of 8 rows, 128 bytes apart) into 32 lanes x 4
+// columns, replicated into all four lane quadrants.  The layout the scale factors of a 128-row operand use.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                         uint32_t accumulate) {
     asm volatile(

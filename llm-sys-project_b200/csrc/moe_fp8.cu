@@ -79,6 +79,7 @@ struct GemmSmem {
     uint64_t tmem_full[2];
     uint64_t tmem_empty[2];
     uint64_t amax_bar[2];
+    uint64_t sf_full[STAGES];      // block-scaled kernel only: the stage's scale factors are in shared memory
     uint32_t tmem_base;
     int abort_flag;
     int total_tiles;
@@ -89,6 +90,10 @@ struct GemmSmem {
 
 constexpr size_t GEMM_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + sizeof(GemmSmem);
 static_assert(GEMM_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
+// block-scaled kernel: per stage one 512-byte scale atom for the 128 rows of A and two for the 256 rows of B
+constexpr int SF_BYTES = 1536;
+constexpr size_t GEMM_MX_SMEM_BYTES = GEMM_SMEM_BYTES + (size_t)STAGES * SF_BYTES;
+static_assert(GEMM_MX_SMEM_BYTES <= 232448, "shared memory budget of one CTA (block-scaled kernel)");
 
 struct GemmParams {
     const float* a_scale;      // [rows, nkb]
@@ -601,6 +606,346 @@ done:
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
 }
 
+// -------------------------------------------------------------------------------------------------
+// The same grouped GEMMs for power-of-two scales (B200_MOE_POW2_SCALES) on the hardware block-scaled MMA
+// (tcgen05.mma kind::mxf8f6f4.block_scale, UE8M0 scale = the exponent byte of the fp32 scale): the tensor core
+// multiplies every 32-deep slice of a row by its scale itself, so the accumulator of a tile stays in TMEM
+// for the whole K loop, nothing is promoted in software and the K-block period is the MMA's own (or the
+// weight stream's).  Differences from the kernel above:
+//   * warp 10 builds the scale factors of every stage in shared memory: a 512-byte atom for the 128 rows of A
+//     (row r -> byte (r % 32) * 16 + (r / 32) * 4 + step, four K = 32 steps of the 128-deep block share the
+//     scale) and two atoms for the 256 rows of B (all rows of a 128-column weight block share its scale); it
+//     also checks that every scale it sees is a power of two (B200_BAD_SCALE otherwise);
+//   * the MMA warp copies the atoms into TMEM (tcgen05.cp 32x128b.warpx4: 4 + 8 columns per stage, at columns
+//     256 + 16 stage) and issues the four MMAs of the K block with scale ids 0..3;
+//   * ONE 256-column accumulator: the eight epilogue warps pull a finished tile into registers (128 columns
+//     per thread) and free it at once, so the next tile's MMAs run under the epilogue;
+//   * GEMM1 requantises with a power-of-two scale as well.
+// Single-CTA tiles only.
+// -------------------------------------------------------------------------------------------------
+template <int MODE>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const GemmParams p) {
+    static_assert(NUM_PROMO_WARPS == 8, "the block-scaled kernel is written for eight epilogue warps");
+    constexpr int W_SF = W_MMA0 + 1;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* sf_area = tiles + (size_t)STAGES * STAGE_BYTES;
+    GemmSmem* sm = reinterpret_cast<GemmSmem*>(sf_area + (size_t)STAGES * SF_BYTES);
+    volatile int* abort_flag = &sm->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int Kdim = (MODE == 1) ? p.D : p.I;
+    const int nkb = Kdim / BK;
+    const int NT = (MODE == 1) ? p.I / 128 : p.D / 256;     // N tiles per expert
+    const int w_rows = (MODE == 1) ? 2 * p.I : p.D;         // weight rows per expert
+    const int walkers = (int)gridDim.x, walker = (int)blockIdx.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            ptx::mbar_init(&sm->full[s], 1);
+            ptx::mbar_init(&sm->empty[s], 1);
+            ptx::mbar_init(&sm->sf_full[s], 1);
+        }
+        ptx::mbar_init(&sm->tmem_full[0], 1);
+        ptx::mbar_init(&sm->tmem_empty[0], NUM_PROMO_WARPS);
+        for (int a = 0; a < 2; a++) ptx::mbar_init(&sm->amax_bar[a], NUM_PROMO_WARPS);
+        sm->abort_flag = 0;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 0) {
+        int running = 0;
+        for (int e0 = 0; e0 < p.E; e0 += 32) {
+            const int e = e0 + lane;
+            int t = 0;
+            if (e < p.E) t = ((p.offsets[e + 1] - p.offsets[e] + BM - 1) / BM) * NT;
+            int incl = t;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, incl, o);
+                if (lane >= o) incl += v;
+            }
+            if (e < p.E) sm->tile_prefix[e] = running + incl - t;
+            running += __shfl_sync(0xffffffffu, incl, 31);
+        }
+        if (lane == 0) { sm->tile_prefix[p.E] = running; sm->total_tiles = running; }
+    }
+    if (warp == W_MMA0) { ptx::tmem_alloc(&sm->tmem_base, 512); ptx::tmem_relinquish(); }
+    if (warp == W_TMA && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = sm->tmem_base;
+    const int total_tiles = sm->total_tiles;
+
+    auto locate = [&](int tile, int& e, int& m_tile, int& n_tile, int& cnt) {
+        int lo = 0, hi = p.E;
+        while (hi - lo > 1) {
+            int mid = (lo + hi) >> 1;
+            if (sm->tile_prefix[mid] <= tile) lo = mid; else hi = mid;
+        }
+        e = lo;
+        cnt = p.offsets[e + 1] - p.offsets[e];
+        int mt = (cnt + BM - 1) / BM;
+        int local = tile - sm->tile_prefix[e];
+        n_tile = local / mt;
+        m_tile = local - n_tile * mt;
+    };
+    // one lane polls the barrier, the warp follows
+    auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        int ok = 1;
+        if (lane == 0) ok = ptx::mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        __syncwarp();
+        return ok != 0;
+    };
+
+    if (warp >= NUM_PROMO_WARPS) {
+        ptx::setmaxnreg_dec<AUX_REGS>();
+      if (warp == W_TMA) {
+        // ===================== TMA producer (operand tiles) =====================
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            for (int tile = walker; tile < total_tiles; tile += walkers) {
+                int e, m_tile, n_tile, cnt;
+                locate(tile, e, m_tile, n_tile, cnt);
+                const int row0 = p.offsets[e] + m_tile * BM;
+                const long long wrow0 = (long long)e * w_rows;
+                for (int kb = 0; kb < nkb; kb++) {
+                    if (!ptx::mbar_wait_relaxed(&sm->empty[s], ph ^ 1, abort_flag, 200)) goto done;
+                    uint8_t* a_dst = tiles + (size_t)s * STAGE_BYTES;
+                    uint8_t* b_dst = a_dst + A_BYTES;
+                    ptx::mbar_expect_tx(&sm->full[s], STAGE_BYTES);
+                    ptx::tma_load_2d(a_dst, &tmap_a, &sm->full[s], kb * BK, row0);
+                    if (p.packed) {
+                        ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], 0, (((e * NT + n_tile) * nkb) + kb) * BN);
+                    } else if (MODE == 1) {
+                        const int j0 = n_tile * 128;
+#pragma unroll
+                        for (int bx = 0; bx < 2 * NQ; bx++)
+                            ptx::tma_load_2d(b_dst + bx * (QCOLS / 2) * 128, &tmap_b, &sm->full[s], kb * BK,
+                                             (int)(wrow0 + ((bx & 1) ? p.I : 0) + j0 + (QCOLS / 2) * (bx >> 1)));
+                    } else {
+                        ptx::tma_load_2d(b_dst, &tmap_b, &sm->full[s], kb * BK, (int)(wrow0 + n_tile * 256));
+                    }
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+            }
+        }
+      } else if (warp == W_MMA0) {
+        // ===================== scale copies + MMAs =====================
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0, tph = 0;
+            for (int tile = walker; tile < total_tiles; tile += walkers) {
+                // the epilogue warps hold the previous tile in registers
+                if (!ptx::mbar_wait(&sm->tmem_empty[0], tph ^ 1, abort_flag)) goto done;
+                ptx::tc_fence_after();
+                for (int kb = 0; kb < nkb; kb++) {
+                    if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
+                    if (!ptx::mbar_wait(&sm->sf_full[s], ph, abort_flag)) goto done;
+                    ptx::tc_fence_after();
+                    const uint32_t a_addr = ptx::smem_u32(tiles + (size_t)s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_BYTES;
+                    const uint32_t sf_addr = ptx::smem_u32(sf_area + (size_t)s * SF_BYTES);
+                    const uint32_t tsfa = tmem_base + BN + 16 * s, tsfb = tsfa + 4;
+                    ptx::tmem_cp_32x128b_warpx4(tsfa, ptx::make_smem_desc(sf_addr, 16, 128, 0));
+                    ptx::tmem_cp_32x128b_warpx4(tsfb, ptx::make_smem_desc(sf_addr + 512, 16, 128, 0));
+                    ptx::tmem_cp_32x128b_warpx4(tsfb + 4, ptx::make_smem_desc(sf_addr + 1024, 16, 128, 0));
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; k4++) {
+                        const uint64_t ad = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
+                        const uint64_t bd = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
+                        ptx::mma_mxf8(tmem_base, ad, bd, ptx::make_idesc_mx(BM, BN, k4, k4), tsfa, tsfb,
+                                      (kb > 0 || k4 > 0) ? 1u : 0u);
+                    }
+                    ptx::tc_commit(&sm->empty[s]);          // operand tiles, scale atoms and their TMEM copies reusable
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                ptx::tc_commit(&sm->tmem_full[0]);
+                tph ^= 1;
+            }
+        }
+      } else if (warp == W_SF) {
+        // ===================== scale factors of every stage =====================
+        int s = 0; uint32_t ph = 0;
+        uint32_t bad = 0;
+        auto expo = [&](float f) -> uint32_t {
+            const uint32_t b = __float_as_uint(f);
+            bad |= (b & 0x807FFFFFu) | (((b >> 23) == 0u) ? 1u : 0u);     // sign, mantissa bits, zero / denormal
+            return ((b >> 23) & 0xFFu) * 0x01010101u;                    // the UE8M0 byte, once per K = 32 step
+        };
+        const int nkb_w = Kdim / 128;
+        for (int tile = walker; tile < total_tiles; tile += walkers) {
+            int e, m_tile, n_tile, cnt;
+            locate(tile, e, m_tile, n_tile, cnt);
+            const float* a_sc[4];
+            bool ok[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int r = m_tile * BM + lane + 32 * q;
+                ok[q] = r < cnt;
+                a_sc[q] = p.a_scale + (size_t)(ok[q] ? (long long)p.offsets[e] + r : 0) * nkb;
+            }
+            const float* w_sc0;
+            const float* w_sc1;
+            if (MODE == 1) {
+                const float* base = p.w_scale + (size_t)e * (2 * p.I / 128) * nkb_w;
+                w_sc0 = base + (size_t)n_tile * nkb_w;                     // gate rows' block
+                w_sc1 = base + (size_t)(p.I / 128 + n_tile) * nkb_w;       // up rows' block
+            } else {
+                const float* base = p.w_scale + (size_t)e * (p.D / 128) * nkb_w;
+                w_sc0 = base + (size_t)(n_tile * 2) * nkb_w;               // columns 0..127 of the tile
+                w_sc1 = w_sc0 + nkb_w;                                     // columns 128..255
+            }
+            float an[4], w0n = w_sc0[0], w1n = w_sc1[0];
+#pragma unroll
+            for (int q = 0; q < 4; q++) an[q] = ok[q] ? a_sc[q][0] : 1.0f;
+            for (int kb = 0; kb < nkb; kb++) {
+                const float a0 = an[0], a1 = an[1], a2 = an[2], a3 = an[3], w0 = w0n, w1 = w1n;
+                if (kb + 1 < nkb) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) an[q] = ok[q] ? a_sc[q][kb + 1] : 1.0f;
+                    w0n = w_sc0[kb + 1];
+                    w1n = w_sc1[kb + 1];
+                }
+                if (!warp_wait(&sm->empty[s], ph ^ 1)) goto done;
+                const uint32_t sfp = ptx::smem_u32(sf_area + (size_t)s * SF_BYTES) + lane * 16;
+                const uint32_t g = expo(w0), u = expo(w1);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sfp), "r"(expo(a0)), "r"(expo(a1)), "r"(expo(a2)), "r"(expo(a3)) : "memory");
+                if (MODE == 1) {
+                    // accumulator columns [gate 64 | up 64 | gate 64 | up 64]
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sfp + 512), "r"(g), "r"(g), "r"(u), "r"(u) : "memory");
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sfp + 1024), "r"(g), "r"(g), "r"(u), "r"(u) : "memory");
+                } else {
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sfp + 512), "r"(g), "r"(g), "r"(g), "r"(g) : "memory");
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sfp + 1024), "r"(u), "r"(u), "r"(u), "r"(u) : "memory");
+                }
+                ptx::fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&sm->sf_full[s]);
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+        }
+        if (__any_sync(0xffffffffu, bad != 0) && lane == 0) atomicExch(p.status, B200_BAD_SCALE);
+      }
+    } else {
+        // ===================== epilogue (warps 0-7) =====================
+        ptx::setmaxnreg_inc<PROMO_REGS>();
+        const int wq = warp >> 2;                         // column half of the accumulator
+        const int row = (warp & 3) * 32 + lane;           // TMEM lane = tile row
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        uint32_t fph = 0;
+        int tile_par = 0; uint32_t amax_ph[2] = {0, 0};
+        for (int tile = walker; tile < total_tiles; tile += walkers) {
+            int e, m_tile, n_tile, cnt;
+            locate(tile, e, m_tile, n_tile, cnt);
+            const int trow0 = m_tile * BM;
+            const long long grow = (long long)p.offsets[e] + trow0 + row;         // sorted row
+            const bool row_ok = (trow0 + row) < cnt;
+            const bool warp_valid = (trow0 + (warp & 3) * 32) < cnt;              // any valid row in this warp's 32
+            float accv[QCOLS];
+            if (!warp_wait(&sm->tmem_full[0], fph)) goto done;
+            fph ^= 1;
+            ptx::tc_fence_after();
+            if (warp_valid) {
+                const uint32_t t0 = tmem_base + lane_addr + wq * QCOLS;
+#pragma unroll
+                for (int c = 0; c < QCOLS / 32; c++) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(t0 + 32 * c, r);
+                    ptx::tc_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) accv[32 * c + i] = __uint_as_float(r[i]);
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[0]);      // the tile is in registers: the MMAs may go on
+
+            if (MODE == 1) {
+                constexpr int AC = QCOLS / 2;          // activation columns of this thread
+                float amax = 0.0f;
+                if (warp_valid) {
+#pragma unroll
+                    for (int i = 0; i < AC; i++) {
+                        const float g = accv[i], u = accv[AC + i];
+                        const float a = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        accv[i] = a;
+                        amax = fmaxf(amax, fabsf(a));
+                    }
+                }
+                sm->amax[tile_par][wq][row] = amax;
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&sm->amax_bar[tile_par]);
+                if (!warp_wait(&sm->amax_bar[tile_par], amax_ph[tile_par])) goto done;
+                amax_ph[tile_par] ^= 1;
+#pragma unroll
+                for (int g = 0; g < NQ; g++) amax = fmaxf(amax, sm->amax[tile_par][g][row]);
+                if (row_ok) {
+                    // power-of-two scale: the reciprocal is exact
+                    const float scale = amax > 0.0f ? ptx::pow2_scale_bits(__fdiv_rn(amax, 448.0f)) : 1.0f;
+                    const float inv = __fdiv_rn(1.0f, scale);
+                    uint32_t packed[AC / 4];
+#pragma unroll
+                    for (int i = 0; i < AC / 4; i++) {
+                        const float a0 = accv[4 * i], a1 = accv[4 * i + 1], a2 = accv[4 * i + 2], a3 = accv[4 * i + 3];
+                        packed[i] = (uint32_t)__nv_cvt_float_to_fp8(a0 * inv, __NV_SATFINITE, __NV_E4M3) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(a1 * inv, __NV_SATFINITE, __NV_E4M3) << 8) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(a2 * inv, __NV_SATFINITE, __NV_E4M3) << 16) |
+                                    ((uint32_t)__nv_cvt_float_to_fp8(a3 * inv, __NV_SATFINITE, __NV_E4M3) << 24);
+                    }
+                    uint4* dst = reinterpret_cast<uint4*>(p.act_q + grow * p.I + n_tile * 128 + wq * AC);
+#pragma unroll
+                    for (int i = 0; i < AC / 16; i++)
+                        dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+                    if (wq == 0) p.act_s[grow * (p.I / 128) + n_tile] = scale;
+                }
+                tile_par ^= 1;
+            } else if (warp_valid) {
+                const float w = row_ok ? p.row_w[grow] : 0.0f;
+                float (*st)[SW + 4] = sm->stage[warp];
+                constexpr int SEGS = SW / 4;
+                const int sub_row = lane / SEGS, seg = lane % SEGS;
+                const int tok = (MODE == 2 && row_ok) ? p.row_tok[grow] : -1;
+                const long long grow0 = (long long)p.offsets[e] + trow0 + (warp & 3) * 32;
+                const int rows_ok = min(32, cnt - (trow0 + (warp & 3) * 32));
+                float* const out_col = p.out + n_tile * 256 + wq * QCOLS;
+#pragma unroll
+                for (int pass = 0; pass < QCOLS / SW; pass++) {
+                    __syncwarp();
+#pragma unroll
+                    for (int q = 0; q < SEGS; q++) {
+                        const float* a4 = accv + pass * SW + q * 4;
+                        *reinterpret_cast<float4*>(&st[lane][q * 4]) = make_float4(w * a4[0], w * a4[1], w * a4[2], w * a4[3]);
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int k = 0; k < SEGS; k++) {
+                        const int r = (32 / SEGS) * k + sub_row;
+                        const float4 x4 = *reinterpret_cast<const float4*>(&st[r][seg * 4]);
+                        if (MODE == 2) {
+                            const int tok_r = __shfl_sync(0xffffffffu, tok, r);
+                            if (tok_r >= 0)
+                                red_add_v4(out_col + (size_t)tok_r * p.D + pass * SW + seg * 4, x4.x, x4.y, x4.z, x4.w);
+                        } else if (r < rows_ok) {
+                            *reinterpret_cast<float4*>(out_col + (size_t)(grow0 + r) * p.D + pass * SW + seg * 4) = x4;
+                        }
+                    }
+                }
+            }
+        }
+    }
+done:
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == W_MMA0) ptx::tmem_dealloc(tmem_base, 512);
+    if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
+}
+
 // Deterministic combine: out[t,:] = sum over the token's K slots, in ascending expert order (ties cannot
 // occur: an expert appears at most once per token), of rows[row_of_pair[t*K+k],:].  One block per token.
 __global__ void __launch_bounds__(256)
@@ -766,14 +1111,17 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
 
     static bool attr_done[64] = {false};
     if (b200_first_call_on_device(attr_done)) {
-        const void* kernels[6] = {(const void*)grouped_gemm_fp8_kernel<1, false>, (const void*)grouped_gemm_fp8_kernel<2, false>,
+        const void* kernels[9] = {(const void*)grouped_gemm_fp8_kernel<1, false>, (const void*)grouped_gemm_fp8_kernel<2, false>,
                                   (const void*)grouped_gemm_fp8_kernel<3, false>, (const void*)grouped_gemm_fp8_kernel<1, true>,
-                                  (const void*)grouped_gemm_fp8_kernel<2, true>, (const void*)grouped_gemm_fp8_kernel<3, true>};
-        for (int i = 0; i < 6; i++)
-            B200_CUDA_TRY(cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM_BYTES));
+                                  (const void*)grouped_gemm_fp8_kernel<2, true>, (const void*)grouped_gemm_fp8_kernel<3, true>,
+                                  (const void*)grouped_gemm_mx_kernel<1>, (const void*)grouped_gemm_mx_kernel<2>,
+                                  (const void*)grouped_gemm_mx_kernel<3>};
+        for (int i = 0; i < 9; i++)
+            B200_CUDA_TRY(cudaFuncSetAttribute(kernels[i], cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)(i < 6 ? GEMM_SMEM_BYTES : GEMM_MX_SMEM_BYTES)));
         // setmaxnreg.inc waits without bound for registers that only setmaxnreg.dec of the same CTA frees:
         // never launch a build whose compiled register count breaks the balance the budgets assume
-        for (int i = 0; i < 6; i++) {
+        for (int i = 0; i < 9; i++) {
             cudaFuncAttributes a{};
             B200_CUDA_TRY(cudaFuncGetAttributes(&a, kernels[i]));
             const int n = a.numRegs;
@@ -792,19 +1140,25 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
     // (config 3: GEMM1 3.0 vs 2.2 ms; 32 experts x 1024 rows: 1.9 vs 1.3 ms): the K-block period is set by the
     // promotion of the accumulator stage through tcgen05.ld, which is the same per SM in both shapes, not by
     // shared-memory bandwidth, and a pair idles half of its rows on experts with fewer than 129 rows.
+    const bool mx = (cfg->flags & B200_MOE_POW2_SCALES) != 0;      // power-of-two scales: hardware block-scaled MMA
     bool pair = (cfg->flags & B200_MOE_CTA_PAIR_TILES) != 0;
-    if (cfg->flags & B200_MOE_SINGLE_CTA_TILES) pair = false;
+    if ((cfg->flags & B200_MOE_SINGLE_CTA_TILES) || mx) pair = false;
     if (ws->sm_count < 2) pair = false;
     const unsigned grid = pair ? (unsigned)(ws->sm_count / 2) * 2 : (unsigned)ws->sm_count;
     auto launch = [&](int mode, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p) -> int {
         cudaLaunchConfig_t lc = {};
-        lc.gridDim = dim3(grid); lc.blockDim = dim3(GEMM_THREADS); lc.dynamicSmemBytes = GEMM_SMEM_BYTES; lc.stream = stream;
+        lc.gridDim = dim3(grid); lc.blockDim = dim3(GEMM_THREADS); lc.stream = stream;
+        lc.dynamicSmemBytes = mx ? GEMM_MX_SMEM_BYTES : GEMM_SMEM_BYTES;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
         lc.attrs = attr; lc.numAttrs = pair ? 1 : 0;
         cudaError_t err;
-        if (pair) {
+        if (mx) {
+            if (mode == 1)      err = cudaLaunchKernelEx(&lc, grouped_gemm_mx_kernel<1>, ta, tb, p);
+            else if (mode == 2) err = cudaLaunchKernelEx(&lc, grouped_gemm_mx_kernel<2>, ta, tb, p);
+            else                err = cudaLaunchKernelEx(&lc, grouped_gemm_mx_kernel<3>, ta, tb, p);
+        } else if (pair) {
             if (mode == 1)      err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<1, true>, ta, tb, p);
             else if (mode == 2) err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<2, true>, ta, tb, p);
             else                err = cudaLaunchKernelEx(&lc, grouped_gemm_fp8_kernel<3, true>, ta, tb, p);

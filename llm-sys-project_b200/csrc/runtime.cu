@@ -26,6 +26,7 @@ const char* b200_status_string(int s) {
         case B200_TIMEOUT: return "device-side wait timed out";
         case B200_NCCL_ERROR: return "NCCL error";
         case B200_BAD_ARG: return "bad argument";
+        case B200_BAD_SCALE: return "a scale is not a power of two";
     }
     return "unknown status";
 }
@@ -146,12 +147,18 @@ __global__ void fill_normal_bf16_kernel(__nv_bfloat16* dst, long long n, unsigne
     for (; i < n; i += stride) dst[i] = __float2bfloat16_rn(synth_normal(seed, (unsigned long long)i, factor));
 }
 
-__device__ inline float block_scale_of(float amax) { return amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f; }
+template <bool POW2>
+__device__ inline float block_scale_of(float amax) {
+    if (!(amax > 0.0f)) return 1.0f;
+    const float q = __fdiv_rn(amax, 448.0f);
+    return POW2 ? ptx::pow2_scale_bits(q) : q;
+}
 __device__ inline uint8_t to_e4m3(float x) {
     return (uint8_t)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
 }
 
 // One block per 128x128 weight block: generate, amax, quantise.
+template <bool POW2>
 __global__ void fill_normal_fp8_w128_kernel(uint8_t* q, float* scales, long long rows, int cols,
                                             unsigned long long seed, float factor) {
     __shared__ float red[32];
@@ -174,7 +181,7 @@ __global__ void fill_normal_fp8_w128_kernel(uint8_t* q, float* scales, long long
     __syncthreads();
     amax = red[0];
     for (int w = 1; w < 8; w++) amax = fmaxf(amax, red[w]);
-    float s = block_scale_of(amax);
+    float s = block_scale_of<POW2>(amax);
     if (threadIdx.x == 0) scales[blk] = s;
 #pragma unroll 4
     for (int j = 0; j < 64; j++) {
@@ -186,6 +193,7 @@ __global__ void fill_normal_fp8_w128_kernel(uint8_t* q, float* scales, long long
 }
 
 // Quantisers over fp32 inputs.
+template <bool POW2>
 __global__ void quant_act_1x128_kernel(const float* x, uint8_t* q, float* scales, long long rows, int cols) {
     // one warp per 1x128 block; lane holds 4 consecutive values
     int nb = cols / 128;
@@ -198,7 +206,7 @@ __global__ void quant_act_1x128_kernel(const float* x, uint8_t* q, float* scales
     const float4 v = *reinterpret_cast<const float4*>(x + r * cols + (long long)b * 128 + lane * 4);
     float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    float s = block_scale_of(amax);
+    float s = block_scale_of<POW2>(amax);
     if (lane == 0) scales[gw] = s;
     uchar4 o4;
     o4.x = to_e4m3(__fdiv_rn(v.x, s));
@@ -208,6 +216,7 @@ __global__ void quant_act_1x128_kernel(const float* x, uint8_t* q, float* scales
     *reinterpret_cast<uchar4*>(q + r * cols + (long long)b * 128 + lane * 4) = o4;
 }
 
+template <bool POW2>
 __global__ void quant_weight_128x128_kernel(const float* w, uint8_t* q, float* scales, long long rows, int cols) {
     __shared__ float red[32];
     int cb = cols / 128;
@@ -228,7 +237,7 @@ __global__ void quant_weight_128x128_kernel(const float* w, uint8_t* q, float* s
     __syncthreads();
     amax = red[0];
     for (int wi = 1; wi < 8; wi++) amax = fmaxf(amax, red[wi]);
-    float s = block_scale_of(amax);
+    float s = block_scale_of<POW2>(amax);
     if (threadIdx.x == 0) scales[blk] = s;
 #pragma unroll 4
     for (int j = 0; j < 64; j++) {
@@ -266,41 +275,70 @@ int b200_fill_normal_bf16(uint16_t* dst, long long n, unsigned long long seed, f
     return B200_OK;
 }
 
-int b200_fill_normal_fp8_w128(uint8_t* q, float* scales, long long rows, int cols, unsigned long long seed,
-                              float sigma, b200_stream_t stream) {
+}  // extern "C"
+static int fill_normal_fp8_w128_impl(uint8_t* q, float* scales, long long rows, int cols, unsigned long long seed,
+                                     float sigma, bool pow2, b200_stream_t stream) {
     if (!q || !scales) return B200_BAD_ARG;
     if (rows <= 0 || cols <= 0 || rows % 128 || cols % 128) return B200_BAD_SHAPE;
     long long blocks = (rows / 128) * (cols / 128);
     if (blocks > 0x7fffffffLL) return B200_BAD_SHAPE;
-    fill_normal_fp8_w128_kernel<<<(unsigned)blocks, 256, 0, stream>>>(q, scales, rows, cols, seed, sigma / SYNTH_SD);
+    if (pow2) fill_normal_fp8_w128_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(q, scales, rows, cols, seed, sigma / SYNTH_SD);
+    else      fill_normal_fp8_w128_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(q, scales, rows, cols, seed, sigma / SYNTH_SD);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 
-int b200_quant_act_1x128(const float* x, uint8_t* q, float* scales, long long rows, int cols, b200_stream_t stream) {
+static int quant_act_1x128_impl(const float* x, uint8_t* q, float* scales, long long rows, int cols, bool pow2,
+                               b200_stream_t stream) {
     if (!x || !q || !scales) return B200_BAD_ARG;
     if (rows < 0 || cols <= 0 || cols % 128) return B200_BAD_SHAPE;
     if (rows == 0) return B200_OK;
     long long warps = rows * (cols / 128);
     long long blocks = (warps + 7) / 8;
     if (blocks > 0x7fffffffLL) return B200_BAD_SHAPE;
-    quant_act_1x128_kernel<<<(unsigned)blocks, 256, 0, stream>>>(x, q, scales, rows, cols);
+    if (pow2) quant_act_1x128_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(x, q, scales, rows, cols);
+    else      quant_act_1x128_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(x, q, scales, rows, cols);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
 }
 
-int b200_quant_weight_128x128(const float* w, uint8_t* q, float* scales, long long rows, int cols,
-                              b200_stream_t stream) {
+static int quant_weight_128x128_impl(const float* w, uint8_t* q, float* scales, long long rows, int cols, bool pow2,
+                                    b200_stream_t stream) {
     if (!w || !q || !scales) return B200_BAD_ARG;
     if (rows <= 0 || cols <= 0 || rows % 128 || cols % 128) return B200_BAD_SHAPE;
     long long blocks = (rows / 128) * (cols / 128);
     if (blocks > 0x7fffffffLL) return B200_BAD_SHAPE;
-    quant_weight_128x128_kernel<<<(unsigned)blocks, 256, 0, stream>>>(w, q, scales, rows, cols);
+    if (pow2) quant_weight_128x128_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(w, q, scales, rows, cols);
+    else      quant_weight_128x128_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(w, q, scales, rows, cols);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
     return B200_OK;
+}
+
+extern "C" {
+int b200_fill_normal_fp8_w128(uint8_t* q, float* scales, long long rows, int cols, unsigned long long seed,
+                              float sigma, b200_stream_t stream) {
+    return fill_normal_fp8_w128_impl(q, scales, rows, cols, seed, sigma, false, stream);
+}
+int b200_fill_normal_fp8_w128_pow2(uint8_t* q, float* scales, long long rows, int cols, unsigned long long seed,
+                                   float sigma, b200_stream_t stream) {
+    return fill_normal_fp8_w128_impl(q, scales, rows, cols, seed, sigma, true, stream);
+}
+int b200_quant_act_1x128(const float* x, uint8_t* q, float* scales, long long rows, int cols, b200_stream_t stream) {
+    return quant_act_1x128_impl(x, q, scales, rows, cols, false, stream);
+}
+int b200_quant_act_1x128_pow2(const float* x, uint8_t* q, float* scales, long long rows, int cols, b200_stream_t stream) {
+    return quant_act_1x128_impl(x, q, scales, rows, cols, true, stream);
+}
+int b200_quant_weight_128x128(const float* w, uint8_t* q, float* scales, long long rows, int cols,
+                              b200_stream_t stream) {
+    return quant_weight_128x128_impl(w, q, scales, rows, cols, false, stream);
+}
+int b200_quant_weight_128x128_pow2(const float* w, uint8_t* q, float* scales, long long rows, int cols,
+                                   b200_stream_t stream) {
+    return quant_weight_128x128_impl(w, q, scales, rows, cols, true, stream);
 }
 
 }  // extern "C"

@@ -26,6 +26,12 @@ B200_API int b200_wait_selftest(b200_ws* ws, long long* elapsed_ns, b200_stream_
  * Synchronises the stream (timed with CUDA events inside the call); iters K blocks of four MMAs per CTA. */
 B200_API int b200_fp8_mma_rate(int pair, int iters, float* tflops, float* ms, b200_stream_t stream);
 
+/* Block-scaled FP8 MMA self check (kind::mxf8f6f4.block_scale): d[128, N] = sum_k a[m,k] 2^(sfa[m,k/32]-127)
+ * b[n,k] 2^(sfb[n,k/32]-127); a [128, K] and b [N, K] e4m3 bytes, sfa [128, K/32] and sfb [N, K/32] UE8M0 bytes,
+ * N in {128, 256}, K in {128, 256, 384, 512}. */
+B200_API int b200_mx_selftest(const void* a, const void* b, const void* sfa, const void* sfb, float* d, int N, int K,
+                              b200_stream_t stream);
+
 /* The approximate router logits [T, E] of the tensor-core path, for the test that bounds their distance from the
  * fixed-order FMA chains.  chain_blocks: length of the accumulation chains in 128-deep blocks of d (0 = the
  * library's choice, D / 128 = one chain over all of d).  B200_UNSUPPORTED when the shape does not take that path. */

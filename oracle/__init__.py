@@ -63,6 +63,7 @@ def lib():
     L.orc_e4m3_encode_n.argtypes = [f32p, u8p, C.c_int64]
     L.orc_bf16_encode.argtypes = [C.c_float]
     L.orc_bf16_encode.restype = C.c_uint16
+    L.orc_set_pow2_scales.argtypes = [C.c_int]
     L.orc_quant_act_1x128.argtypes = [f32p, C.c_int64, C.c_int, u8p, f32p]
     L.orc_quant_weight_128x128.argtypes = [f32p, C.c_int64, C.c_int, u8p, f32p]
     L.orc_gate_logits_fp8.argtypes = [u8p, f32p, f32p, C.c_int, C.c_int, C.c_int, f32p]
@@ -205,6 +206,19 @@ def bf16_bits(f):
 
 def bf16_to_f32(h):
     return (np.ascontiguousarray(h, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+class pow2_scales:
+    """Context manager: block scales are powers of two (the smallest one >= amax/448) in quant_act, quant_weight
+    and in the requantisation inside moe_fp8_experts / moe_fp8_gemm1_row while it is active."""
+
+    def __enter__(self):
+        lib().orc_set_pow2_scales(1)
+        return self
+
+    def __exit__(self, *exc):
+        lib().orc_set_pow2_scales(0)
+        return False
 
 
 def quant_act(x):

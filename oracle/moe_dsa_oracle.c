@@ -258,7 +258,25 @@ ORC_API float orc_bf16_decode(uint16_t h) {
 
 /* Block scale rule shared by both quantisers: scale = amax/448, or 1 for an
  * all-zero block; q = e4m3(x / scale). */
-static inline float block_scale(float amax) { return amax > 0.0f ? amax / 448.0f : 1.0f; }
+static int g_pow2_scales = 0;
+/* Power-of-two scale rule (the UE8M0 scale format; no reference counterpart): the smallest power of two
+ * >= amax/448, at least 2^-126, at most 2^127.  Applies to both quantisers and to the requantisation inside the
+ * FP8 expert emulation while switched on. */
+ORC_API void orc_set_pow2_scales(int on) { g_pow2_scales = on; }
+static inline float pow2_ceil(float q) {
+    uint32_t u; memcpy(&u, &q, 4);
+    uint32_t e = (u >> 23) & 0xFFu;
+    if (e == 0) e = 1;
+    else if (u & 0x7FFFFFu) e += 1;
+    if (e > 254) e = 254;
+    u = e << 23;
+    float f; memcpy(&f, &u, 4); return f;
+}
+static inline float block_scale(float amax) {
+    if (!(amax > 0.0f)) return 1.0f;
+    float q = amax / 448.0f;
+    return g_pow2_scales ? pow2_ceil(q) : q;
+}
 
 /* Activations: one fp32 scale per 1x128 block of a row.  cols % 128 == 0. */
 ORC_API void orc_quant_act_1x128(const float* x, int64_t rows, int cols, uint8_t* q, float* scales) {

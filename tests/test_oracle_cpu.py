@@ -190,3 +190,24 @@ def test_dsa_bf16_oracle_and_duplicates():
     ob = oracle.dsa_forward_bf16(*b, idx)
     of = oracle.dsa_forward_f32(*[oracle.bf16_to_f32(a) for a in b], idx)
     assert np.array_equal(ob, of)
+
+
+def test_pow2_scale_rule():
+    """Power-of-two block scales: the smallest power of two >= amax/448, 1 for an all-zero block; the quantised
+    values then stay inside the e4m3 range, and the emulation's requantisation follows the same rule."""
+    rng = np.random.default_rng(3)
+    x = (rng.normal(0, 1, (16, 384)) * np.exp2(rng.integers(-30, 30, (16, 1)))).astype(np.float32)
+    x[2, :128] = 0
+    x[3, :128] = np.float32(448.0 * 2.0 ** 5) * np.sign(x[3, :128] + 1e-30)       # quotient exactly 2^5
+    q0, s0 = oracle.quant_act(x)
+    with oracle.pow2_scales():
+        q, s = oracle.quant_act(x)
+        wq, ws = oracle.quant_weight(x[:, :128].repeat(8, axis=0))
+    q1, s1 = oracle.quant_act(x)
+    assert np.array_equal(s0, s1) and np.array_equal(q0, q1)             # the switch is off again
+    m, _ = np.frexp(s)
+    assert np.all(m == 0.5) and np.all(np.frexp(ws)[0] == 0.5)
+    assert np.all(s >= s0) and np.all(s < 2 * s0 * (1 + 1e-6))
+    assert s[2, 0] == 1.0 and s[3, 0] == 2.0 ** 5
+    deq = oracle.e4m3_decode(q) * np.repeat(s, 128, axis=1)
+    assert np.all(np.abs(deq - x) <= np.abs(x) * 2.0 ** -4 + np.repeat(s, 128, axis=1) * 2.0 ** -10)
