@@ -259,6 +259,55 @@ def moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out_dev, n_tokens, thread
             "ref_absmax": float(np.abs(ref).max()), "ids": ids, "toks": toks, "gids": gids}
 
 
+def bench_moe_pow2_variant(b200, torch, oracle, layer, dev, args, threads):
+    """The same layer, the same seeded values, quantised with power-of-two scales (the UE8M0 scale format) and run
+    with MOE_POW2_SCALES: the grouped GEMMs take the hardware block-scaled MMA.  A secondary figure beside the
+    headline (whose scales are amax/448 as the emulation of the reference defines them); checked against the CPU
+    emulation with the same scale rule on a sample of tokens."""
+    c = MOE
+    b200.fill_normal_fp8_w128_(layer.w1q, layer.w1s, 1000, 0.02, pow2=True)
+    b200.fill_normal_fp8_w128_(layer.w2q, layer.w2s, 2000, 0.02, pow2=True)
+    layer.w1p = layer.w2p = None
+    layer.pack()
+    x = torch.empty((c["T"], c["D"]), dtype=torch.float32, device=dev)
+    b200.fill_normal_(x, 4000, 1.0)
+    xq = torch.empty((c["T"], c["D"]), dtype=torch.uint8, device=dev)
+    xs = torch.empty((c["T"], c["D"] // 128), dtype=torch.float32, device=dev)
+    b200.quant_act_1x128(x, xq, xs, pow2=True)
+    del x
+    layer.flags |= b200.MOE_POW2_SCALES
+    out = torch.empty((c["T"], c["D"]), dtype=torch.float32, device=dev)
+    for _ in range(3):
+        layer.forward(xq, xs, out)
+    torch.cuda.synchronize()
+    status = b200.device_status()
+    b200.moe_fp8_profile(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        layer.forward(xq, xs, out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    g1_ms, g2_ms, _ = b200.moe_fp8_profile_read()
+    b200.moe_fp8_profile(False)
+    with oracle.pow2_scales():
+        cpu = moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out, min(args.cpu_tokens, 24), threads)
+    ids, _ = layer.route(xq, xs)
+    counts = torch.bincount(ids.reshape(-1).long(), minlength=c["E"]).cpu().numpy()
+    g1_bytes, active, rows = moe_gemm1_bytes(counts)
+    hbm, _, which = measured_peaks()
+    return {"ms_per_step": ms, "tokens_per_s": c["T"] / (ms * 1e-3), "gemm1_ms": g1_ms, "gemm2_ms": g2_ms,
+            "gemm1_hbm_gbs": g1_bytes / (g1_ms * 1e-3) / 1e9 if g1_ms > 0 else None,
+            "gemm1_hbm_frac": g1_bytes / (g1_ms * 1e-3) / 1e9 / hbm if g1_ms > 0 else None,
+            "gemm_tflops": 6.0 * rows * c["D"] * c["I"] / ((g1_ms + g2_ms) * 1e-3) / 1e12 if g1_ms > 0 else None,
+            "device_status": int(status),
+            "parity": {"checked_tokens": cpu["tokens"], "ok": cpu["ok"], "max_abs_err": cpu["max_abs_err"],
+                       "ref_absmax": cpu["ref_absmax"], "tolerance": f"{RTOL} rel + {ATOL} abs"},
+            "note": "power-of-two scales (MOE_POW2_SCALES): tcgen05.mma kind::mxf8f6f4.block_scale, no software "
+                    "promotion; not the headline configuration"}
+
+
 def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     c = MOE
     layer, xq, xs = build_moe(b200, torch, dev, 1, 0)
@@ -365,6 +414,13 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     cpu = moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out, args.cpu_tokens, threads)
     hbm, bf16_tf, which = measured_peaks()
     fp8_peak = fp8_peak_tflops(b200)
+    pow2 = None
+    if not args.skip_pow2:
+        try:
+            pow2 = bench_moe_pow2_variant(b200, torch, oracle, layer, dev, args, threads)
+        except Exception as exc:                          # a secondary figure never costs the headline
+            pow2 = {"error": str(exc)[:200]}
+            torch.cuda.synchronize()
     g1_bytes, active, rows = moe_gemm1_bytes(counts)
     g2_bytes = (active * (c["D"] * c["I"] + 4 * (c["D"] // 128) * (c["I"] // 128)) + rows * (c["I"] + 4 * c["I"] // 128)
                 + c["T"] * c["D"] * 4)
@@ -396,6 +452,7 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
                              "algorithmic_bytes": int(route_bytes)},
         "kernels": {"gemm1_ms": g1_ms, "gemm2_ms": g2_ms, "other_ms": ms - g1_ms - g2_ms, "token_sweep": sweep,
                     "fp8_peak_tflops_measured": fp8_peak,
+                    "pow2_scales_variant": pow2,
                     "gemm_frac_of_measured_fp8_peak": (6.0 * rows * c["D"] * c["I"] / ((g1_ms + g2_ms) * 1e-3) / 1e12
                                                        / fp8_peak["burst"]) if g1_ms > 0 and fp8_peak else None,
                     "layer_bytes": int(moe_layer_bytes(counts)),
@@ -820,6 +877,8 @@ def main():
     ap.add_argument("--skip-moe", action="store_true")
     ap.add_argument("--cpu-tokens", type=int, default=96)
     ap.add_argument("--cpu-queries", type=int, default=16)
+    ap.add_argument("--skip-pow2", action="store_true",
+                    help="skip the secondary measurement of the power-of-two-scale variant of the MoE layer")
     ap.add_argument("--route-only", action="store_true",
                     help="run only the routing call of the MoE layer at the full token count (profiler captures)")
     ap.add_argument("--small", action="store_true",

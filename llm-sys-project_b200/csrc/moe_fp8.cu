@@ -80,6 +80,7 @@ struct GemmSmem {
     uint64_t tmem_empty[2];
     uint64_t amax_bar[2];
     uint64_t sf_full[STAGES];      // block-scaled kernel only: the stage's scale factors are in shared memory
+    uint64_t pair_go;              // single-CTA tiles launched as clusters of two: the neighbour starts its tile
     uint32_t tmem_base;
     int abort_flag;
     int total_tiles;
@@ -92,6 +93,11 @@ constexpr size_t GEMM_SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * S
 static_assert(GEMM_SMEM_BYTES <= 232448, "shared memory budget of one CTA");
 // block-scaled kernel: per stage one 512-byte scale atom for the 128 rows of A and two for the 256 rows of B
 constexpr int SF_BYTES = 1536;
+// block-scaled kernel: the accumulator is moved into fp32 registers every MX_FLUSH K blocks.  The tensor core's own
+// accumulation over a long chain is less exact than fp32 additions (one chain over K = 7168 put ~1e-4 relative
+// error on GEMM1, enough to flip one e4m3 code in a thousand at the requantisation and to push a few outputs of
+// the full-size layer past the 1e-2 absolute bound); 32 MMAs per chain keep it near fp32.
+constexpr int MX_FLUSH = 8;
 constexpr size_t GEMM_MX_SMEM_BYTES = GEMM_SMEM_BYTES + (size_t)STAGES * SF_BYTES;
 static_assert(GEMM_MX_SMEM_BYTES <= 232448, "shared memory budget of one CTA (block-scaled kernel)");
 
@@ -133,6 +139,22 @@ __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
     return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+// Tiles 2i and 2i+1 run on the two CTAs of a cluster at the same time; when an expert has 129..256 rows they are
+// the two row tiles of one weight slab.  The slab comes from DRAM once only if both CTAs stream it within the
+// time a line stays in L2 (~20 us at full DRAM rate), and without a rendezvous the CTA with the nearly empty row
+// tile gains a few microseconds per tile and is a whole tile ahead after some rounds (measured: every second
+// row tile re-read from DRAM, 11.7 GB instead of 7.8 GB per GEMM1 launch).  So the two producers meet before
+// every tile: each arrives on the neighbour's barrier and waits on its own (bounded).
+__device__ __forceinline__ bool pair_rendezvous(uint64_t* own_bar, uint32_t peer_bar_cluster_addr, uint32_t parity,
+                                                volatile int* abort_flag) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(peer_bar_cluster_addr) : "memory");
+    return ptx::mbar_wait_relaxed(own_bar, parity, abort_flag, 100);
 }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -250,6 +272,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 
     // ---- prologue ---------------------------------------------------------
     const uint32_t crank = PAIR ? cluster_ctarank() : 0u;     // 0 = leader
+    const bool duo = !PAIR && cluster_nctarank() == 2;        // single-CTA tiles, launched two CTAs to a cluster
     const int pair_count = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;     // tile walkers
     const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     if (threadIdx.x == 0) {
@@ -261,6 +284,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             ptx::mbar_init(&sm->tmem_empty[a], PAIR ? 2 * NUM_PROMO_WARPS : NUM_PROMO_WARPS);
             ptx::mbar_init(&sm->amax_bar[a], NUM_PROMO_WARPS);
         }
+        ptx::mbar_init(&sm->pair_go, 1);
         sm->abort_flag = 0;
         ptx::fence_mbar_init();
     }
@@ -292,7 +316,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
     }
     ptx::tc_fence_before();
     __syncthreads();
-    if (PAIR) cluster_sync_all();             // the peer's barriers are initialised before anyone signals them
+    if (PAIR || duo) cluster_sync_all();      // the peer's barriers are initialised before anyone signals them
     ptx::tc_fence_after();
     const uint32_t tmem_base = sm->tmem_base;
     const int total_tiles = sm->total_tiles;
@@ -321,9 +345,15 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
         // ===================== TMA producer =====================
         if (lane == 0) {
             int s = 0; uint32_t ph = 0; int gk = 0; (void)gk;
+            uint32_t go_ph = 0;
+            const uint32_t peer_go = duo ? map_to_cta(&sm->pair_go, cluster_ctarank() ^ 1u) : 0u;
             for (int tile = walker; tile < total_tiles; tile += pair_count) {
                 int e, m_tile, n_tile, cnt;
                 locate(tile, e, m_tile, n_tile, cnt);
+                if (duo && (tile | 1) < total_tiles) {        // the neighbour has a tile in this round too
+                    if (!pair_rendezvous(&sm->pair_go, peer_go, go_ph, abort_flag)) goto done;
+                    go_ph ^= 1;
+                }
                 const int row0 = p.offsets[e] + m_tile * TM + (int)crank * BM;
                 const long long wrow0 = (long long)e * w_rows;
                 for (int kb = 0; kb < nkb; kb++) {
@@ -598,7 +628,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
 done:
     ptx::tc_fence_before();
     __syncthreads();
-    if (PAIR) cluster_sync_all();            // the pair's MMAs, remote arrivals and TMEM reads are over in both CTAs
+    if (PAIR || duo) cluster_sync_all();     // the pair's MMAs, remote arrivals and TMEM reads are over in both CTAs
     if (warp == W_MMA0) {
         if (PAIR) tmem_dealloc2(tmem_base, 512);
         else      ptx::tmem_dealloc(tmem_base, 512);
@@ -618,8 +648,9 @@ done:
 //     also checks that every scale it sees is a power of two (B200_BAD_SCALE otherwise);
 //   * the MMA warp copies the atoms into TMEM (tcgen05.cp 32x128b.warpx4: 4 + 8 columns per stage, at columns
 //     256 + 16 stage) and issues the four MMAs of the K block with scale ids 0..3;
-//   * ONE 256-column accumulator: the eight epilogue warps pull a finished tile into registers (128 columns
-//     per thread) and free it at once, so the next tile's MMAs run under the epilogue;
+//   * ONE 256-column accumulator: the eight epilogue warps add it into registers (128 columns per thread) every
+//     MX_FLUSH K blocks and free it at once, so the next segment's (or tile's) MMAs run under the additions and
+//     the epilogue;
 //   * GEMM1 requantises with a power-of-two scale as well.
 // Single-CTA tiles only.
 // -------------------------------------------------------------------------------------------------
@@ -641,6 +672,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     const int NT = (MODE == 1) ? p.I / 128 : p.D / 256;     // N tiles per expert
     const int w_rows = (MODE == 1) ? 2 * p.I : p.D;         // weight rows per expert
     const int walkers = (int)gridDim.x, walker = (int)blockIdx.x;
+    const bool duo = cluster_nctarank() == 2;               // launched two CTAs to a cluster
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -648,6 +680,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             ptx::mbar_init(&sm->empty[s], 1);
             ptx::mbar_init(&sm->sf_full[s], 1);
         }
+        ptx::mbar_init(&sm->pair_go, 1);
         ptx::mbar_init(&sm->tmem_full[0], 1);
         ptx::mbar_init(&sm->tmem_empty[0], NUM_PROMO_WARPS);
         for (int a = 0; a < 2; a++) ptx::mbar_init(&sm->amax_bar[a], NUM_PROMO_WARPS);
@@ -678,6 +711,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     }
     ptx::tc_fence_before();
     __syncthreads();
+    if (duo) cluster_sync_all();              // the neighbour's barrier is initialised before anyone signals it
     ptx::tc_fence_after();
     const uint32_t tmem_base = sm->tmem_base;
     const int total_tiles = sm->total_tiles;
@@ -709,10 +743,15 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       if (warp == W_TMA) {
         // ===================== TMA producer (operand tiles) =====================
         if (lane == 0) {
-            int s = 0; uint32_t ph = 0;
+            int s = 0; uint32_t ph = 0, go_ph = 0;
+            const uint32_t peer_go = duo ? map_to_cta(&sm->pair_go, cluster_ctarank() ^ 1u) : 0u;
             for (int tile = walker; tile < total_tiles; tile += walkers) {
                 int e, m_tile, n_tile, cnt;
                 locate(tile, e, m_tile, n_tile, cnt);
+                if (duo && (tile | 1) < total_tiles) {        // the neighbour has a tile in this round too
+                    if (!pair_rendezvous(&sm->pair_go, peer_go, go_ph, abort_flag)) goto done;
+                    go_ph ^= 1;
+                }
                 const int row0 = p.offsets[e] + m_tile * BM;
                 const long long wrow0 = (long long)e * w_rows;
                 for (int kb = 0; kb < nkb; kb++) {
@@ -741,10 +780,12 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         if (lane == 0) {
             int s = 0; uint32_t ph = 0, tph = 0;
             for (int tile = walker; tile < total_tiles; tile += walkers) {
-                // the epilogue warps hold the previous tile in registers
+              for (int kb0 = 0; kb0 < nkb; kb0 += MX_FLUSH) {
+                // the epilogue warps have added the previous segment (or tile) into their registers
                 if (!ptx::mbar_wait(&sm->tmem_empty[0], tph ^ 1, abort_flag)) goto done;
                 ptx::tc_fence_after();
-                for (int kb = 0; kb < nkb; kb++) {
+                const int kb1 = min(nkb, kb0 + MX_FLUSH);
+                for (int kb = kb0; kb < kb1; kb++) {
                     if (!ptx::mbar_wait(&sm->full[s], ph, abort_flag)) goto done;
                     if (!ptx::mbar_wait(&sm->sf_full[s], ph, abort_flag)) goto done;
                     ptx::tc_fence_after();
@@ -760,13 +801,14 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                         const uint64_t ad = ptx::make_smem_desc(a_addr + k4 * 32, 16, 1024, 2);
                         const uint64_t bd = ptx::make_smem_desc(b_addr + k4 * 32, 16, 1024, 2);
                         ptx::mma_mxf8(tmem_base, ad, bd, ptx::make_idesc_mx(BM, BN, k4, k4), tsfa, tsfb,
-                                      (kb > 0 || k4 > 0) ? 1u : 0u);
+                                      (kb > kb0 || k4 > 0) ? 1u : 0u);
                     }
                     ptx::tc_commit(&sm->empty[s]);          // operand tiles, scale atoms and their TMEM copies reusable
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 ptx::tc_commit(&sm->tmem_full[0]);
                 tph ^= 1;
+              }
             }
         }
       } else if (warp == W_SF) {
@@ -848,23 +890,27 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const bool row_ok = (trow0 + row) < cnt;
             const bool warp_valid = (trow0 + (warp & 3) * 32) < cnt;              // any valid row in this warp's 32
             float accv[QCOLS];
-            if (!warp_wait(&sm->tmem_full[0], fph)) goto done;
-            fph ^= 1;
-            ptx::tc_fence_after();
-            if (warp_valid) {
-                const uint32_t t0 = tmem_base + lane_addr + wq * QCOLS;
 #pragma unroll
-                for (int c = 0; c < QCOLS / 32; c++) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32(t0 + 32 * c, r);
-                    ptx::tc_wait_ld();
+            for (int i = 0; i < QCOLS; i++) accv[i] = 0.0f;
+            for (int kb0 = 0; kb0 < nkb; kb0 += MX_FLUSH) {
+                if (!warp_wait(&sm->tmem_full[0], fph)) goto done;
+                fph ^= 1;
+                ptx::tc_fence_after();
+                if (warp_valid) {
+                    const uint32_t t0 = tmem_base + lane_addr + wq * QCOLS;
 #pragma unroll
-                    for (int i = 0; i < 32; i++) accv[32 * c + i] = __uint_as_float(r[i]);
+                    for (int c = 0; c < QCOLS / 32; c++) {
+                        uint32_t r[32];
+                        ptx::tmem_ld_32x32(t0 + 32 * c, r);
+                        ptx::tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i++) accv[32 * c + i] += __uint_as_float(r[i]);
+                    }
                 }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[0]);  // the segment is in registers: the MMAs may go on
             }
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&sm->tmem_empty[0]);      // the tile is in registers: the MMAs may go on
 
             if (MODE == 1) {
                 constexpr int AC = QCOLS / 2;          // activation columns of this thread
@@ -942,6 +988,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 done:
     ptx::tc_fence_before();
     __syncthreads();
+    if (duo) cluster_sync_all();              // no remote arrival is in flight towards a CTA that has left
     if (warp == W_MMA0) ptx::tmem_dealloc(tmem_base, 512);
     if (threadIdx.x == 0 && sm->abort_flag) atomicExch(p.status, B200_TIMEOUT);
 }
@@ -1152,7 +1199,14 @@ int run_experts(b200_ws* ws, const Fp8Scratch& s, const uint8_t* xq, const float
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-        lc.attrs = attr; lc.numAttrs = pair ? 1 : 0;
+#ifndef B200_GEMM_CLUSTER2
+#define B200_GEMM_CLUSTER2 1
+#endif
+        // Single-CTA tiles are launched as clusters of two as well: tiles 2i and 2i+1 (the two 128-row tiles of
+        // an expert's weight slab when it has 129..256 rows) then run on SMs of one GPC, behind the same L2
+        // partition, and the slab comes from DRAM once instead of once per die.
+        const bool cluster2 = pair || (B200_GEMM_CLUSTER2 && grid % 2 == 0);
+        lc.attrs = attr; lc.numAttrs = cluster2 ? 1 : 0;
         cudaError_t err;
         if (mx) {
             if (mode == 1)      err = cudaLaunchKernelEx(&lc, grouped_gemm_mx_kernel<1>, ta, tb, p);
