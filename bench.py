@@ -604,10 +604,14 @@ def bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler):
     b200.moe_fp8_profile(True, ws_handle)
     if not peer:
         ep.profile = True
+    else:
+        ep.phase_profile(True)
     ep.forward(xq, xs)
     if not peer:
         phases = ep.phase_ms()
         ep.profile = False
+    else:
+        phases = ep.phase_profile(False)
     g1_ms, g2_ms, _ = b200.moe_fp8_profile_read(ws_handle)
     b200.moe_fp8_profile(False, ws_handle)
     El = c["E"] // world

@@ -215,6 +215,9 @@ struct b200_ep {
     char** d_peer = nullptr;          // device copy of peer[]
     unsigned int step = 0;
     int sm_count = 0;
+    // phase timeline of a step (b200_ep_phase_profile, a test / benchmark hook): events on the launch stream
+    bool prof_on = false;
+    cudaEvent_t prof_ev[7] = {nullptr};
 };
 
 namespace {
@@ -350,7 +353,7 @@ template <bool HALF>
 __global__ void __launch_bounds__(256)
 ep_push_kernel(const EpDev e, float* __restrict__ y, const int* __restrict__ recv_counts, unsigned int* done) {
     __shared__ int s_start[65];
-    __shared__ float s_red[8];
+    __shared__ float s_red[2][8];
     __shared__ bool s_last;
     if (threadIdx.x == 0) {
         int acc = 0;
@@ -360,7 +363,8 @@ ep_push_kernel(const EpDev e, float* __restrict__ y, const int* __restrict__ rec
     __syncthreads();
     const int total = s_start[e.W];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int i = blockIdx.x; i < total; i += gridDim.x) {
+    int it = 0;
+    for (int i = blockIdx.x; i < total; i += gridDim.x, it++) {
         int s = 0;
         while (i >= s_start[s + 1]) s++;
         const int row = i - s_start[s];
@@ -368,29 +372,51 @@ ep_push_kernel(const EpDev e, float* __restrict__ y, const int* __restrict__ rec
         char* dst = e.peer[s] + e.L.back;
         const size_t slot = (size_t)e.rank * e.Tm + row;
         if (HALF) {
+            // The row stays in registers between the maximum and the conversion (up to 8 float4 per thread: D <=
+            // 8192; wider rows read the rest again): one pass over memory, one block barrier per row.
+            constexpr int NPT = 8;
+            const int nvec = e.D / 4;
+            float4 v[NPT];
             float amax = 0.0f;
-            for (int c = threadIdx.x; c < e.D / 4; c += blockDim.x) {
+#pragma unroll
+            for (int k = 0; k < NPT; k++) {
+                const int c = threadIdx.x + k * 256;
+                v[k] = (c < nvec) ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int k = 0; k < NPT; k++)
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)), fmaxf(fabsf(v[k].z), fabsf(v[k].w))));
+            for (int c = threadIdx.x + NPT * 256; c < nvec; c += 256) {
                 const float4 a = src[c];
                 amax = fmaxf(amax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
             }
             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            __syncthreads();                      // s_red of the previous row has been read
-            if (lane == 0) s_red[warp] = amax;
+            float* red = s_red[it & 1];               // two sets: the next row's writers do not wait for this row's readers
+            if (lane == 0) red[warp] = amax;
             __syncthreads();
-            amax = s_red[0];
-            for (int w = 1; w < 8; w++) amax = fmaxf(amax, s_red[w]);
+            amax = red[0];
+            for (int w = 1; w < 8; w++) amax = fmaxf(amax, red[w]);
             const float inv = amax > 0.0f ? 1.0f / amax : 0.0f;
             if (threadIdx.x == 0) reinterpret_cast<float*>(e.peer[s] + e.L.back_scale)[slot] = amax;
-            for (int c = threadIdx.x; c < e.D / 8; c += blockDim.x) {
-                const float4 a = src[2 * c], b = src[2 * c + 1];      // second read: from L1 / L2
-                src[2 * c] = make_float4(0.f, 0.f, 0.f, 0.f);
-                src[2 * c + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                __half2 h0 = __floats2half2_rn(a.x * inv, a.y * inv), h1 = __floats2half2_rn(a.z * inv, a.w * inv);
-                __half2 h2 = __floats2half2_rn(b.x * inv, b.y * inv), h3 = __floats2half2_rn(b.z * inv, b.w * inv);
-                uint4 v;
-                v.x = *reinterpret_cast<uint32_t*>(&h0); v.y = *reinterpret_cast<uint32_t*>(&h1);
-                v.z = *reinterpret_cast<uint32_t*>(&h2); v.w = *reinterpret_cast<uint32_t*>(&h3);
-                reinterpret_cast<uint4*>(dst + slot * e.D * 2)[c] = v;
+            uint2* drow = reinterpret_cast<uint2*>(dst + slot * e.D * 2);
+#pragma unroll
+            for (int k = 0; k < NPT; k++) {
+                const int c = threadIdx.x + k * 256;
+                if (c < nvec) {
+                    src[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const __half2 h0 = __floats2half2_rn(v[k].x * inv, v[k].y * inv), h1 = __floats2half2_rn(v[k].z * inv, v[k].w * inv);
+                    uint2 u;
+                    u.x = *reinterpret_cast<const uint32_t*>(&h0); u.y = *reinterpret_cast<const uint32_t*>(&h1);
+                    drow[c] = u;
+                }
+            }
+            for (int c = threadIdx.x + NPT * 256; c < nvec; c += 256) {
+                const float4 a = src[c];
+                src[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                const __half2 h0 = __floats2half2_rn(a.x * inv, a.y * inv), h1 = __floats2half2_rn(a.z * inv, a.w * inv);
+                uint2 u;
+                u.x = *reinterpret_cast<const uint32_t*>(&h0); u.y = *reinterpret_cast<const uint32_t*>(&h1);
+                drow[c] = u;
             }
         } else {
             for (int c = threadIdx.x; c < e.D / 4; c += blockDim.x) {
@@ -438,28 +464,55 @@ ep_combine_kernel(const EpDev e, const int* __restrict__ pos, const int* __restr
                                         : 1.0f;
     }
     __syncthreads();
+    // the owners that hold a row of this token, in rank order (the order of the sum)
+    __shared__ int s_n;
+    __shared__ size_t s_slot[64];
+    __shared__ float s_sc[64];
+    if (threadIdx.x == 0) {
+        int n = 0;
+        for (int r = 0; r < e.W; r++)
+            if (s_row[r] >= 0) { s_slot[n] = (size_t)r * e.Tm + s_row[r]; s_sc[n] = s_scale[r]; n++; }
+        s_n = n;
+    }
+    __syncthreads();
+    const int nv = s_n;
     const char* back = e.self + e.L.back;
     for (int c = threadIdx.x * 8; c < e.D; c += blockDim.x * 8) {
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int r = 0; r < e.W; r++) {
-            const int row = s_row[r];
-            if (row < 0) continue;
-            const size_t slot = (size_t)r * e.Tm + row;
+        // four rows' loads in flight at a time; the additions stay in rank order
+        for (int r0 = 0; r0 < nv; r0 += 4) {
             if (HALF) {
-                const uint4 v = *reinterpret_cast<const uint4*>(back + (slot * e.D + c) * 2);
-                const __half2* h = reinterpret_cast<const __half2*>(&v);
-                const float sc = s_scale[r];
+                uint4 v[4];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float2 f = __half22float2(h[i]);
-                    acc[2 * i] = fmaf(f.x, sc, acc[2 * i]);
-                    acc[2 * i + 1] = fmaf(f.y, sc, acc[2 * i + 1]);
+                for (int j = 0; j < 4; j++)
+                    if (r0 + j < nv) v[j] = *reinterpret_cast<const uint4*>(back + (s_slot[r0 + j] * e.D + c) * 2);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (r0 + j < nv) {
+                        const __half2* h = reinterpret_cast<const __half2*>(&v[j]);
+                        const float sc = s_sc[r0 + j];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const float2 f = __half22float2(h[i]);
+                            acc[2 * i] = fmaf(f.x, sc, acc[2 * i]);
+                            acc[2 * i + 1] = fmaf(f.y, sc, acc[2 * i + 1]);
+                        }
+                    }
                 }
             } else {
-                const float4* src = reinterpret_cast<const float4*>(back + (slot * e.D + c) * 4);
-                const float4 a = src[0], b = src[1];
-                acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
-                acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+                float4 va[4], vb[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (r0 + j < nv) {
+                        const float4* src = reinterpret_cast<const float4*>(back + (s_slot[r0 + j] * e.D + c) * 4);
+                        va[j] = src[0]; vb[j] = src[1];
+                    }
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (r0 + j < nv) {
+                        acc[0] += va[j].x; acc[1] += va[j].y; acc[2] += va[j].z; acc[3] += va[j].w;
+                        acc[4] += vb[j].x; acc[5] += vb[j].y; acc[6] += vb[j].z; acc[7] += vb[j].w;
+                    }
             }
         }
         float4* dst = reinterpret_cast<float4*>(out + (size_t)t * e.D + c);
@@ -601,6 +654,8 @@ int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float*
     if (T <= 0 || T > c.max_tokens) return B200_BAD_SHAPE;
     ep->step++;
     if (ep->step == 0) ep->step = 1;        // 0 is what the words hold before the first step
+    auto mark = [&](int i) { if (ep->prof_on) cudaEventRecord(ep->prof_ev[i], stream); };
+    mark(0);
     const EpDev e = ep_dev(ep);
     const bool half = !(c.flags & B200_EP_COMBINE_F32);
 
@@ -618,6 +673,7 @@ int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float*
     if (st) return st;
     if (ids_out) B200_CUDA_TRY(cudaMemcpyAsync(ids_out, ep->ids, sizeof(int) * (size_t)T * K, cudaMemcpyDeviceToDevice, stream));
     if (w_out) B200_CUDA_TRY(cudaMemcpyAsync(w_out, ep->wts, sizeof(float) * (size_t)T * K, cudaMemcpyDeviceToDevice, stream));
+    mark(1);
 
     // dispatch: rows to their owners' regions, then the counts
     const int grid = ep->sm_count * 8;
@@ -626,10 +682,12 @@ int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float*
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
 
+    mark(2);
     // owner side
     ep_recv_ready_kernel<<<W, 256, 0, stream>>>(e, ep->recv_counts);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
+    mark(3);
     b200_moe_fp8_config lc{};
     lc.num_tokens = W * c.max_tokens; lc.num_experts = ep->E_local; lc.top_k = K; lc.hidden_dim = D;
     lc.intermediate_dim = c.intermediate_dim; lc.scoring = c.scoring; lc.n_group = 1; lc.topk_group = 1;
@@ -640,16 +698,34 @@ int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float*
                                          reinterpret_cast<const float*>(ep->xbuf + e.L.recv_w), w1, w1s, w2, w2s, ep->y,
                                          &lc, packed != 0, stream);
     if (st) return st;
+    mark(4);
     if (half) ep_push_kernel<true><<<grid, 256, 0, stream>>>(e, ep->y, ep->recv_counts, ep->done + 1);
     else      ep_push_kernel<false><<<grid, 256, 0, stream>>>(e, ep->y, ep->recv_counts, ep->done + 1);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
 
+    mark(5);
     // source side
     if (half) ep_combine_kernel<true><<<T, 256, 0, stream>>>(e, ep->pos, ep->send_counts, T, out);
     else      ep_combine_kernel<false><<<T, 256, 0, stream>>>(e, ep->pos, ep->send_counts, T, out);
     b200_count_launch(1);
     B200_CUDA_TRY(cudaGetLastError());
+    mark(6);
+    return B200_OK;
+}
+
+// Test / benchmark hook (declared in selftest.h): time the phases of the following steps with events on the launch
+// stream.  ms[6] of the last step: route + plan, dispatch, wait for the senders, local experts, push, combine
+// (the last one includes the wait for the owners' partial rows).
+int b200_ep_phase_profile(b200_ep* ep, int enable, float* ms) {
+    if (!ep) return B200_BAD_ARG;
+    if (enable && !ep->prof_ev[0])
+        for (int i = 0; i < 7; i++) B200_CUDA_TRY(cudaEventCreate(&ep->prof_ev[i]));
+    if (ms && ep->prof_on) {
+        B200_CUDA_TRY(cudaEventSynchronize(ep->prof_ev[6]));
+        for (int i = 0; i < 6; i++) B200_CUDA_TRY(cudaEventElapsedTime(&ms[i], ep->prof_ev[i], ep->prof_ev[i + 1]));
+    }
+    ep->prof_on = enable != 0;
     return B200_OK;
 }
 
@@ -674,6 +750,8 @@ int b200_ep_destroy(b200_ep* ep) {
         if (ep->peer_opened[r] && ep->peer[r]) cudaIpcCloseMemHandle(ep->peer[r]);
     if (ep->xbuf) cudaFree(ep->xbuf);
     if (ep->lbuf) cudaFree(ep->lbuf);
+    for (int i = 0; i < 7; i++)
+        if (ep->prof_ev[i]) cudaEventDestroy(ep->prof_ev[i]);
     if (ep->ws) b200_ws_destroy(ep->ws);
     delete ep;
     return B200_OK;

@@ -45,6 +45,10 @@ B200_API int b200_moe_route_last_flagged(b200_ws* ws, b200_stream_t stream, int*
  * GPU can run the step of "rank 0 of 2": the words of the absent rank never arrive, the bounded waits run
  * out, and the step reports B200_TIMEOUT (results are meaningless; every access stays inside the buffers). */
 B200_API int b200_ep_connect_loopback(b200_ep* ep);
+/* Phase timeline of expert-parallel steps (events on the launch stream).  enable != 0 switches it on for the
+ * following steps; ms[6], when given and the timeline was on, receives the last step's route + plan, dispatch,
+ * wait for the senders, local experts, push and combine times. */
+B200_API int b200_ep_phase_profile(b200_ep* ep, int enable, float* ms);
 
 #ifdef __cplusplus
 }

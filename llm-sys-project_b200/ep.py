@@ -284,6 +284,15 @@ class PeerExpertParallelMoe:
                                             sc, rc), "b200_ep_stats")
         return st.value, list(sc), list(rc)
 
+    def phase_profile(self, enable=True):
+        """Benchmark hook: switch the phase timeline on / off; returns the last step's phase times in ms (a dict)
+        when it was on."""
+        C = self._C
+        ms = (C.c_float * 6)()
+        self._check(self._lib.b200_ep_phase_profile(self._h, 1 if enable else 0, ms), "b200_ep_phase_profile")
+        names = ("route_plan", "dispatch", "wait_senders", "local_experts", "push", "combine_incl_wait")
+        return {n: float(v) for n, v in zip(names, ms)}
+
     def workspace(self):
         """Handle of the object's workspace (for moe_fp8_profile / moe_fp8_profile_read)."""
         return self._lib.b200_ep_workspace(self._h)
