@@ -599,8 +599,6 @@ int b200_ep_create(b200_ep** out, const b200_ep_config* cfg, const int* owner_ma
     B200_CUDA_TRY(cudaMemcpy(ep->d_local, loc.data(), sizeof(int) * E, cudaMemcpyHostToDevice));
     // scratch of the owner-side grouped GEMMs at the worst case (every source sends all its tokens)
     {
-        b200_moe_fp8_config c{};
-        c.num_tokens = (int)WT; c.num_experts = ep->E_local; c.top_k = K; c.hidden_dim = D; c.intermediate_dim = I;
         const size_t TK = WT * K;
         const size_t need = TK * D + TK * (D / 128) * 4 + TK * I + TK * (I / 128) * 4 + TK * 24 + (size_t)E * 16 + (1 << 20);
         st = b200_ws_ensure(ep->ws, need);

@@ -350,7 +350,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid
             for (int tile = walker; tile < total_tiles; tile += pair_count) {
                 int e, m_tile, n_tile, cnt;
                 locate(tile, e, m_tile, n_tile, cnt);
-                if (duo && (tile | 1) < total_tiles) {        // the neighbour has a tile in this round too
+                if (duo && (tile | 1) < total_tiles) {        // the neighbour has a tile in this pass over the grid too
                     if (!pair_rendezvous(&sm->pair_go, peer_go, go_ph, abort_flag)) goto done;
                     go_ph ^= 1;
                 }
@@ -748,7 +748,7 @@ grouped_gemm_mx_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             for (int tile = walker; tile < total_tiles; tile += walkers) {
                 int e, m_tile, n_tile, cnt;
                 locate(tile, e, m_tile, n_tile, cnt);
-                if (duo && (tile | 1) < total_tiles) {        // the neighbour has a tile in this round too
+                if (duo && (tile | 1) < total_tiles) {        // the neighbour has a tile in this pass over the grid too
                     if (!pair_rendezvous(&sm->pair_go, peer_go, go_ph, abort_flag)) goto done;
                     go_ph ^= 1;
                 }
