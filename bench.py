@@ -39,6 +39,7 @@ ZIPF_S, ZIPF_BETA = 1.1, 0.08
 # all GPUs); "balanced": greedy placement by the expert loads of a calibration batch; "contiguous": blocks of E/N
 EP_PLACEMENT = "balanced"
 MOE_FLAGS = 0          # --moe-tiles: force the grouped GEMMs' tile shape (4 = single CTA, 8 = CTA pairs)
+POW2_SCALES = False    # --pow2-scales: variant run with power-of-two scales
 RTOL, ATOL = 2e-2, 1e-2
 
 
@@ -154,8 +155,8 @@ def build_moe(b200, torch, dev, world, rank):
     w1s = torch.empty((E_local, 2 * c["I"] // 128, c["D"] // 128), dtype=torch.float32, device=dev)
     w2q = torch.empty((E_local, c["D"], c["I"]), dtype=torch.uint8, device=dev)
     w2s = torch.empty((E_local, c["D"] // 128, c["I"] // 128), dtype=torch.float32, device=dev)
-    b200.fill_normal_fp8_w128_(w1q, w1s, 1000 + rank, 0.02)
-    b200.fill_normal_fp8_w128_(w2q, w2s, 2000 + rank, 0.02)
+    b200.fill_normal_fp8_w128_(w1q, w1s, 1000 + rank, 0.02, pow2=POW2_SCALES)
+    b200.fill_normal_fp8_w128_(w2q, w2s, 2000 + rank, 0.02, pow2=POW2_SCALES)
     gate_w = torch.empty((c["E"], c["D"]), dtype=torch.float32, device=dev)
     b200.fill_normal_(gate_w, 3000, c["D"] ** -0.5)
     bias_h = b200.synth_normal_host(3001, 0, c["E"], 0.01)
@@ -166,12 +167,11 @@ def build_moe(b200, torch, dev, world, rank):
     b200.fill_normal_(x, 4000 + rank, 1.0)
     xq = torch.empty((c["T"], c["D"]), dtype=torch.uint8, device=dev)
     xs = torch.empty((c["T"], c["D"] // 128), dtype=torch.float32, device=dev)
-    b200.quant_act_1x128(x, xq, xs)
+    b200.quant_act_1x128(x, xq, xs, pow2=POW2_SCALES)
     del x
     layer = b200.MoeFp8Layer(gate_w, bias, w1q, w1s, w2q, w2s, c["K"], b200.SCORE_SIGMOID_GROUPED, c["n_group"],
-                             c["topk_group"], c["routed_scale"])
+                             c["topk_group"], c["routed_scale"], flags=MOE_FLAGS)
     layer.pack()          # pre-tiled weights for the grouped GEMMs (the row-major copy stays for the CPU check)
-    layer.flags = MOE_FLAGS
     return layer, xq, xs
 
 
@@ -227,6 +227,14 @@ def moe_layer_bytes(counts):
     return w + c["T"] * (c["D"] + 4 * c["D"] // 128) + 4 * c["E"] * c["D"] + c["T"] * c["D"] * 4
 
 
+def _emulate(oracle, *a):
+    """oracle.moe_fp8_experts under the scale rule of this run (the requantisation between the GEMMs follows it)."""
+    if POW2_SCALES:
+        with oracle.pow2_scales():
+            return oracle.moe_fp8_experts(*a)
+    return oracle.moe_fp8_experts(*a)
+
+
 def moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out_dev, n_tokens, threads):
     """Oracle (CPU emulation of the same FP8 sequence) on a seeded sample of tokens: parity of the
     GPU output rows and the CPU throughput.  Only the experts the sample uses are copied to the host."""
@@ -249,7 +257,7 @@ def moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out_dev, n_tokens, thread
     w2q = layer.w2q.index_select(0, sel).cpu().numpy()
     w2s = layer.w2s.index_select(0, sel).cpu().numpy()
     t0 = time.perf_counter()
-    ref = oracle.moe_fp8_experts(xq_h, xs_h, w1q, w1s, w2q, w2s, remap[ids], wts,
+    ref = _emulate(oracle, xq_h, xs_h, w1q, w1s, w2q, w2s, remap[ids], wts,
                                  np.arange(n_tokens, dtype=np.int32))
     t_ffn = time.perf_counter() - t0
     got = out_dev.index_select(0, torch.from_numpy(toks).to(xq.device).long()).cpu().numpy()
@@ -520,8 +528,8 @@ def ep_parity_sample(b200, torch, oracle, layer, placement, world, xq, xs, out_d
     s1q, s1s = torch.empty_like(layer.w1q), torch.empty_like(layer.w1s)
     s2q, s2s = torch.empty_like(layer.w2q), torch.empty_like(layer.w2s)
     for r in sorted(set(owner[uniq].tolist())):
-        b200.fill_normal_fp8_w128_(s1q, s1s, 1000 + r, 0.02)        # the weights rank r generated for itself
-        b200.fill_normal_fp8_w128_(s2q, s2s, 2000 + r, 0.02)
+        b200.fill_normal_fp8_w128_(s1q, s1s, 1000 + r, 0.02, pow2=POW2_SCALES)   # the weights rank r generated for itself
+        b200.fill_normal_fp8_w128_(s2q, s2s, 2000 + r, 0.02, pow2=POW2_SCALES)
         mine = uniq[owner[uniq] == r]
         sel = torch.from_numpy(local[mine]).to(xq.device)
         dst = remap[mine]
@@ -529,7 +537,7 @@ def ep_parity_sample(b200, torch, oracle, layer, placement, world, xq, xs, out_d
         w2q_h[dst], w2s_h[dst] = s2q.index_select(0, sel).cpu().numpy(), s2s.index_select(0, sel).cpu().numpy()
     del s1q, s1s, s2q, s2s
     t0 = time.perf_counter()
-    ref = oracle.moe_fp8_experts(xq_h, xs_h, w1q_h, w1s_h, w2q_h, w2s_h, remap[ids], wts,
+    ref = _emulate(oracle, xq_h, xs_h, w1q_h, w1s_h, w2q_h, w2s_h, remap[ids], wts,
                                  np.arange(n_tokens, dtype=np.int32))
     cpu_s += time.perf_counter() - t0
     got = out_dev.index_select(0, sel_t).float().cpu().numpy()
@@ -882,6 +890,9 @@ def main():
     ap.add_argument("--skip-moe", action="store_true")
     ap.add_argument("--cpu-tokens", type=int, default=96)
     ap.add_argument("--cpu-queries", type=int, default=16)
+    ap.add_argument("--pow2-scales", action="store_true",
+                    help="variant run, not the headline: all weights and activations quantised with power-of-two "
+                         "scales and the layer run with MOE_POW2_SCALES (hardware block-scaled MMA), at any N")
     ap.add_argument("--skip-pow2", action="store_true",
                     help="skip the secondary measurement of the power-of-two-scale variant of the MoE layer")
     ap.add_argument("--route-only", action="store_true",
@@ -898,9 +909,13 @@ def main():
     ap.add_argument("--ep-placement", default="balanced", choices=["balanced", "strided", "contiguous"],
                     help="expert placement of the expert-parallel layer (N > 1)")
     args = ap.parse_args()
-    global EP_PLACEMENT, MOE_FLAGS
+    global EP_PLACEMENT, MOE_FLAGS, POW2_SCALES
     EP_PLACEMENT = args.ep_placement
     MOE_FLAGS = {"auto": 0, "single": 4, "pair": 8}[args.moe_tiles]
+    POW2_SCALES = bool(args.pow2_scales)
+    if POW2_SCALES:
+        MOE_FLAGS |= 32          # MOE_POW2_SCALES
+        args.skip_pow2 = True
     if args.small:
         MOE.update(T=512, E=32, n_group=4, topk_group=2)
         DSA.update(B=16, seq_min=8192, seq_max=16384)
@@ -951,6 +966,7 @@ def main():
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3",
                 "data": "synthetic",
                 "config": {"workload": ("profiling-sized case, not a bench value: " if args.small else "")
+                           + ("VARIANT with power-of-two (UE8M0) scales, not the headline configuration: " if POW2_SCALES else "")
                            + ("C3" if world == 1 else "C5") + f": FP8 block-scale MoE layer, D={c['D']} I={c['I']} "
                            f"E={c['E']} top-{c['K']} ({c['n_group']} groups / top-{c['topk_group']}), sigmoid+bias scoring, "
                            f"routed_scaling 2.5, T={c['T']} per GPU"

@@ -112,7 +112,7 @@ enum b200_moe_flags {
      * block-scaled MMA (tcgen05.mma kind::mxf8f6f4.block_scale): the scales are applied inside the tensor core,
      * the accumulator stays in TMEM for the whole K loop and the software promotion per 128-deep K block
      * disappears.  The requantisation between the two GEMMs also takes power-of-two scales.  Same tolerance as the
-     * default path against the fp32 emulation with the same scale rule.  Single GPU entry points only. */
+     * default path against the fp32 emulation with the same scale rule.  Also accepted in b200_ep_config.flags. */
     B200_MOE_POW2_SCALES = 32
 };
 
@@ -328,6 +328,8 @@ enum b200_ep_flags {
     /* partial rows travel back as fp32 (twice the combine bytes).  Default: fp16 values relative to the row's
      * largest magnitude plus that magnitude, i.e. 11 significant bits against the row maximum */
     B200_EP_COMBINE_F32 = 2
+    /* B200_MOE_EXACT_ROUTER_LOGITS and B200_MOE_POW2_SCALES (enum b200_moe_flags; their values do not collide with
+     * the one above) may be set as well and mean what they mean for the single-GPU layer. */
 };
 typedef struct b200_ep_config {
     int rank, world;      /* this rank, number of ranks (<= 64); rank g holds num_experts / world experts */

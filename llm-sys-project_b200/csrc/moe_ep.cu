@@ -689,7 +689,7 @@ int b200_ep_forward(b200_ep* ep, int num_tokens, const uint8_t* xq, const float*
     b200_moe_fp8_config lc{};
     lc.num_tokens = W * c.max_tokens; lc.num_experts = ep->E_local; lc.top_k = K; lc.hidden_dim = D;
     lc.intermediate_dim = c.intermediate_dim; lc.scoring = c.scoring; lc.n_group = 1; lc.topk_group = 1;
-    lc.routed_scale = 1.0f; lc.flags = 0;
+    lc.routed_scale = 1.0f; lc.flags = c.flags & B200_MOE_POW2_SCALES;
     st = b200_moe_fp8_experts_accumulate(ep->ws, reinterpret_cast<const uint8_t*>(ep->xbuf + e.L.recv_q),
                                          reinterpret_cast<const float*>(ep->xbuf + e.L.recv_s),
                                          reinterpret_cast<const int*>(ep->xbuf + e.L.recv_id),

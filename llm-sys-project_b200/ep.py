@@ -233,6 +233,7 @@ class PeerExpertParallelMoe:
         if combine_dtype not in (torch.float16, torch.float32):
             raise ValueError("combine_dtype: torch.float16 (row-scaled, the default) or torch.float32")
         flags = 0 if combine_dtype == torch.float16 else 2
+        flags |= int(layer.flags) & (16 | 32)         # exact router logits, power-of-two scales: as for the plain layer
         cfg = EpConfig(self.rank, self.world, max_tokens, num_experts, layer.K, layer.D, layer.I, layer.scoring,
                        layer.n_group, layer.topk_group, layer.routed_scale, flags, int(wait_limit_ms))
         om = lm = None

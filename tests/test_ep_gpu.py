@@ -109,28 +109,31 @@ def test_ep_sum_rows_kernel(b200, cuda, dtype):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
-def _small_layer(b200, cuda, rng, T, E, K, D, I, ng, tg):
+def _small_layer(b200, cuda, rng, T, E, K, D, I, ng, tg, pow2=False):
+    import contextlib
     x = rng.normal(0, 1, (T, D)).astype(np.float32)
     wg = rng.normal(0, D ** -0.5, (E, D)).astype(np.float32)
     bias = rng.normal(0, 0.01, E).astype(np.float32)
-    xq, xs = oracle.quant_act(x)
-    w1q, w1s = oracle.quant_weight(rng.normal(0, 0.05, (E, 2 * I, D)).astype(np.float32))
-    w2q, w2s = oracle.quant_weight(rng.normal(0, 0.05, (E, D, I)).astype(np.float32))
+    with (oracle.pow2_scales() if pow2 else contextlib.nullcontext()):
+        xq, xs = oracle.quant_act(x)
+        w1q, w1s = oracle.quant_weight(rng.normal(0, 0.05, (E, 2 * I, D)).astype(np.float32))
+        w2q, w2s = oracle.quant_weight(rng.normal(0, 0.05, (E, D, I)).astype(np.float32))
     to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(cuda)
     layer = b200.MoeFp8Layer(to(wg), to(bias), to(w1q), to(w1s), to(w2q), to(w2s), K, b200.SCORE_SIGMOID_GROUPED, ng, tg,
-                             2.5)
+                             2.5, flags=b200.MOE_POW2_SCALES if pow2 else 0)
     return layer, (xq, xs, wg, bias, w1q, w1s, w2q, w2s), to
 
 
+@pytest.mark.parametrize("pow2", [False, True])
 @pytest.mark.parametrize("combine_dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("packed", [False, True])
-def test_peer_ep_world1_matches_plain_layer_and_oracle(b200, cuda, combine_dtype, packed):
+def test_peer_ep_world1_matches_plain_layer_and_oracle(b200, cuda, combine_dtype, packed, pow2):
     """The C-ABI expert-parallel object with one rank: dispatch into its own receive region, grouped GEMMs
     on the region, push and combine; several steps in a row with different token counts (the flag words
     carry the step number, buffers are reused)."""
     rng = np.random.default_rng(17)
     T, E, K, D, I = 96, 16, 4, 512, 256
-    layer, (xq, xs, wg, bias, w1q, w1s, w2q, w2s), to = _small_layer(b200, cuda, rng, T, E, K, D, I, 4, 2)
+    layer, (xq, xs, wg, bias, w1q, w1s, w2q, w2s), to = _small_layer(b200, cuda, rng, T, E, K, D, I, 4, 2, pow2)
     if packed:
         layer.pack()
     ep = b200.PeerExpertParallelMoe(None, layer, E, max_tokens=T, combine_dtype=combine_dtype)
@@ -147,7 +150,9 @@ def test_peer_ep_world1_matches_plain_layer_and_oracle(b200, cuda, combine_dtype
             got = out.cpu().numpy()
             tol = 1e-4 if combine_dtype == torch.float32 else 2.0 ** -10
             assert np.allclose(got, plain, rtol=tol, atol=tol * np.abs(plain).max())   # fp16 is relative to the row maximum
-            ref = oracle.moe_fp8_experts(xq[:Ts], xs[:Ts], w1q, w1s, w2q, w2s, oi, ow, np.arange(Ts, dtype=np.int32))
+            import contextlib
+            with (oracle.pow2_scales() if pow2 else contextlib.nullcontext()):      # the emulation's requantisation rule
+                ref = oracle.moe_fp8_experts(xq[:Ts], xs[:Ts], w1q, w1s, w2q, w2s, oi, ow, np.arange(Ts, dtype=np.int32))
             assert not (np.abs(got - ref) > 1e-2 + 2e-2 * np.abs(ref)).any()
     finally:
         ep.close()
