@@ -418,6 +418,19 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
     e2e_s = (time.perf_counter() - t0) / args.steps
     # both buffers hold a result of the same input (the scatter-add order differs from run to run)
     e2e_same = bool(torch.allclose(out_hs[0][:64], out_hs[1][:64], rtol=1e-4, atol=1e-5))
+    # the step's copies alone (inputs in, result out, on two streams at once, no kernels): the floor the host link
+    # sets for the end-to-end step
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        with torch.cuda.stream(s_in):
+            xq.copy_(xq_h, non_blocking=True)
+            xs.copy_(xs_h, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            out_hs[i % 2].copy_(out, non_blocking=True)
+    torch.cuda.synchronize()
+    copy_only_s = (time.perf_counter() - t0) / args.steps
 
     threads = oracle.host_threads()
     cpu = moe_cpu_sample(b200, torch, oracle, layer, xq, xs, out, args.cpu_tokens, threads)
@@ -439,6 +452,7 @@ def bench_moe_single(b200, torch, oracle, dev, args, sampler):
         "value": c["T"] / (ms * 1e-3), "ms_per_step": ms, "gpu_launches": int(launches),
         "e2e": {"value": c["T"] / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": int(xq_h.numel() + xs_h.numel() * 4),
                 "d2h_bytes_per_step": int(out_h.numel() * 4), "ms_per_step": e2e_s * 1e3,
+                "copies_only_ms_per_step": copy_only_s * 1e3,
                 "mode": "double-buffered host pipeline (MoeFp8Layer.forward_host_async): every step copies its "
                         "inputs in and its result out; copies overlap the neighbouring steps' kernels",
                 "synchronous_value": c["T"] / e2e_sync_s, "synchronous_ms_per_step": e2e_sync_s * 1e3,
@@ -655,6 +669,24 @@ def bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler):
     te = torch.tensor([(time.perf_counter() - t0) / args.steps], device=dev, dtype=torch.float64)
     dist.all_reduce(te, op=dist.ReduceOp.MAX)
     e2e_s = float(te.item())
+    # the same host pipeline with the copies only (no kernels): what the ranks' shared host memory and PCIe paths
+    # allow when all ranks copy at once; e2e close to it means the step is bound by the host side, not by the GPUs
+    def copy_only(dq, ds, do):
+        return None
+    for i in range(2):
+        tk = pipe.submit([xq_h, xs_h], out_hs[i % 2], copy_only)
+    tk.synchronize()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        tk = pipe.submit([xq_h, xs_h], out_hs[i % 2], copy_only)
+    tk.synchronize()
+    torch.cuda.synchronize()
+    dist.barrier()
+    tc = torch.tensor([(time.perf_counter() - t0) / args.steps], device=dev, dtype=torch.float64)
+    dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+    copy_only_s = float(tc.item())
     if EP_PLACEMENT == "balanced":
         own = placement[0].numpy()
         per_gpu = np.array([counts[own == g].sum() for g in range(world)])
@@ -669,7 +701,9 @@ def bench_moe_ep(b200, torch, oracle, dist, dev, args, world, rank, sampler):
         "e2e": {"value": world * c["T"] / e2e_s, "unit": "tokens/s",
                 "h2d_bytes_per_step": int(world * (xq_h.numel() + xs_h.numel() * 4)),
                 "d2h_bytes_per_step": int(world * out_h.numel() * 4), "ms_per_step": e2e_s * 1e3,
-                "mode": "double-buffered host pipeline (HostPipeline around ExpertParallelMoe.forward)"},
+                "copies_only_ms_per_step": copy_only_s * 1e3,
+                "mode": "double-buffered host pipeline (HostPipeline around ExpertParallelMoe.forward); "
+                        "copies_only_ms_per_step = the same pipeline without kernels, all ranks copying at once"},
         # with E / N experts per GPU and ~32 K rows the grouped GEMMs are bound by the tensor pipe, not by HBM
         "roofline": {"kernel": "grouped_gemm_fp8<1> + <2> on rank 0", "bound": "tensor",
                      "achieved": flops_rank0 / ((g1_ms + g2_ms) * 1e-3) / 1e12 if g1_ms > 0 else None,
