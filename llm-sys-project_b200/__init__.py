@@ -74,7 +74,7 @@ EXPORTED_SYMBOLS = [
 ]
 # exported for the test suite only (declared in csrc/selftest.h, not in the public header)
 TEST_ONLY_SYMBOLS = ["b200_umma_selftest", "b200_wait_selftest", "b200_ep_connect_loopback", "b200_fp8_mma_rate",
-                     "b200_moe_gate_logits_tc", "b200_moe_route_last_flagged", "b200_mx_selftest", "b200_ep_phase_profile"]
+                     "b200_moe_gate_logits_tc", "b200_moe_route_last_flagged", "b200_mx_selftest", "b200_ep_phase_profile", "b200_tc_plan_selftest"]
 
 
 def lib():

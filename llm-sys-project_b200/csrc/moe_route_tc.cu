@@ -30,6 +30,7 @@
 #include "moe_internal.cuh"
 #include "selftest.h"
 #include "tma_host.cuh"
+#include <vector>
 
 namespace {
 
@@ -333,6 +334,45 @@ int launch_gate_logits_tc(const uint8_t* xq, const float* xs, const float* wg, f
     B200_CUDA_TRY(cudaGetLastError());
     *plan_out = plan;
     return B200_OK;
+}
+
+// Test hook (host only, no GPU needed): walks the work split of T tokens x D on `sms` CTAs exactly as the kernel's
+// roles do and checks that every tile's pieces get the slots 0 .. n-1 in order of d, cover its blocks once, and
+// stay within the bound the scratch is sized with.  Returns 0 when consistent, a positive code otherwise;
+// *max_slots_out receives the largest number of slots of a tile.
+extern "C" int b200_tc_plan_selftest(int T, int D, int sms, int chain_blocks, int* max_slots_out) {
+    if (T <= 0 || D <= 0 || D % 128 || sms <= 0 || chain_blocks < 0) return B200_BAD_ARG;
+    TcPlan plan;
+    plan.nblk = D / 128;
+    plan.ch = min(chain_blocks > 0 ? chain_blocks : TC_CHAIN, plan.nblk);
+    const int ntile = ceil_div(T, TM);
+    const long long units = (long long)ntile * plan.nblk;
+    plan.L = max((int)((units + sms - 1) / sms), plan.ch);
+    const int grid = (int)((units + plan.L - 1) / plan.L);
+    std::vector<int> next_slot(ntile, 0), next_kb(ntile, 0);
+    for (int c = 0; c < grid; c++) {
+        const int u0 = c * plan.L;
+        const long long end = (long long)u0 + plan.L;
+        const int u1 = (int)(end < units ? end : units);
+        for (int u = u0; u < u1;) {
+            const int tile = u / plan.nblk, kb = u - tile * plan.nblk;
+            const int len = min(plan.ch, min(plan.nblk - kb, u1 - u));
+            if (tc_slots_before(plan, tile, u) != next_slot[tile]) return 101;      // slots count up in order of d
+            if (kb != next_kb[tile]) return 102;                                    // blocks covered once, in order
+            next_slot[tile]++;
+            next_kb[tile] += len;
+            u += len;
+        }
+    }
+    int mx = 0;
+    for (int t = 0; t < ntile; t++) {
+        if (next_kb[t] != plan.nblk) return 103;
+        if (tc_slots_before(plan, t, (t + 1) * plan.nblk) != next_slot[t]) return 104;     // what the selection kernel adds up
+        mx = max(mx, next_slot[t]);
+    }
+    if (mx > 2 * ceil_div(plan.nblk, plan.ch) + 1) return 105;                      // the bound of moe_gate_tc_slots
+    if (max_slots_out) *max_slots_out = mx;
+    return 0;
 }
 
 // Test hook: the tensor-core logits [T, E] (a token's partial sums added in slot order).  chain_blocks > 0 asks

@@ -32,6 +32,10 @@ B200_API int b200_fp8_mma_rate(int pair, int iters, float* tflops, float* ms, b2
 B200_API int b200_mx_selftest(const void* a, const void* b, const void* sfa, const void* sfb, float* d, int N, int K,
                               b200_stream_t stream);
 
+/* Work split of the tensor-core router logits kernel, checked on the host (no GPU): 0 when every tile's partial
+ * sums get consecutive slots in order of d, cover d once and stay within the bound the scratch is sized with. */
+B200_API int b200_tc_plan_selftest(int T, int D, int sms, int chain_blocks, int* max_slots_out);
+
 /* The approximate router logits [T, E] of the tensor-core path, for the test that bounds their distance from the
  * fixed-order FMA chains.  chain_blocks: length of the accumulation chains in 128-deep blocks of d (0 = the
  * library's choice, D / 128 = one chain over all of d).  B200_UNSUPPORTED when the shape does not take that path. */
