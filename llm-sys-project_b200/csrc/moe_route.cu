@@ -486,9 +486,10 @@ route_select_kernel(const float* __restrict__ partials, int n_chunks, const floa
     }
 }
 
-// The register path as a kernel of its own (fewer registers than the generic kernel: more resident warps).
+// The register path as a kernel of its own (fewer registers than the generic kernel: more resident warps).  Seven
+// blocks per SM (72 registers, a few spilled words): 148 x 7 x 4 warps take 4096 tokens in one wave.
 template <int PER>
-__global__ void __launch_bounds__(128, 5)
+__global__ void __launch_bounds__(128, 7)
 route_select_regs_kernel(const float* __restrict__ partials, int n_chunks, const float* __restrict__ bias,
                          int* __restrict__ ids, float* __restrict__ wts, int* __restrict__ counts,
                          float* __restrict__ logits_out, int T, int E, int K, int n_group, int topk_group,
